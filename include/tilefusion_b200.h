@@ -1,0 +1,214 @@
+/*
+ * tilefusion_b200 -- C-ABI of the fused-attention path (prefill + flash
+ * decoding) for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and strides; no torch
+ * types cross this boundary.  The torch operator layer
+ * (tilefusion_b200/csrc/torch_bind.cc) and the tests bind exactly these
+ * symbols.  All functions return 0 on success or a negative TfStatus; the
+ * text of the last failure on the calling thread is available from
+ * tf_last_error().  Nothing here calls exit() or abort().
+ *
+ * Which interface of microsoft/TileFusion each entry point stands in for is
+ * cited as file:line (paths relative to the TileFusion source tree).
+ */
+#ifndef TILEFUSION_B200_H_
+#define TILEFUSION_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TF_EXPORT __attribute__((visibility("default")))
+
+typedef enum TfStatus {
+  TF_OK = 0,
+  TF_ERR_BAD_ARG = -1,       /* null pointer, non-positive size, bad stride   */
+  TF_ERR_UNSUPPORTED = -2,   /* shape / dtype / layout with no compiled kernel */
+  TF_ERR_CUDA = -3,          /* a CUDA runtime or driver call failed          */
+  TF_ERR_DEVICE_TIMEOUT = -4,/* a bounded device-side wait ran out            */
+  TF_ERR_WORKSPACE = -5      /* caller's workspace is too small               */
+} TfStatus;
+
+typedef enum TfDType { TF_F16 = 0, TF_BF16 = 1 } TfDType;
+
+/*
+ * Prefill attention problem: O = softmax(Q K^T * scale [+ causal]) V, fp32
+ * accumulation, one independent problem per (batch, head).
+ *
+ * All strides are in ELEMENTS.  Q and O rows must be contiguous (stride 1
+ * along the head dimension).  K is addressed as K[l, d] and V as V[l, d]; for
+ * each of them exactly one of (stride_l, stride_d) must be 1:
+ *   k_stride_d == 1 : K stored [Lk, D] row-major  (the operand layout of
+ *                     TileFusion's op, src/kernels/flash_attn.cu:73-76)
+ *   k_stride_l == 1 : K stored [D, Lk] row-major  (the `key` argument of
+ *                     python/ops/flash_attention.py:45-83 before its .t() copy)
+ *   v_stride_d == 1 : V stored [Lk, Dv] row-major (the `value` argument there)
+ *   v_stride_l == 1 : V stored [Dv, Lk] row-major (the op's V^T operand)
+ * Both forms feed the tensor cores directly (K-major / MN-major shared-memory
+ * descriptors); no transposing copy is ever made.
+ */
+typedef struct TfAttnDesc {
+  int32_t dtype;        /* TfDType                                            */
+  int32_t batch;        /* B                                                  */
+  int32_t heads;        /* H                                                  */
+  int32_t len_q;        /* Lq >= 1                                            */
+  int32_t len_kv;       /* Lk >= 1                                            */
+  int32_t head_dim;     /* D  in {64, 128}                                    */
+  int32_t head_dim_v;   /* Dv, must equal D                                   */
+  int32_t causal;       /* 1: mask key index > query index (top-left aligned,
+                           include/cell/mask.hpp:19-113)                      */
+  float softmax_scale;  /* multiplies Q K^T before the softmax                */
+  int32_t tile_q;       /* hint; 0 lets the registry choose                   */
+  int32_t tile_kv;      /* hint; 0 lets the registry choose                   */
+  int32_t reserved;
+  int64_t q_stride_b, q_stride_h, q_stride_l;
+  int64_t k_stride_b, k_stride_h, k_stride_l, k_stride_d;
+  int64_t v_stride_b, v_stride_h, v_stride_l, v_stride_d;
+  int64_t o_stride_b, o_stride_h, o_stride_l;
+} TfAttnDesc;
+
+/*
+ * Flash-decoding problem: one query row per (batch, head) against Lk keys.
+ * Q[B,H,D], K[B,H,Lk,D], V[B,H,Lk,D], O[B,H,D]; rows of K and V are
+ * contiguous with stride D between consecutive keys.  Strides in elements.
+ */
+typedef struct TfDecodeDesc {
+  int32_t dtype;        /* TfDType                                            */
+  int32_t batch;
+  int32_t heads;
+  int32_t len_kv;       /* keys held by THIS call (a shard when KV is split
+                           across GPUs); may be 0                             */
+  int32_t head_dim;     /* D in {64, 128}                                     */
+  int32_t kv_chunk;     /* keys per chunk, a multiple of 128; 0 -> 512        */
+  int32_t num_splits;   /* splits per (b,h); 0 lets the registry choose       */
+  float softmax_scale;
+  int64_t q_stride_b, q_stride_h;
+  int64_t k_stride_b, k_stride_h;
+  int64_t v_stride_b, v_stride_h;
+  int64_t o_stride_b, o_stride_h;
+} TfDecodeDesc;
+
+/* What the registry chose for a decode problem (tf_decode_plan). */
+typedef struct TfDecodePlan {
+  int32_t num_splits;        /* partial rows per (b,h)                        */
+  int32_t chunks_per_split;  /* kv_chunk-sized chunks walked by one split     */
+  int32_t kv_chunk;
+  int32_t grid;              /* CTAs of the split kernel                      */
+  int32_t stages;            /* depth of the shared-memory ring               */
+  int32_t reserved;
+  uint64_t workspace_bytes;  /* fp32 partials: B*H*num_splits*(D+2)*4         */
+} TfDecodePlan;
+
+/* What the registry chose for a prefill problem (tf_attn_plan). */
+typedef struct TfAttnPlan {
+  int32_t tile_q;
+  int32_t tile_kv;
+  int32_t ctas_per_sm;
+  int32_t grid;
+  int32_t k_mn_major;   /* 1 when K is read as [D, Lk]                        */
+  int32_t v_mn_major;   /* 1 when V is read as [Lk, Dv]                       */
+  uint64_t smem_bytes;
+} TfAttnPlan;
+
+/* ---- prefill ------------------------------------------------------------ */
+
+/*
+ * Fused attention forward on `stream` (a cudaStream_t; NULL = legacy stream).
+ * Replaces the host operator tilefusion::kernels::flash_attention
+ * (include/kernels/ops.hpp:54-58, src/kernels/flash_attn.cu:58-152) and the
+ * kernel it JIT-compiles (include/kernels/flash_attention_device.cuh:130-312).
+ * `lse` may be NULL; otherwise it receives log-sum-exp rows, fp32 [B,H,Lq],
+ * natural log of sum(exp(scale * q.k)).  Asynchronous: no device sync.
+ */
+TF_EXPORT int tf_attn_fwd(const void* q, const void* k, const void* v, void* o,
+                          float* lse, const TfAttnDesc* desc, void* stream);
+
+/*
+ * Tile plan the registry would use for `desc`.  Stands in for the tile
+ * arguments the reference bakes in as template constants
+ * (src/kernels/flash_attn.cu:16-55, :87-99) and for its per-shape JIT cache
+ * (src/jit/compiler.cc:123-145): variants here are compiled ahead of time and
+ * looked up by (dtype, head_dim).
+ */
+TF_EXPORT int tf_attn_plan(const TfAttnDesc* desc, TfAttnPlan* plan);
+
+/* ---- flash decoding (no counterpart in the reference: it has no decode
+ *      op; registered in the style of include/kernels/kernel_list.hpp:25-30) */
+
+/* Split count, grid and workspace size for `desc`. */
+TF_EXPORT int tf_decode_plan(const TfDecodeDesc* desc, TfDecodePlan* plan);
+
+/*
+ * Split-KV pass: for every (b, h, split) writes one partial row into
+ * `workspace`: D fp32 of un-normalised output, then (m, l) with m the running
+ * maximum of scale*log2(e)*q.k and l the sum of 2^(s-m).
+ * Workspace layout: [B*H*num_splits][D] fp32, then [B*H*num_splits][2] fp32.
+ */
+TF_EXPORT int tf_decode_split(const void* q, const void* k, const void* v,
+                              void* workspace, uint64_t workspace_bytes,
+                              const TfDecodeDesc* desc, void* stream);
+
+/*
+ * Log-sum-exp combine of `n_parts` partial rows per (b,h).
+ *   part_o  : fp32, element (p, r, d) at part_o[p*part_stride_o + r*row_stride_o + d]
+ *   part_ml : fp32 pairs, (p, r) at part_ml[p*part_stride_ml + r*row_stride_ml]
+ * with r = b*H + h in [0, rows).  Exactly one output form is written:
+ *   final   : o (dtype, element (r, d) at o[(r/H)*o_stride_b + (r%H)*o_stride_h + d])
+ *             and, when non-NULL, lse fp32 [rows] (natural log);
+ *   merged  : when out_part_o != NULL, one fp32 partial row per r in the same
+ *             (O, then m,l) form: out_part_o[r*D + d], out_part_ml[r*2 + {0,1}].
+ */
+TF_EXPORT int tf_decode_combine(const float* part_o, const float* part_ml,
+                                int32_t n_parts, int64_t part_stride_o,
+                                int64_t row_stride_o, int64_t part_stride_ml,
+                                int64_t row_stride_ml, int32_t rows,
+                                int32_t heads, int32_t head_dim, int32_t dtype,
+                                void* o, int64_t o_stride_b, int64_t o_stride_h,
+                                float* lse, float* out_part_o,
+                                float* out_part_ml, void* stream);
+
+/* Split + combine: O[B,H,D] (dtype) and LSE[B,H] fp32 (may be NULL). */
+TF_EXPORT int tf_decode(const void* q, const void* k, const void* v, void* o,
+                        float* lse, void* workspace, uint64_t workspace_bytes,
+                        const TfDecodeDesc* desc, void* stream);
+
+/*
+ * Split + local merge for a KV shard: writes ONE partial row per (b,h) into
+ * `slot`, laid out [B*H][D] fp32 followed by [B*H][2] fp32 -- the send slot of
+ * an all-gather over the GPUs that hold the other shards.  tf_decode_gathered
+ * then combines the gathered slots.
+ */
+TF_EXPORT int tf_decode_partial(const void* q, const void* k, const void* v,
+                                float* slot, void* workspace,
+                                uint64_t workspace_bytes,
+                                const TfDecodeDesc* desc, void* stream);
+
+/* Final combine over `n_ranks` gathered slots (each B*H*(D+2) fp32). */
+TF_EXPORT int tf_decode_gathered(const float* slots, int32_t n_ranks,
+                                 int32_t batch, int32_t heads, int32_t head_dim,
+                                 int32_t dtype, void* o, int64_t o_stride_b,
+                                 int64_t o_stride_h, float* lse, void* stream);
+
+/* ---- diagnostics -------------------------------------------------------- */
+
+/* Text of the last error raised on the calling thread ("" if none). */
+TF_EXPORT const char* tf_last_error(void);
+
+/*
+ * Reads and clears the device-side status word of the current device
+ * (synchronises the device).  0 = every bounded wait completed; otherwise the
+ * code of the first wait that gave up, and TF_ERR_DEVICE_TIMEOUT is returned.
+ */
+TF_EXPORT int tf_device_status(int32_t* code_out);
+
+/* Library ABI version (bumped when a struct above changes). */
+TF_EXPORT int tf_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TILEFUSION_B200_H_ */

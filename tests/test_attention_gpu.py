@@ -1,0 +1,193 @@
+"""Parity of the CUDA prefill kernel with the oracle, through the C-ABI.
+
+Tolerances (fp16 in, fp32 accumulate, fp16 out): max-abs <= 2e-2 and
+relative-L2 <= 1e-3 on O, |LSE error| <= 1e-3.  For bf16 the output rounding
+alone (8 mantissa bits) gives a relative-L2 of about 1.7e-3, so the bf16 bound
+on relative-L2 is 4e-3; max-abs and LSE bounds are unchanged.
+"""
+
+import math
+
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 2e-2
+REL_L2 = {torch.float16: 1e-3, torch.bfloat16: 4e-3}
+LSE_ABS = 1e-3
+
+
+def _check(o, lse, ref_o, ref_lse, dtype):
+    assert torch.isfinite(o.float()).all(), "kernel left NaN/Inf in O"
+    assert orc.max_abs(o.cpu(), ref_o) <= MAX_ABS
+    assert orc.rel_l2(o.cpu(), ref_o) <= REL_L2[dtype]
+    if lse is not None:
+        assert torch.isfinite(lse).all(), "kernel left NaN/Inf in LSE"
+        assert orc.max_abs(lse.cpu(), ref_lse) <= LSE_ABS
+
+
+def _layout(t, order):
+    """Returns a tensor equal to `t` ([B,H,L,D]) whose memory is [B,H,D,L] when order == 'DL'."""
+    if order == "LD":
+        return t.contiguous()
+    return t.transpose(-1, -2).contiguous().transpose(-1, -2)
+
+
+@pytest.mark.parametrize("name", ["ref_case1", "ref_case2", "c1_head", "multi_kv"])
+@pytest.mark.parametrize("k_order,v_order", [("LD", "LD"), ("DL", "DL"), ("DL", "LD"), ("LD", "DL")])
+def test_golden_fixtures(golden, name, k_order, v_order):
+    from cabi_helpers import attn_fwd, device_status
+
+    data, meta = golden
+    m = meta[name]
+    q = torch.from_numpy(data[f"{name}.q"]).cuda()[None, None]
+    k = torch.from_numpy(data[f"{name}.key_t"]).cuda().t()[None, None]
+    v = torch.from_numpy(data[f"{name}.v"]).cuda()[None, None]
+    ref = torch.from_numpy(data[f"{name}.out_fp32"])[None, None]
+    o, lse = attn_fwd(q.contiguous(), _layout(k, k_order), _layout(v, v_order), m["softmax_scale"], m["causal"])
+    _, lse_ref = orc.attention_fp32(q.cpu(), k.cpu(), v.cpu(), m["softmax_scale"], m["causal"])
+    _check(o, lse, ref, lse_ref, torch.float16)
+    if m["has_fp16"]:
+        # the acceptance test of TileFusion's own suite (tests/python/test_flash_attn.py:199)
+        ref16 = torch.from_numpy(data[f"{name}.out_fp16"]).float()[None, None]
+        assert torch.allclose(ref16, o.float().cpu(), atol=1e-2, rtol=1e-2)
+    assert device_status() == 0
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_reference_suite_through_python_api(causal):
+    """TileFusion's two test cases, called as its test calls the op
+    (tests/python/test_flash_attn.py:143-199): key is [D, Lk]."""
+    import tilefusion_b200 as tilefusion
+
+    torch.manual_seed(1234)
+    lq = 128 if causal else 64
+    query = torch.randn(lq, 128, dtype=torch.float16, device="cuda")
+    key = torch.randn(128, 128, dtype=torch.float16, device="cuda")
+    value = torch.randn(128, 128, dtype=torch.float16, device="cuda")
+    scale = 1.0 / math.sqrt(128)
+    out = tilefusion.ops.flash_attention(
+        query=query, key=key, value=value, tile_length_q=64, tile_length_kv=128,
+        tile_hidden_qk=128, tile_hidden_v=128, softmax_scale=scale, causal=causal)
+    ref, _ = orc.attention_fp32(query.cpu(), key.cpu().t(), value.cpu(), scale, causal)
+    assert out.shape == (lq, 128) and out.dtype == torch.float16
+    assert torch.allclose(ref, out.float().cpu(), atol=1e-2, rtol=1e-2)
+    _check(out, None, ref, None, torch.float16)
+
+
+def test_config1_plumbing():
+    """B1 H8 Lq=Lk=128 D64, scale 1/8, seed 0."""
+    from cabi_helpers import attn_fwd
+
+    q, k, v = orc.seeded_inputs(0, (1, 8, 128, 64), (1, 8, 128, 64), (1, 8, 128, 64), 1.0)
+    o, lse = attn_fwd(q.cuda(), k.cuda(), v.cuda(), 0.125, False)
+    ref, lse_ref = orc.attention_fp32(q, k, v, 0.125, False)
+    _check(o, lse, ref, lse_ref, torch.float16)
+
+
+SHAPES = [
+    # B, H, Lq, Lk, D, causal
+    (1, 1, 128, 128, 128, False),
+    (2, 3, 100, 200, 128, False),    # ragged Q and KV tiles
+    (1, 2, 1, 1, 128, False),        # single query, single key
+    (1, 2, 1, 300, 64, False),
+    (2, 2, 384, 1024, 128, False),   # 8 KV tiles
+    (1, 4, 512, 512, 128, True),
+    (1, 2, 300, 200, 64, True),      # causal, Lq > Lk, ragged
+    (1, 2, 200, 456, 128, True),     # causal, Lq < Lk
+    (3, 5, 257, 129, 64, False),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+def test_shapes(shape, dtype):
+    from cabi_helpers import attn_fwd, device_status
+
+    b, h, lq, lk, d, causal = shape
+    q, k, v = orc.seeded_inputs(11, (b, h, lq, d), (b, h, lk, d), (b, h, lk, d), 1.0, dtype)
+    scale = 1.0 / math.sqrt(d)
+    o, lse = attn_fwd(q.cuda(), k.cuda(), v.cuda(), scale, causal)
+    ref, lse_ref = orc.attention_fp32(q, k, v, scale, causal)
+    _check(o, lse, ref, lse_ref, dtype)
+    assert device_status() == 0
+
+
+def test_large_scores_exercise_rescale():
+    """Row maxima that grow tile after tile force the O rescale path."""
+    from cabi_helpers import attn_fwd
+
+    b, h, lq, lk, d = 1, 2, 128, 1024, 128
+    q, k, v = orc.seeded_inputs(5, (b, h, lq, d), (b, h, lk, d), (b, h, lk, d), 1.0)
+    ramp = torch.linspace(0.2, 3.0, lk).view(1, 1, lk, 1)
+    k = (k.float() * ramp).half()
+    scale = 1.0
+    o, lse = attn_fwd(q.cuda(), k.cuda(), v.cuda(), scale, False)
+    ref, lse_ref = orc.attention_fp32(q, k, v, scale, False)
+    _check(o, lse, ref, lse_ref, torch.float16)
+
+
+def test_strided_views_need_no_copy():
+    """Q/K/V/O as slices of packed [B, L, 3, H, D] / [B, L, H, D] buffers."""
+    from cabi_helpers import attn_fwd
+
+    b, h, l, d = 2, 4, 256, 128
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(b, l, 3, h, d, generator=g).half().cuda()
+    q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    scale = 1.0 / math.sqrt(d)
+    o, lse = attn_fwd(q, k, v, scale, False)
+    ref, lse_ref = orc.attention_fp32(q.cpu(), k.cpu(), v.cpu(), scale, False)
+    _check(o, lse, ref, lse_ref, torch.float16)
+
+
+def test_config2_size_properties_and_subset():
+    """Full prefill config (B8 H32 L2048 D128, sigma 0.5, seed 1): a subset of
+    heads against the CPU oracle, every head against the same expression
+    evaluated in fp32 on the GPU, and two size-independent properties."""
+    from cabi_helpers import attn_fwd, device_status
+
+    b, h, l, d = 8, 32, 2048, 128
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q = (torch.randn(b, h, l, d, generator=g, device="cuda") * 0.5).half()
+    k = (torch.randn(b, h, l, d, generator=g, device="cuda") * 0.5).half()
+    v = (torch.randn(b, h, l, d, generator=g, device="cuda") * 0.5).half()
+    scale = 1.0 / math.sqrt(d)
+    o, lse = attn_fwd(q, k, v, scale, False)
+    assert device_status() == 0
+    # (1) CPU oracle on 4 heads
+    for (bi, hi) in [(0, 0), (3, 17), (7, 31), (5, 2)]:
+        ref, lse_ref = orc.attention_fp32(q[bi, hi].cpu(), k[bi, hi].cpu(), v[bi, hi].cpu(), scale)
+        _check(o[bi, hi], lse[bi, hi], ref, lse_ref, torch.float16)
+    # (2) every head against the fp32 expression on the GPU
+    worst_abs, num, den = 0.0, 0.0, 0.0
+    for bi in range(b):
+        ref, lse_ref = orc.attention_fp32(q[bi], k[bi], v[bi], scale)
+        diff = o[bi].float() - ref
+        worst_abs = max(worst_abs, diff.abs().max().item())
+        num += diff.double().pow(2).sum().item()
+        den += ref.double().pow(2).sum().item()
+        assert (lse[bi] - lse_ref).abs().max().item() <= LSE_ABS
+    assert worst_abs <= MAX_ABS and math.sqrt(num / den) <= REL_L2[torch.float16]
+    # (3) rows of softmax sum to one: V = 1 gives O = 1
+    ones = torch.ones_like(v[:1])
+    o1, _ = attn_fwd(q[:1], k[:1], ones, scale, False)
+    assert (o1.float() - 1.0).abs().max().item() <= 2e-3
+    # (4) permuting the keys (with their values) leaves O unchanged
+    perm = torch.randperm(l, device="cuda")
+    o2, lse2 = attn_fwd(q[:1], k[:1, :, perm].contiguous(), v[:1, :, perm].contiguous(), scale, False)
+    assert (o2.float() - o[:1].float()).abs().max().item() <= 5e-3
+    assert (lse2 - lse[:1]).abs().max().item() <= LSE_ABS
+
+
+def test_unsupported_inputs_report_errors():
+    from cabi_helpers import attn_fwd
+    from tilefusion_b200._cabi import TileFusionError, TF_ERR_UNSUPPORTED
+
+    q = torch.zeros(1, 1, 16, 96, dtype=torch.float16, device="cuda")
+    with pytest.raises(TileFusionError) as e:
+        attn_fwd(q, q, q, 1.0)
+    assert e.value.code == TF_ERR_UNSUPPORTED and "head_dim" in str(e.value)

@@ -1,0 +1,178 @@
+"""The C-ABI library and the host-side logic, without a GPU.
+
+No compute entry point is launched here: these tests check that the library
+loads, exports what the header declares, validates arguments before it
+touches CUDA, and that the registry plans sensibly.
+"""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from tilefusion_b200 import _cabi
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "tilefusion_b200.h").read_text()
+
+
+def test_library_exports_every_declared_symbol(native_lib):
+    declared = re.findall(r"TF_EXPORT\s+[\w\s\*]+?\b(tf_\w+)\s*\(", HEADER)
+    assert sorted(declared) == sorted(_cabi.EXPORTED)
+    for name in declared:
+        assert hasattr(native_lib, name), f"{name} is declared but not exported"
+    assert native_lib.tf_abi_version() == 1
+
+
+def test_struct_layouts_match_header():
+    # field order and types are mirrored by hand; sizes catch a drift
+    assert C.sizeof(_cabi.TfAttnDesc) == 12 * 4 + 14 * 8
+    assert C.sizeof(_cabi.TfDecodeDesc) == 8 * 4 + 8 * 8
+    assert C.sizeof(_cabi.TfDecodePlan) == 6 * 4 + 8
+    assert C.sizeof(_cabi.TfAttnPlan) == 6 * 4 + 8
+    for struct, cname in [(_cabi.TfAttnDesc, "TfAttnDesc"), (_cabi.TfDecodeDesc, "TfDecodeDesc"),
+                          (_cabi.TfDecodePlan, "TfDecodePlan"), (_cabi.TfAttnPlan, "TfAttnPlan")]:
+        body = re.search(r"typedef struct " + cname + r" \{(.*?)\} " + cname, HEADER, re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        names = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            decl = re.sub(r"^(u?int\d+_t|float)\s+", "", decl)
+            names += [n.strip() for n in decl.split(",")]
+        assert names == [f[0] for f in struct._fields_], cname
+
+
+def _attn_desc(**kw):
+    d = _cabi.TfAttnDesc()
+    d.dtype, d.batch, d.heads, d.len_q, d.len_kv = _cabi.TF_F16, 8, 32, 2048, 2048
+    d.head_dim = d.head_dim_v = 128
+    d.softmax_scale = 0.088
+    d.q_stride_l = d.k_stride_l = d.v_stride_l = d.o_stride_l = 128
+    d.k_stride_d = d.v_stride_d = 1
+    d.q_stride_h = d.k_stride_h = d.v_stride_h = d.o_stride_h = 2048 * 128
+    d.q_stride_b = d.k_stride_b = d.v_stride_b = d.o_stride_b = 32 * 2048 * 128
+    for k, v in kw.items():
+        setattr(d, k, v)
+    return d
+
+
+def test_attn_plan_and_layout_detection(native_lib):
+    plan = _cabi.TfAttnPlan()
+    assert native_lib.tf_attn_plan(C.byref(_attn_desc()), C.byref(plan)) == 0
+    assert (plan.tile_q, plan.tile_kv, plan.ctas_per_sm) == (128, 128, 2)
+    assert plan.grid == 16 * 32 * 8
+    assert (plan.k_mn_major, plan.v_mn_major) == (0, 1)     # K [Lk, D], V [Lk, Dv]
+    assert 0 < plan.smem_bytes * plan.ctas_per_sm <= 227 * 1024
+    # the layouts TileFusion's operator receives: K [Lk, D], V^T [Dv, Lk]
+    d = _attn_desc(v_stride_l=1, v_stride_d=2048)
+    assert native_lib.tf_attn_plan(C.byref(d), C.byref(plan)) == 0
+    assert (plan.k_mn_major, plan.v_mn_major) == (0, 0)
+    # the layouts its Python wrapper receives: key [D, Lk], value [Lk, Dv]
+    d = _attn_desc(k_stride_l=1, k_stride_d=2048)
+    assert native_lib.tf_attn_plan(C.byref(d), C.byref(plan)) == 0
+    assert (plan.k_mn_major, plan.v_mn_major) == (1, 1)
+
+
+@pytest.mark.parametrize("field,value,code,needle", [
+    ("head_dim", 96, _cabi.TF_ERR_UNSUPPORTED, "head_dim"),
+    ("dtype", 7, _cabi.TF_ERR_UNSUPPORTED, "half-precision"),
+    ("len_kv", 0, _cabi.TF_ERR_BAD_ARG, "positive"),
+    ("softmax_scale", -1.0, _cabi.TF_ERR_UNSUPPORTED, "softmax_scale"),
+    ("k_stride_d", 3, _cabi.TF_ERR_UNSUPPORTED, "K must be contiguous"),
+])
+def test_attn_validation_precedes_cuda(native_lib, field, value, code, needle):
+    d = _attn_desc(**{field: value})
+    if field == "head_dim":
+        d.head_dim_v = value
+    rc = native_lib.tf_attn_fwd(None, None, None, None, None, C.byref(d), None)
+    assert rc == code and needle in native_lib.tf_last_error().decode()
+
+
+def test_null_pointers_are_rejected(native_lib):
+    assert native_lib.tf_attn_fwd(None, None, None, None, None, C.byref(_attn_desc()), None) == _cabi.TF_ERR_BAD_ARG
+    assert native_lib.tf_attn_fwd(None, None, None, None, None, None, None) == _cabi.TF_ERR_BAD_ARG
+    assert native_lib.tf_decode_plan(None, None) == _cabi.TF_ERR_BAD_ARG
+
+
+def _decode_desc(b, h, lk, d=128, chunk=512, splits=0):
+    x = _cabi.TfDecodeDesc()
+    x.dtype, x.batch, x.heads, x.len_kv, x.head_dim = _cabi.TF_F16, b, h, lk, d
+    x.kv_chunk, x.num_splits, x.softmax_scale = chunk, splits, 0.088
+    x.q_stride_h = d
+    x.q_stride_b = h * d
+    x.k_stride_h = x.v_stride_h = lk * d
+    x.k_stride_b = x.v_stride_b = h * lk * d
+    return x
+
+
+@pytest.mark.parametrize("b,h,lk", [(32, 32, 8192), (4, 32, 131072), (4, 32, 16384), (1, 1, 1), (2, 3, 1000)])
+def test_decode_plan_covers_every_key(native_lib, b, h, lk):
+    plan = _cabi.TfDecodePlan()
+    assert native_lib.tf_decode_plan(C.byref(_decode_desc(b, h, lk)), C.byref(plan)) == 0
+    n_chunks = -(-lk // plan.kv_chunk)
+    assert plan.kv_chunk == 512
+    assert plan.num_splits * plan.chunks_per_split >= n_chunks
+    assert (plan.num_splits - 1) * plan.chunks_per_split < n_chunks      # no empty split
+    assert plan.workspace_bytes == b * h * plan.num_splits * 130 * 4
+    assert 1 <= plan.grid <= 2 * 148
+    # round-robin makespan within 2 % of perfect balance when there is enough work
+    items = b * h * plan.num_splits
+    if items >= 4 * plan.grid:
+        span = -(-items // plan.grid) * plan.chunks_per_split
+        assert span * plan.grid <= 1.02 * b * h * n_chunks + plan.grid * plan.chunks_per_split
+
+
+def test_decode_plan_honours_requested_splits(native_lib):
+    plan = _cabi.TfDecodePlan()
+    assert native_lib.tf_decode_plan(C.byref(_decode_desc(4, 8, 4096, splits=3)), C.byref(plan)) == 0
+    assert (plan.num_splits, plan.chunks_per_split) == (3, 3)
+    assert native_lib.tf_decode_plan(C.byref(_decode_desc(4, 8, 4096, splits=100)), C.byref(plan)) == 0
+    assert (plan.num_splits, plan.chunks_per_split) == (8, 1)
+
+
+@pytest.mark.parametrize("kw,needle", [
+    (dict(chunk=100), "kv_chunk"), (dict(chunk=2048), "kv_chunk"), (dict(d=96), "head_dim"),
+])
+def test_decode_validation(native_lib, kw, needle):
+    plan = _cabi.TfDecodePlan()
+    rc = native_lib.tf_decode_plan(C.byref(_decode_desc(1, 1, 1024, **kw)), C.byref(plan))
+    assert rc == _cabi.TF_ERR_UNSUPPORTED and needle in native_lib.tf_last_error().decode()
+
+
+def test_workspace_too_small_is_reported(native_lib):
+    d = _decode_desc(2, 2, 4096)
+    buf = (C.c_char * 64)()           # host memory: never dereferenced, the size check comes first
+    p = C.addressof(buf)
+    p += (-p) % 16
+    rc = native_lib.tf_decode(p, p, p, p, None, p, 16, C.byref(d), None)
+    assert rc == _cabi.TF_ERR_WORKSPACE and "workspace" in native_lib.tf_last_error().decode()
+
+
+def test_torch_operator_schema_matches_tilefusion():
+    """The schema string of include/kernels/kernel_list.hpp:25-30, verbatim."""
+    import torch
+
+    import tilefusion_b200
+
+    tilefusion_b200.load_torch_ops()
+    schema = str(torch.ops.tilefusion.flash_attention.default._schema)
+    expected = ("tilefusion::flash_attention(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, "
+                "int tile_length_q, int tile_length_kv, int tile_hidden_qk, int tile_hidden_v, "
+                "float softmax_scale, bool causal) -> ()")
+    assert schema == expected
+    for op in ("flash_attention_lse", "flash_decoding", "flash_decoding_partial", "flash_decoding_gathered"):
+        assert hasattr(torch.ops.tilefusion, op)
+
+
+def test_operator_refuses_cpu_tensors():
+    """No CPU fallback: the operators exist for the CUDA dispatch key only."""
+    import torch
+
+    import tilefusion_b200 as tilefusion
+
+    q = torch.zeros(64, 128, dtype=torch.float16)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        tilefusion.ops.flash_attention(q, q.t(), q, 64, 128, 128, 128, 0.1, False)

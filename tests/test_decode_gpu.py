@@ -1,0 +1,155 @@
+"""Parity of the CUDA flash-decoding kernels with the oracle, through the C-ABI.
+
+Tolerances: max-abs <= 2e-2, relative-L2 <= 1e-3 (4e-3 for bf16 outputs, whose
+rounding alone is ~1.7e-3), |LSE error| <= 1e-3; fp32 partials are compared
+with relative-L2 <= 1e-5.
+"""
+
+import math
+
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 2e-2
+REL_L2 = {torch.float16: 1e-3, torch.bfloat16: 4e-3}
+LSE_ABS = 1e-3
+
+
+def _inputs(seed, b, h, lk, d, dtype=torch.float16):
+    return orc.seeded_inputs(seed, (b, h, 1, d), (b, h, lk, d), (b, h, lk, d), 1.0, dtype)
+
+
+def _check(o, lse, ref_o, ref_lse, dtype):
+    assert torch.isfinite(o.float()).all() and torch.isfinite(lse).all()
+    assert orc.max_abs(o.cpu(), ref_o) <= MAX_ABS
+    assert orc.rel_l2(o.cpu(), ref_o) <= REL_L2[dtype]
+    assert orc.max_abs(lse.cpu(), ref_lse) <= LSE_ABS
+
+
+CASES = [
+    # B, H, Lk, D, kv_chunk, num_splits
+    (1, 1, 512, 128, 512, 0),
+    (2, 3, 1000, 128, 512, 0),     # ragged last chunk and stage
+    (1, 2, 1, 128, 512, 0),        # a single key
+    (2, 2, 130, 64, 128, 0),
+    (4, 8, 4096, 128, 512, 0),
+    (4, 8, 4096, 128, 512, 3),     # 8 chunks over 3 splits: uneven splits
+    (1, 4, 3000, 64, 256, 0),
+    (2, 2, 2048, 128, 1024, 1),    # one split walks two chunks: running (m, l)
+    (3, 5, 777, 128, 128, 0),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c)))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+def test_decode_matches_oracle(case, dtype):
+    from cabi_helpers import decode, device_status
+
+    b, h, lk, d, chunk, splits = case
+    q, k, v = _inputs(21, b, h, lk, d, dtype)
+    o, lse = decode(q.cuda(), k.cuda(), v.cuda(), None, chunk, splits)
+    ref, lse_ref = orc.decode_fp32(q, k, v)
+    _check(o, lse, ref, lse_ref, dtype)
+    assert device_status() == 0
+
+
+@pytest.mark.parametrize("lk,chunk,splits", [(4096, 512, 0), (1000, 256, 2), (2048, 512, 1)])
+def test_split_partials_match_oracle(lk, chunk, splits):
+    from cabi_helpers import decode_split
+
+    b, h, d = 2, 4, 128
+    q, k, v = _inputs(22, b, h, lk, d)
+    part_o, part_ml, plan = decode_split(q.cuda(), k.cuda(), v.cuda(), None, chunk, splits)
+    ref_o, ref_ml = orc.decode_split(q.squeeze(2), k, v, 1.0 / math.sqrt(d), plan.kv_chunk * plan.chunks_per_split)
+    assert part_o.shape == ref_o.shape
+    # m is a maximum over the same keys; l and O are sums in a different order
+    assert orc.max_abs(part_ml[..., 0].cpu(), ref_ml[..., 0]) <= 1e-4
+    assert orc.rel_l2(part_ml[..., 1].cpu(), ref_ml[..., 1]) <= 1e-5
+    assert orc.rel_l2(part_o.cpu(), ref_o) <= 1e-5
+
+
+@pytest.mark.parametrize("n_shards", [2, 4, 8])
+def test_sharded_partial_then_gathered(n_shards):
+    """The multi-GPU decode path on one GPU: each KV shard writes its slot, the
+    gathered combine merges them (the all-gather is the identity here)."""
+    from cabi_helpers import decode_gathered, decode_partial_into
+    from tilefusion_b200.shard import kv_slice
+
+    b, h, lk, d = 2, 4, 5000, 128
+    q, k, v = _inputs(23, b, h, lk, d)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    slots = torch.full((n_shards, b * h * (d + 2)), float("nan"), dtype=torch.float32, device="cuda")
+    for r in range(n_shards):
+        k0, k1 = kv_slice(lk, r, n_shards)
+        decode_partial_into(qc, kc[:, :, k0:k1].contiguous(), vc[:, :, k0:k1].contiguous(), slots[r])
+    o, lse = decode_gathered(slots, b, h, d, torch.float16)
+    ref, lse_ref = orc.decode_fp32(q, k, v)
+    _check(o, lse, ref, lse_ref, torch.float16)
+
+
+def test_empty_shard_contributes_nothing():
+    from cabi_helpers import decode_gathered, decode_partial_into
+
+    b, h, lk, d = 1, 2, 300, 128
+    q, k, v = _inputs(24, b, h, lk, d)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    slots = torch.full((2, b * h * (d + 2)), float("nan"), dtype=torch.float32, device="cuda")
+    decode_partial_into(qc, kc, vc, slots[0])
+    decode_partial_into(qc, kc[:, :, :0].contiguous(), vc[:, :, :0].contiguous(), slots[1])
+    o, lse = decode_gathered(slots, b, h, d, torch.float16)
+    ref, lse_ref = orc.decode_fp32(q, k, v)
+    _check(o, lse, ref, lse_ref, torch.float16)
+
+
+def test_python_api_matches_oracle():
+    import tilefusion_b200 as tilefusion
+
+    q, k, v = _inputs(25, 2, 4, 2500, 128)
+    o, lse = tilefusion.ops.flash_decoding(q.cuda(), k.cuda(), v.cuda())
+    ref, lse_ref = orc.decode_fp32(q, k, v)
+    assert o.shape == (2, 4, 1, 128) and lse.shape == (2, 4, 1)
+    _check(o, lse, ref, lse_ref, torch.float16)
+
+
+def test_config3_size_properties_and_subset():
+    """Full decode config (B32 H32 Lk8192 D128, seed 2): a subset of (b, h)
+    against the CPU oracle, all of them against the fp32 expression on the GPU,
+    and the V = 1 property."""
+    from cabi_helpers import decode, device_status
+
+    b, h, lk, d = 32, 32, 8192, 128
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn(b, h, 1, d, generator=g, device="cuda").half()
+    k = torch.randn(b, h, lk, d, generator=g, device="cuda").half()
+    v = torch.randn(b, h, lk, d, generator=g, device="cuda").half()
+    o, lse = decode(q, k, v)
+    assert device_status() == 0
+    for (bi, hi) in [(0, 0), (13, 7), (31, 31)]:
+        ref, lse_ref = orc.decode_fp32(q[bi:bi + 1, hi:hi + 1].cpu(), k[bi:bi + 1, hi:hi + 1].cpu(),
+                                       v[bi:bi + 1, hi:hi + 1].cpu())
+        _check(o[bi:bi + 1, hi:hi + 1], lse[bi:bi + 1, hi:hi + 1], ref, lse_ref, torch.float16)
+    worst, num, den = 0.0, 0.0, 0.0
+    for bi in range(b):
+        ref, lse_ref = orc.decode_fp32(q[bi:bi + 1], k[bi:bi + 1], v[bi:bi + 1])
+        diff = o[bi:bi + 1].float() - ref
+        worst = max(worst, diff.abs().max().item())
+        num += diff.double().pow(2).sum().item()
+        den += ref.double().pow(2).sum().item()
+        assert (lse[bi:bi + 1] - lse_ref).abs().max().item() <= LSE_ABS
+    assert worst <= MAX_ABS and math.sqrt(num / den) <= REL_L2[torch.float16]
+    o1, _ = decode(q[:2], k[:2], torch.ones_like(v[:2]))
+    assert (o1.float() - 1.0).abs().max().item() <= 2e-3
+
+
+def test_bad_arguments_report_errors():
+    from cabi_helpers import decode
+    from tilefusion_b200._cabi import TileFusionError, TF_ERR_UNSUPPORTED
+
+    q, k, v = _inputs(26, 1, 1, 256, 128)
+    with pytest.raises(TileFusionError) as e:
+        decode(q.cuda(), k.cuda(), v.cuda(), None, 100, 0)
+    assert e.value.code == TF_ERR_UNSUPPORTED and "kv_chunk" in str(e.value)

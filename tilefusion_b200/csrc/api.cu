@@ -1,0 +1,420 @@
+// C-ABI of the library (declared in include/tilefusion_b200.h): argument
+// validation, the variant registry's launch side, TMA tensor-map construction
+// and kernel launches.  Host-only planning logic lives in registry.cc.
+//
+// This is the single CUDA translation unit of the library; it includes the
+// kernel headers so that the device status word has one definition.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "attn_fwd_sm100.cuh"
+#include "decode_sm100.cuh"
+#include "registry.h"
+#include "tilefusion_b200.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define TF_CUDA_TRY(expr)                                                          \
+  do {                                                                             \
+    cudaError_t e__ = (expr);                                                      \
+    if (e__ != cudaSuccess)                                                        \
+      return fail(TF_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));   \
+  } while (0)
+
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library
+// does not link libcuda (it must load on machines without a driver).
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault,
+                                         &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Rank-4 tensor map over a 16-bit tensor: dims[0] is innermost (stride 1),
+// strides_elems[i] is the stride of dims[i+1] in elements.
+int encode_map(CUtensorMap* map, int dtype, const void* base, const uint64_t dims[4],
+               const int64_t strides_elems[3], uint32_t box0, uint32_t box1, const char* what) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return fail(TF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdims[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t gstr[3];
+  uint64_t packed = dims[0] * 2;
+  for (int i = 0; i < 3; ++i) {
+    // A dimension of extent 1 never advances; give it the packed stride so
+    // that any caller-provided value (0 for an expanded view) is acceptable.
+    uint64_t s = dims[i + 1] == 1 ? packed : (uint64_t)strides_elems[i] * 2;
+    if (strides_elems[i] < 0 && dims[i + 1] != 1)
+      return fail(TF_ERR_BAD_ARG, "%s: negative stride", what);
+    if (s % 16 != 0 || s == 0)
+      return fail(TF_ERR_UNSUPPORTED, "%s: stride of dim %d (%llu bytes) is not a positive multiple of 16 bytes",
+                  what, i + 1, (unsigned long long)s);
+    gstr[i] = s;
+    packed = s * dims[i + 1];
+  }
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0)
+    return fail(TF_ERR_UNSUPPORTED, "%s: base pointer is not 16-byte aligned", what);
+  cuuint32_t box[4] = {box0, box1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, dtype == TF_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                  4, const_cast<void*>(base), gdims, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TF_ERR_CUDA, "%s: cuTensorMapEncodeTiled returned %d", what, (int)r);
+  return TF_OK;
+}
+
+int check_attn_desc(const TfAttnDesc* d) {
+  if (d == nullptr) return fail(TF_ERR_BAD_ARG, "desc is null");
+  if (d->dtype != TF_F16 && d->dtype != TF_BF16)
+    return fail(TF_ERR_UNSUPPORTED, "the inputs and output must be half-precision (fp16 or bf16); got dtype code %d", d->dtype);
+  if (d->batch < 1 || d->heads < 1 || d->len_q < 1 || d->len_kv < 1)
+    return fail(TF_ERR_BAD_ARG, "batch, heads, len_q and len_kv must be positive (got %d, %d, %d, %d)",
+                d->batch, d->heads, d->len_q, d->len_kv);
+  if (d->head_dim != 64 && d->head_dim != 128)
+    return fail(TF_ERR_UNSUPPORTED, "head_dim %d has no compiled variant (64 and 128 do)", d->head_dim);
+  if (d->head_dim_v != d->head_dim)
+    return fail(TF_ERR_UNSUPPORTED, "head_dim_v (%d) must equal head_dim (%d)", d->head_dim_v, d->head_dim);
+  if (!(d->softmax_scale > 0.f) || !std::isfinite(d->softmax_scale))
+    return fail(TF_ERR_UNSUPPORTED, "softmax_scale must be positive and finite");
+  if (d->heads > 65535 || d->batch > 65535) return fail(TF_ERR_UNSUPPORTED, "batch and heads must each be <= 65535");
+  if (d->k_stride_d != 1 && d->k_stride_l != 1)
+    return fail(TF_ERR_UNSUPPORTED, "K must be contiguous along the head dim or along the key index");
+  if (d->v_stride_d != 1 && d->v_stride_l != 1)
+    return fail(TF_ERR_UNSUPPORTED, "V must be contiguous along the head dim or along the key index");
+  if (d->o_stride_l % 8 != 0 || d->o_stride_h % 8 != 0 || d->o_stride_b % 8 != 0)
+    return fail(TF_ERR_UNSUPPORTED, "O strides must be multiples of 8 elements (16-byte rows)");
+  return TF_OK;
+}
+
+int sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+  return n;
+}
+
+template <typename T, int D>
+int launch_attn(const void* q, const void* k, const void* v, void* o, float* lse, const TfAttnDesc* d,
+                const TfAttnPlan& plan, cudaStream_t stream) {
+  using Smem = tfb::AttnSmem<D>;
+  CUtensorMap mq, mk, mv;
+  const uint64_t B = d->batch, H = d->heads;
+  {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->len_q, H, B};
+    const int64_t str[3] = {d->q_stride_l, d->q_stride_h, d->q_stride_b};
+    if (int rc = encode_map(&mq, d->dtype, q, dims, str, 64, tfb::kAttnTile, "Q")) return rc;
+  }
+  if (!plan.k_mn_major) {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->len_kv, H, B};
+    const int64_t str[3] = {d->k_stride_l, d->k_stride_h, d->k_stride_b};
+    if (int rc = encode_map(&mk, d->dtype, k, dims, str, 64, tfb::kAttnTile, "K")) return rc;
+  } else {
+    const uint64_t dims[4] = {(uint64_t)d->len_kv, (uint64_t)D, H, B};
+    const int64_t str[3] = {d->k_stride_d, d->k_stride_h, d->k_stride_b};
+    if (int rc = encode_map(&mk, d->dtype, k, dims, str, 64, D, "K (stored [D, Lk])")) return rc;
+  }
+  if (plan.v_mn_major) {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->len_kv, H, B};
+    const int64_t str[3] = {d->v_stride_l, d->v_stride_h, d->v_stride_b};
+    if (int rc = encode_map(&mv, d->dtype, v, dims, str, 64, tfb::kAttnTile, "V")) return rc;
+  } else {
+    const uint64_t dims[4] = {(uint64_t)d->len_kv, (uint64_t)D, H, B};
+    const int64_t str[3] = {d->v_stride_d, d->v_stride_h, d->v_stride_b};
+    if (int rc = encode_map(&mv, d->dtype, v, dims, str, 64, D, "V (stored [Dv, Lk])")) return rc;
+  }
+
+  tfb::AttnFwdArgs args;
+  args.o = o;
+  args.lse = lse;
+  args.len_q = d->len_q;
+  args.len_kv = d->len_kv;
+  args.causal = d->causal ? 1 : 0;
+  args.k_mn_major = plan.k_mn_major;
+  args.v_mn_major = plan.v_mn_major;
+  args.scale_log2 = d->softmax_scale * 1.4426950408889634f;
+  args.o_stride_b = d->o_stride_b;
+  args.o_stride_h = d->o_stride_h;
+  args.o_stride_l = d->o_stride_l;
+  args.lse_stride_b = (long long)d->heads * d->len_q;
+  args.lse_stride_h = d->len_q;
+
+  auto kern = tfb::attn_fwd_kernel<T, D>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  TF_CUDA_TRY(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    TF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
+    configured_device = dev;
+  }
+  const int n_q_tiles = (d->len_q + tfb::kAttnTile - 1) / tfb::kAttnTile;
+  dim3 grid(n_q_tiles, d->heads, d->batch);
+  kern<<<grid, tfb::kAttnThreads, Smem::kBytes, stream>>>(mq, mk, mv, args);
+  TF_CUDA_TRY(cudaGetLastError());
+  return TF_OK;
+}
+
+int check_decode_desc(const TfDecodeDesc* d) {
+  if (d == nullptr) return fail(TF_ERR_BAD_ARG, "desc is null");
+  if (d->dtype != TF_F16 && d->dtype != TF_BF16)
+    return fail(TF_ERR_UNSUPPORTED, "the inputs and output must be half-precision (fp16 or bf16); got dtype code %d", d->dtype);
+  if (d->batch < 1 || d->heads < 1 || d->len_kv < 0)
+    return fail(TF_ERR_BAD_ARG, "batch and heads must be positive and len_kv non-negative (got %d, %d, %d)",
+                d->batch, d->heads, d->len_kv);
+  if (d->head_dim != 64 && d->head_dim != 128)
+    return fail(TF_ERR_UNSUPPORTED, "head_dim %d has no compiled variant (64 and 128 do)", d->head_dim);
+  if (!(d->softmax_scale > 0.f) || !std::isfinite(d->softmax_scale))
+    return fail(TF_ERR_UNSUPPORTED, "softmax_scale must be positive and finite");
+  const int chunk = d->kv_chunk == 0 ? 512 : d->kv_chunk;
+  if (chunk < 128 || chunk % 128 != 0 || chunk > tfb::kDecMaxChunk)
+    return fail(TF_ERR_UNSUPPORTED, "kv_chunk must be a multiple of 128 in [128, %d] (got %d)", tfb::kDecMaxChunk, chunk);
+  if (d->num_splits < 0) return fail(TF_ERR_BAD_ARG, "num_splits must be >= 0");
+  const int64_t s[] = {d->q_stride_b, d->q_stride_h, d->k_stride_b, d->k_stride_h,
+                       d->v_stride_b, d->v_stride_h};
+  for (int64_t x : s)
+    if (x % 8 != 0 || x < 0) return fail(TF_ERR_UNSUPPORTED, "Q/K/V strides must be non-negative multiples of 8 elements (16 bytes)");
+  return TF_OK;
+}
+
+bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+template <typename T, int D>
+int launch_decode_split(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
+                        const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream) {
+  constexpr int kStages = 3;
+  using Smem = tfb::DecodeSmem<D, kStages>;
+  tfb::DecodeSplitArgs a;
+  a.q = q;
+  a.k = k;
+  a.v = v;
+  a.part_o = part_o;
+  a.part_ml = part_ml;
+  a.heads = d->heads;
+  a.len_kv = d->len_kv;
+  a.kv_chunk = plan.kv_chunk;
+  a.num_splits = plan.num_splits;
+  a.chunks_per_split = plan.chunks_per_split;
+  a.items = d->batch * d->heads * plan.num_splits;
+  a.scale_log2 = d->softmax_scale * 1.4426950408889634f;
+  a.q_stride_b = d->q_stride_b;
+  a.q_stride_h = d->q_stride_h;
+  a.k_stride_b = d->k_stride_b;
+  a.k_stride_h = d->k_stride_h;
+  a.v_stride_b = d->v_stride_b;
+  a.v_stride_h = d->v_stride_h;
+  auto kern = tfb::decode_split_kernel<T, D, kStages>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  TF_CUDA_TRY(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    TF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
+    configured_device = dev;
+  }
+  const int grid = plan.grid < a.items ? plan.grid : a.items;
+  kern<<<grid, tfb::kDecThreads, Smem::kBytes, stream>>>(a);
+  TF_CUDA_TRY(cudaGetLastError());
+  return TF_OK;
+}
+
+template <typename T, int D>
+int launch_combine(const tfb::DecodeCombineArgs& a, int rows, cudaStream_t stream) {
+  dim3 block(D, tfb::kCombineGroups);
+  tfb::decode_combine_kernel<T, D><<<rows, block, 0, stream>>>(a);
+  TF_CUDA_TRY(cudaGetLastError());
+  return TF_OK;
+}
+
+int dispatch_combine(const tfb::DecodeCombineArgs& a, int rows, int head_dim, int dtype, cudaStream_t stream) {
+  if (head_dim == 128)
+    return dtype == TF_F16 ? launch_combine<__half, 128>(a, rows, stream)
+                           : launch_combine<__nv_bfloat16, 128>(a, rows, stream);
+  if (head_dim == 64)
+    return dtype == TF_F16 ? launch_combine<__half, 64>(a, rows, stream)
+                           : launch_combine<__nv_bfloat16, 64>(a, rows, stream);
+  return fail(TF_ERR_UNSUPPORTED, "head_dim %d has no compiled variant (64 and 128 do)", head_dim);
+}
+
+int dispatch_split(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
+                   const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream) {
+  if (d->head_dim == 128)
+    return d->dtype == TF_F16 ? launch_decode_split<__half, 128>(q, k, v, part_o, part_ml, d, plan, stream)
+                              : launch_decode_split<__nv_bfloat16, 128>(q, k, v, part_o, part_ml, d, plan, stream);
+  return d->dtype == TF_F16 ? launch_decode_split<__half, 64>(q, k, v, part_o, part_ml, d, plan, stream)
+                            : launch_decode_split<__nv_bfloat16, 64>(q, k, v, part_o, part_ml, d, plan, stream);
+}
+
+int plan_and_check_decode(const void* q, const void* k, const void* v, const void* workspace,
+                          uint64_t workspace_bytes, const TfDecodeDesc* d, TfDecodePlan* plan) {
+  if (int rc = check_decode_desc(d)) return rc;
+  if (q == nullptr || (d->len_kv > 0 && (k == nullptr || v == nullptr)) || workspace == nullptr)
+    return fail(TF_ERR_BAD_ARG, "q, k, v and workspace must be non-null");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(workspace))
+    return fail(TF_ERR_UNSUPPORTED, "q, k, v and workspace must be 16-byte aligned");
+  tfb::plan_decode(*d, sm_count(), plan);
+  if (workspace_bytes < plan->workspace_bytes)
+    return fail(TF_ERR_WORKSPACE, "workspace holds %llu bytes but %llu are needed",
+                (unsigned long long)workspace_bytes, (unsigned long long)plan->workspace_bytes);
+  return TF_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tf_attn_plan(const TfAttnDesc* desc, TfAttnPlan* plan) {
+  if (plan == nullptr) return fail(TF_ERR_BAD_ARG, "plan is null");
+  if (int rc = check_attn_desc(desc)) return rc;
+  tfb::plan_attn(*desc, sm_count(), plan);
+  plan->smem_bytes = desc->head_dim == 128 ? tfb::AttnSmem<128>::kBytes : tfb::AttnSmem<64>::kBytes;
+  return TF_OK;
+}
+
+int tf_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const TfAttnDesc* desc,
+                void* stream) {
+  if (int rc = check_attn_desc(desc)) return rc;
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr)
+    return fail(TF_ERR_BAD_ARG, "q, k, v and o must be non-null");
+  if (!aligned16(o)) return fail(TF_ERR_UNSUPPORTED, "o must be 16-byte aligned");
+  TfAttnPlan plan;
+  tfb::plan_attn(*desc, sm_count(), &plan);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (desc->head_dim == 128)
+    return desc->dtype == TF_F16 ? launch_attn<__half, 128>(q, k, v, o, lse, desc, plan, s)
+                                 : launch_attn<__nv_bfloat16, 128>(q, k, v, o, lse, desc, plan, s);
+  return desc->dtype == TF_F16 ? launch_attn<__half, 64>(q, k, v, o, lse, desc, plan, s)
+                               : launch_attn<__nv_bfloat16, 64>(q, k, v, o, lse, desc, plan, s);
+}
+
+int tf_decode_plan(const TfDecodeDesc* desc, TfDecodePlan* plan) {
+  if (plan == nullptr) return fail(TF_ERR_BAD_ARG, "plan is null");
+  if (int rc = check_decode_desc(desc)) return rc;
+  tfb::plan_decode(*desc, sm_count(), plan);
+  return TF_OK;
+}
+
+int tf_decode_split(const void* q, const void* k, const void* v, void* workspace, uint64_t workspace_bytes,
+                    const TfDecodeDesc* desc, void* stream) {
+  TfDecodePlan plan;
+  if (int rc = plan_and_check_decode(q, k, v, workspace, workspace_bytes, desc, &plan)) return rc;
+  const int64_t rows = (int64_t)desc->batch * desc->heads * plan.num_splits;
+  float* part_o = static_cast<float*>(workspace);
+  float* part_ml = part_o + rows * desc->head_dim;
+  return dispatch_split(q, k, v, part_o, part_ml, desc, plan, static_cast<cudaStream_t>(stream));
+}
+
+int tf_decode_combine(const float* part_o, const float* part_ml, int32_t n_parts, int64_t part_stride_o,
+                      int64_t row_stride_o, int64_t part_stride_ml, int64_t row_stride_ml, int32_t rows,
+                      int32_t heads, int32_t head_dim, int32_t dtype, void* o, int64_t o_stride_b,
+                      int64_t o_stride_h, float* lse, float* out_part_o, float* out_part_ml, void* stream) {
+  if (part_o == nullptr || part_ml == nullptr) return fail(TF_ERR_BAD_ARG, "partials are null");
+  if (n_parts < 1 || rows < 1 || heads < 1) return fail(TF_ERR_BAD_ARG, "n_parts, rows and heads must be positive");
+  if (dtype != TF_F16 && dtype != TF_BF16) return fail(TF_ERR_UNSUPPORTED, "dtype code %d is not fp16 or bf16", dtype);
+  const bool merged = out_part_o != nullptr;
+  if (merged && out_part_ml == nullptr) return fail(TF_ERR_BAD_ARG, "out_part_ml is null");
+  if (!merged && o == nullptr) return fail(TF_ERR_BAD_ARG, "neither o nor out_part_o given");
+  tfb::DecodeCombineArgs a;
+  a.part_o = part_o;
+  a.part_ml = part_ml;
+  a.n_parts = n_parts;
+  a.part_stride_o = part_stride_o;
+  a.row_stride_o = row_stride_o;
+  a.part_stride_ml = part_stride_ml;
+  a.row_stride_ml = row_stride_ml;
+  a.heads = heads;
+  a.o = merged ? nullptr : o;
+  a.o_stride_b = o_stride_b;
+  a.o_stride_h = o_stride_h;
+  a.lse = lse;
+  a.out_part_o = out_part_o;
+  a.out_part_ml = out_part_ml;
+  return dispatch_combine(a, rows, head_dim, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int tf_decode(const void* q, const void* k, const void* v, void* o, float* lse, void* workspace,
+              uint64_t workspace_bytes, const TfDecodeDesc* desc, void* stream) {
+  TfDecodePlan plan;
+  if (int rc = plan_and_check_decode(q, k, v, workspace, workspace_bytes, desc, &plan)) return rc;
+  if (o == nullptr) return fail(TF_ERR_BAD_ARG, "o is null");
+  if (desc->len_kv < 1) return fail(TF_ERR_BAD_ARG, "len_kv must be positive for a full decode");
+  const int rows = desc->batch * desc->heads;
+  const int D = desc->head_dim;
+  float* part_o = static_cast<float*>(workspace);
+  float* part_ml = part_o + (int64_t)rows * plan.num_splits * D;
+  if (int rc = dispatch_split(q, k, v, part_o, part_ml, desc, plan, static_cast<cudaStream_t>(stream))) return rc;
+  return tf_decode_combine(part_o, part_ml, plan.num_splits, D, (int64_t)plan.num_splits * D, 2,
+                           (int64_t)plan.num_splits * 2, rows, desc->heads, D, desc->dtype, o,
+                           desc->o_stride_b, desc->o_stride_h, lse, nullptr, nullptr, stream);
+}
+
+int tf_decode_partial(const void* q, const void* k, const void* v, float* slot, void* workspace,
+                      uint64_t workspace_bytes, const TfDecodeDesc* desc, void* stream) {
+  TfDecodePlan plan;
+  if (int rc = plan_and_check_decode(q, k, v, workspace, workspace_bytes, desc, &plan)) return rc;
+  if (slot == nullptr) return fail(TF_ERR_BAD_ARG, "slot is null");
+  const int rows = desc->batch * desc->heads;
+  const int D = desc->head_dim;
+  float* part_o = static_cast<float*>(workspace);
+  float* part_ml = part_o + (int64_t)rows * plan.num_splits * D;
+  if (int rc = dispatch_split(q, k, v, part_o, part_ml, desc, plan, static_cast<cudaStream_t>(stream))) return rc;
+  return tf_decode_combine(part_o, part_ml, plan.num_splits, D, (int64_t)plan.num_splits * D, 2,
+                           (int64_t)plan.num_splits * 2, rows, desc->heads, D, desc->dtype, nullptr, 0, 0,
+                           nullptr, slot, slot + (int64_t)rows * D, stream);
+}
+
+int tf_decode_gathered(const float* slots, int32_t n_ranks, int32_t batch, int32_t heads, int32_t head_dim,
+                       int32_t dtype, void* o, int64_t o_stride_b, int64_t o_stride_h, float* lse,
+                       void* stream) {
+  if (slots == nullptr || o == nullptr) return fail(TF_ERR_BAD_ARG, "slots and o must be non-null");
+  if (n_ranks < 1 || batch < 1 || heads < 1) return fail(TF_ERR_BAD_ARG, "n_ranks, batch and heads must be positive");
+  const int64_t rows = (int64_t)batch * heads;
+  const int64_t slot_floats = rows * (head_dim + 2);
+  return tf_decode_combine(slots, slots + rows * head_dim, n_ranks, slot_floats, head_dim, slot_floats, 2,
+                           (int32_t)rows, heads, head_dim, dtype, o, o_stride_b, o_stride_h, lse, nullptr,
+                           nullptr, stream);
+}
+
+const char* tf_last_error(void) { return g_err; }
+
+int tf_device_status(int32_t* code_out) {
+  int code = 0;
+  TF_CUDA_TRY(cudaDeviceSynchronize());
+  TF_CUDA_TRY(cudaMemcpyFromSymbol(&code, tfb::g_status_word, sizeof(int)));
+  if (code != 0) {
+    const int zero = 0;
+    TF_CUDA_TRY(cudaMemcpyToSymbol(tfb::g_status_word, &zero, sizeof(int)));
+  }
+  if (code_out != nullptr) *code_out = code;
+  if (code != 0) return fail(TF_ERR_DEVICE_TIMEOUT, "a device-side wait gave up (site code %d)", code);
+  return TF_OK;
+}
+
+int tf_abi_version(void) { return 1; }
+
+}  // extern "C"

@@ -1,0 +1,443 @@
+// Flash decoding for sm_100a: one query row per (batch, head) against a long
+// KV sequence, as split-KV partials followed by a log-sum-exp combine.
+// TileFusion has no decode operator; these kernels extend its attention path
+// (include/kernels/flash_attention_device.cuh:130-312 walks the whole KV
+// length in one CTA) with the split the long-KV case needs.
+//
+// decode_split_kernel is bound by HBM bandwidth (about one flop per byte), so
+// it is organised around the K/V byte stream:
+//   * a persistent grid, two CTAs per SM; each work item is one (b, h, split)
+//     and covers one or more kv_chunk-sized chunks of that head;
+//   * one producer thread streams K then V of each chunk through a ring of
+//     32-KB shared-memory stages with 1-D bulk TMA copies (evict-first in L2)
+//     that complete on "full" mbarriers; eight consumer warps release stages
+//     through "empty" mbarriers, so ~192 KB per SM stay in flight;
+//   * consumers keep q (pre-multiplied by scale*log2 e) in registers; a group
+//     of D/8 lanes reads one 16-byte-vectorised key row, partial dot products
+//     are reduced with a transposing shuffle butterfly (one shuffle per key);
+//   * softmax is per chunk with a running (m, l) across the chunks of a split;
+//     P.V accumulates 8 output dims per lane in fp32 and is reduced across the
+//     key groups once per work item.
+// Each item writes D fp32 of un-normalised output plus (m, l), m in log2 units.
+//
+// decode_combine_kernel merges n partial rows per (b, h): it either writes the
+// final O (16-bit) and LSE (natural log), or one merged partial row (used when
+// the KV sequence is sharded across GPUs and the merge continues after an
+// all-gather).
+#pragma once
+
+#include <type_traits>
+
+#include "sm100_ptx.cuh"
+
+namespace tfb {
+
+constexpr int kDecKeysPerStage = 128;
+constexpr int kDecConsumerThreads = 256;
+constexpr int kDecThreads = kDecConsumerThreads + 32;
+constexpr int kDecMaxChunk = 1024;        // keys; bounds the score buffers
+
+struct DecodeSplitArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  float* part_o;      // [items][D]
+  float* part_ml;     // [items][2]
+  int heads;
+  int len_kv;
+  int kv_chunk;
+  int num_splits;
+  int chunks_per_split;
+  int items;          // B*H*num_splits
+  float scale_log2;
+  long long q_stride_b, q_stride_h;
+  long long k_stride_b, k_stride_h;
+  long long v_stride_b, v_stride_h;
+};
+
+template <int D, int kStages>
+struct DecodeSmem {
+  static constexpr int kStageBytes = kDecKeysPerStage * D * 2;
+  static constexpr int kOffStages = 0;
+  static constexpr int kOffScores = kStages * kStageBytes;              // 2 x kDecMaxChunk fp32
+  static constexpr int kOffRed = kOffScores + 2 * kDecMaxChunk * 4;     // [groups][D] fp32
+  static constexpr int kGroups = kDecConsumerThreads / (D / 8);
+  static constexpr int kOffWarp = kOffRed + kGroups * D * 4;            // 16 fp32 scratch
+  static constexpr int kOffBar = kOffWarp + 64;                         // 2*kStages mbarriers
+  static constexpr int kOffAbort = kOffBar + 2 * kStages * 8;
+  static constexpr int kBytes = kOffAbort + 16 + 128;                   // + alignment slack
+};
+
+enum DecodeWaitCode { kWaitDecEmpty = 201, kWaitDecFullK = 202, kWaitDecFullV = 203 };
+
+__device__ __forceinline__ void consumer_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerThreads) : "memory");
+}
+
+template <typename T, int D, int kStages>
+__global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const DecodeSplitArgs args) {
+  using S = DecodeSmem<D, kStages>;
+  constexpr int kLpr = D / 8;                          // lanes per key row (16 B each)
+  constexpr int kGroups = kDecConsumerThreads / kLpr;  // key rows read per step
+  constexpr int kKpt = kDecKeysPerStage / kGroups;     // keys per thread per stage
+  static_assert(kKpt == 8 || kKpt == 4, "unexpected keys per thread");
+  static_assert(kLpr >= kKpt, "butterfly needs at least kKpt lanes per row");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 127u) & ~127u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  float* scores = reinterpret_cast<float*>(smem_gen + S::kOffScores);
+  float* red = reinterpret_cast<float*>(smem_gen + S::kOffRed);
+  float* warp_scratch = reinterpret_cast<float*>(smem_gen + S::kOffWarp);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
+  const uint32_t bar_full = smem_base + S::kOffBar;
+  const uint32_t bar_empty = smem_base + S::kOffBar + kStages * 8;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + s * 8, 1);
+      mbar_init(bar_empty + s * 8, kDecConsumerThreads / 32);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const int chunk = args.kv_chunk;
+  const int keys_per_split = chunk * args.chunks_per_split;
+
+  if (warp == kDecConsumerThreads / 32) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      const uint64_t policy = l2_policy_evict_first();
+      uint32_t stage = 0, phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < args.items; item += gridDim.x) {
+        const int bh = item / args.num_splits;
+        const int split = item - bh * args.num_splits;
+        const int b = bh / args.heads, h = bh - b * args.heads;
+        const T* kbase = reinterpret_cast<const T*>(args.k) + b * args.k_stride_b + h * args.k_stride_h;
+        const T* vbase = reinterpret_cast<const T*>(args.v) + b * args.v_stride_b + h * args.v_stride_h;
+        const int key_begin = split * keys_per_split;
+        const int key_end = min(args.len_kv, key_begin + keys_per_split);
+        for (int c0 = key_begin; ok && c0 < key_end; c0 += chunk) {
+          const int c1 = min(key_end, c0 + chunk);
+          for (int pass = 0; ok && pass < 2; ++pass) {
+            const T* base = pass == 0 ? kbase : vbase;
+            for (int s0 = c0; s0 < c1; s0 += kDecKeysPerStage) {
+              const int n = min(kDecKeysPerStage, c1 - s0);
+              if (issued >= kStages) {
+                ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, kWaitDecEmpty);
+                if (!ok) break;
+              }
+              const uint32_t bytes = uint32_t(n) * D * 2;
+              mbar_arrive_expect_tx(bar_full + stage * 8, bytes);
+              tma_load_1d(smem_base + S::kOffStages + stage * S::kStageBytes,
+                          base + (long long)s0 * D, bytes, bar_full + stage * 8, policy);
+              ++issued;
+              if (++stage == kStages) {
+                stage = 0;
+                phase ^= 1;
+              }
+            }
+          }
+        }
+      }
+      // The consumers observe every copy through the full barriers before they
+      // leave, so nothing is in flight at exit unless a wait gave up; in that
+      // case let the outstanding copies land (bounded) before retiring.
+      if (!ok) {
+        const unsigned long long t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else {
+    // ----------------------------------------------------------- consumers --
+    const int g = tid % kLpr;        // which 8 head dims this lane owns
+    const int r = tid / kLpr;        // key group
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+
+    // Index (within the kKpt keys this thread touches per stage) of the key
+    // whose complete dot product the butterfly leaves in this lane.
+    int own = 0;
+    {
+      int n = kKpt, bit = kLpr >> 1;
+      while (n > 1) {
+        n >>= 1;
+        if (g & bit) own += n;
+        bit >>= 1;
+      }
+    }
+    // Lanes whose remaining low bits are zero publish the score.
+    constexpr int kLowBits = kLpr / kKpt;   // lanes holding the same key after halving
+    const bool publishes = (g % kLowBits) == 0;
+
+    for (int item = blockIdx.x; ok && item < args.items; item += gridDim.x) {
+      const int bh = item / args.num_splits;
+      const int split = item - bh * args.num_splits;
+      const int b = bh / args.heads, h = bh - b * args.heads;
+      const int key_begin = split * keys_per_split;
+      const int key_end = min(args.len_kv, key_begin + keys_per_split);
+
+      // q * scale * log2(e) for this lane's 8 dims
+      float qf[8];
+      {
+        const T* qp = reinterpret_cast<const T*>(args.q) + b * args.q_stride_b + h * args.q_stride_h + g * 8;
+        const uint4 qv = *reinterpret_cast<const uint4*>(qp);
+        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = unpack2<T>(qw[i]);
+          qf[2 * i] = f.x * args.scale_log2;
+          qf[2 * i + 1] = f.y * args.scale_log2;
+        }
+      }
+
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      float m_run = -INFINITY;
+      float l_thread = 0.f;      // this thread's share of sum(p); reduced at the end
+      int chunk_idx = 0;
+
+      for (int c0 = key_begin; ok && c0 < key_end; c0 += chunk, ++chunk_idx) {
+        const int c1 = min(key_end, c0 + chunk);
+        const int n_chunk = c1 - c0;
+        float* sc = scores + (chunk_idx & 1) * kDecMaxChunk;
+
+        // ---- scores of this chunk ----
+        for (int s0 = 0; s0 < n_chunk; s0 += kDecKeysPerStage) {
+          const int n = min(kDecKeysPerStage, n_chunk - s0);
+          ok = __all_sync(0xffffffffu,
+                          mbar_wait(bar_full + stage * 8, phase, abort_flag, kWaitDecFullK));
+          if (!ok) break;
+          const uint8_t* st = smem_gen + S::kOffStages + stage * S::kStageBytes;
+          float part[kKpt];
+#pragma unroll
+          for (int i = 0; i < kKpt; ++i) {
+            const int key = i * kGroups + r;
+            float d = 0.f;
+            if (key < n) {
+              const uint4 kv = *reinterpret_cast<const uint4*>(st + key * (D * 2) + g * 16);
+              const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = unpack2<T>(kw[e]);
+                d = fmaf(f.x, qf[2 * e], d);
+                d = fmaf(f.y, qf[2 * e + 1], d);
+              }
+            }
+            part[i] = d;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_empty + stage * 8);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+          // Transposing butterfly over the kLpr lanes of a row: each step
+          // halves the values held and doubles the lanes summed.
+          {
+            int n_live = kKpt;
+#pragma unroll
+            for (int bit = kLpr >> 1; bit >= 1; bit >>= 1) {
+              if (n_live > 1) {
+                const int half = n_live >> 1;
+                const bool upper = (g & bit) != 0;
+#pragma unroll
+                for (int i = 0; i < kKpt / 2; ++i) {
+                  if (i < half) {
+                    const float send = upper ? part[i] : part[i + half];
+                    const float keep = upper ? part[i + half] : part[i];
+                    part[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+                  }
+                }
+                n_live = half;
+              } else {
+                part[0] += __shfl_xor_sync(0xffffffffu, part[0], bit);
+              }
+            }
+          }
+          if (publishes) {
+            const int key = own * kGroups + r;
+            sc[s0 + key] = key < n ? part[0] : -INFINITY;
+          }
+        }
+        if (!ok) break;
+        consumer_sync();
+
+        // ---- chunk maximum, probabilities ----
+        float m_loc = -INFINITY;
+        for (int i = tid; i < n_chunk; i += kDecConsumerThreads) m_loc = fmaxf(m_loc, sc[i]);
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1)
+          m_loc = fmaxf(m_loc, __shfl_xor_sync(0xffffffffu, m_loc, off));
+        float* wmax = warp_scratch + (chunk_idx & 1) * 8;
+        if (lane == 0) wmax[warp] = m_loc;
+        consumer_sync();
+        float m_chunk = wmax[0];
+#pragma unroll
+        for (int w = 1; w < kDecConsumerThreads / 32; ++w) m_chunk = fmaxf(m_chunk, wmax[w]);
+        const float m_new = fmaxf(m_run, m_chunk);
+        const float alpha = fast_exp2(m_run - m_new);   // 0 on the first chunk
+        m_run = m_new;
+        l_thread *= alpha;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= alpha;
+        for (int i = tid; i < n_chunk; i += kDecConsumerThreads) {
+          const float p = fast_exp2(sc[i] - m_new);
+          sc[i] = p;
+          l_thread += p;
+        }
+        consumer_sync();
+
+        // ---- O += P V ----
+        for (int s0 = 0; s0 < n_chunk; s0 += kDecKeysPerStage) {
+          const int n = min(kDecKeysPerStage, n_chunk - s0);
+          ok = __all_sync(0xffffffffu,
+                          mbar_wait(bar_full + stage * 8, phase, abort_flag, kWaitDecFullV));
+          if (!ok) break;
+          const uint8_t* st = smem_gen + S::kOffStages + stage * S::kStageBytes;
+#pragma unroll
+          for (int i = 0; i < kKpt; ++i) {
+            const int key = i * kGroups + r;
+            if (key < n) {
+              const float p = sc[s0 + key];
+              const uint4 vv = *reinterpret_cast<const uint4*>(st + key * (D * 2) + g * 16);
+              const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = unpack2<T>(vw[e]);
+                acc[2 * e] = fmaf(p, f.x, acc[2 * e]);
+                acc[2 * e + 1] = fmaf(p, f.y, acc[2 * e + 1]);
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_empty + stage * 8);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) break;
+
+      // ---- reduce the key groups, write the partial row ----
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1)
+        l_thread += __shfl_xor_sync(0xffffffffu, l_thread, off);
+      consumer_sync();   // previous item's readers of red / warp_scratch are done
+      if (lane == 0) warp_scratch[warp] = l_thread;
+      {
+        float4* dst = reinterpret_cast<float4*>(red + r * D + g * 8);
+        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      }
+      consumer_sync();
+      if (tid < D) {
+        float o = 0.f;
+#pragma unroll 8
+        for (int grp = 0; grp < kGroups; ++grp) o += red[grp * D + tid];
+        args.part_o[(long long)item * D + tid] = o;
+      } else if (tid == D) {
+        float l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDecConsumerThreads / 32; ++w) l += warp_scratch[w];
+        args.part_ml[(long long)item * 2 + 0] = m_run;
+        args.part_ml[(long long)item * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ combine --
+struct DecodeCombineArgs {
+  const float* part_o;
+  const float* part_ml;
+  int n_parts;
+  long long part_stride_o, row_stride_o;
+  long long part_stride_ml, row_stride_ml;
+  int heads;
+  void* o;                 // final output (16-bit) or null
+  long long o_stride_b, o_stride_h;
+  float* lse;              // [rows] or null
+  float* out_part_o;       // merged partial [rows][D] or null
+  float* out_part_ml;      // merged partial [rows][2]
+};
+
+constexpr int kCombineGroups = 4;
+
+// grid = rows, block = (D, kCombineGroups).  Thread (d, j) walks parts j,
+// j + kCombineGroups, ... of output dim d.
+template <typename T, int D>
+__global__ void __launch_bounds__(D * kCombineGroups) decode_combine_kernel(const DecodeCombineArgs a) {
+  __shared__ float s_red[kCombineGroups][D];
+  __shared__ float s_m[kCombineGroups * D / 32];
+  __shared__ float s_l[kCombineGroups];
+  const int row = blockIdx.x;
+  const int d = threadIdx.x;
+  const int j = threadIdx.y;
+  const int tid = j * D + d;
+  const int n_threads = D * kCombineGroups;
+  const float* ml = a.part_ml + (long long)row * a.row_stride_ml;
+  const float* po = a.part_o + (long long)row * a.row_stride_o;
+
+  // pass 1: global maximum
+  float m = -INFINITY;
+  for (int p = tid; p < a.n_parts; p += n_threads) m = fmaxf(m, ml[(long long)p * a.part_stride_ml]);
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if ((tid & 31) == 0) s_m[tid >> 5] = m;
+  __syncthreads();
+  m = s_m[0];
+#pragma unroll
+  for (int w = 1; w < kCombineGroups * D / 32; ++w) m = fmaxf(m, s_m[w]);
+
+  // pass 2: weighted sums
+  float acc = 0.f, l = 0.f;
+  for (int p = j; p < a.n_parts; p += kCombineGroups) {
+    const float mp = ml[(long long)p * a.part_stride_ml];
+    const float lp = ml[(long long)p * a.part_stride_ml + 1];
+    const float w = (mp == -INFINITY) ? 0.f : fast_exp2(mp - m);
+    l = fmaf(lp, w, l);
+    acc = fmaf(po[(long long)p * a.part_stride_o + d], w, acc);
+  }
+  s_red[j][d] = acc;
+  if (d == 0) s_l[j] = l;
+  __syncthreads();
+  if (j == 0) {
+    float o = 0.f, lt = 0.f;
+#pragma unroll
+    for (int q = 0; q < kCombineGroups; ++q) {
+      o += s_red[q][d];
+      lt += s_l[q];
+    }
+    if (a.out_part_o != nullptr) {
+      a.out_part_o[(long long)row * D + d] = o;
+      if (d == 0) {
+        a.out_part_ml[(long long)row * 2 + 0] = m;
+        a.out_part_ml[(long long)row * 2 + 1] = lt;
+      }
+    } else {
+      const int b = row / a.heads, h = row - b * a.heads;
+      T* op = reinterpret_cast<T*>(a.o) + b * a.o_stride_b + h * a.o_stride_h;
+      const float val = o / lt;
+      if constexpr (std::is_same<T, __half>::value) {
+        op[d] = __float2half_rn(val);
+      } else {
+        op[d] = __float2bfloat16_rn(val);
+      }
+      if (d == 0 && a.lse != nullptr) a.lse[row] = 0.6931471805599453f * (m + log2f(lt));
+    }
+  }
+}
+
+}  // namespace tfb

@@ -1,0 +1,86 @@
+#include "registry.h"
+
+#include <algorithm>
+#include <cstdint>
+
+namespace tfb {
+
+namespace {
+constexpr AttnVariant kAttnVariants[] = {
+    {TF_F16, 128, 128, 128, 2}, {TF_BF16, 128, 128, 128, 2},
+    {TF_F16, 64, 128, 128, 2},  {TF_BF16, 64, 128, 128, 2},
+    {0, 0, 0, 0, 0},
+};
+constexpr int kDecodeCtasPerSm = 2;
+constexpr int kDecodeStages = 3;
+}  // namespace
+
+const AttnVariant* attn_variants() { return kAttnVariants; }
+
+void plan_attn(const TfAttnDesc& d, int sm_count, TfAttnPlan* plan) {
+  (void)sm_count;
+  const AttnVariant* best = nullptr;
+  for (const AttnVariant* v = kAttnVariants; v->head_dim != 0; ++v) {
+    if (v->dtype != d.dtype || v->head_dim != d.head_dim) continue;
+    // A caller's tile hint wins when it names a compiled variant.
+    if (best == nullptr) best = v;
+    if (d.tile_q == v->tile_q && d.tile_kv == v->tile_kv) {
+      best = v;
+      break;
+    }
+  }
+  plan->tile_q = best->tile_q;
+  plan->tile_kv = best->tile_kv;
+  plan->ctas_per_sm = best->ctas_per_sm;
+  const int64_t q_tiles = (d.len_q + best->tile_q - 1) / best->tile_q;
+  plan->grid = (int32_t)std::min<int64_t>(q_tiles * d.heads * d.batch, INT32_MAX);
+  // With both strides 1 (a single key or a single head dim) either reading
+  // is valid; the row-contiguous one is kept.
+  plan->k_mn_major = d.k_stride_d == 1 ? 0 : 1;
+  plan->v_mn_major = d.v_stride_d == 1 ? 1 : 0;
+  plan->smem_bytes = 0;
+}
+
+void plan_decode(const TfDecodeDesc& d, int sm_count, TfDecodePlan* plan) {
+  const int chunk = d.kv_chunk == 0 ? 512 : d.kv_chunk;
+  const int64_t bh = (int64_t)d.batch * d.heads;
+  const int n_chunks = std::max(1, (d.len_kv + chunk - 1) / chunk);
+  const int grid = std::max(1, sm_count) * kDecodeCtasPerSm;
+
+  int cps = 1;
+  if (d.num_splits > 0) {
+    const int want = std::min(d.num_splits, n_chunks);
+    cps = (n_chunks + want - 1) / want;
+  } else {
+    // Items are dealt round-robin to a persistent grid, so the step takes
+    // ceil(items / grid) * chunks_per_split chunk-times.  Take the coarsest
+    // split (fewest partial rows to combine) whose makespan is within 0.5 % of
+    // the best one.
+    int64_t best_span = INT64_MAX;
+    for (int c = 1; c <= n_chunks; ++c) {
+      const int64_t splits = (n_chunks + c - 1) / c;
+      const int64_t items = bh * splits;
+      const int64_t span = ((items + grid - 1) / grid) * c;
+      best_span = std::min(best_span, span);
+    }
+    for (int c = n_chunks; c >= 1; --c) {
+      const int64_t splits = (n_chunks + c - 1) / c;
+      const int64_t items = bh * splits;
+      const int64_t span = ((items + grid - 1) / grid) * c;
+      if (span * 1000 <= best_span * 1005) {
+        cps = c;
+        break;
+      }
+    }
+  }
+  const int splits = (n_chunks + cps - 1) / cps;
+  plan->num_splits = splits;
+  plan->chunks_per_split = cps;
+  plan->kv_chunk = chunk;
+  plan->grid = (int32_t)std::min<int64_t>(grid, bh * splits);
+  plan->stages = kDecodeStages;
+  plan->reserved = 0;
+  plan->workspace_bytes = (uint64_t)bh * splits * (d.head_dim + 2) * sizeof(float);
+}
+
+}  // namespace tfb

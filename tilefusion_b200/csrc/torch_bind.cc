@@ -1,0 +1,272 @@
+// Operator layer: registers the attention operators with the torch dispatcher
+// under the `tilefusion` namespace and forwards each to the C-ABI of
+// libtilefusion_b200.so.  torch types stop here.
+//
+// `flash_attention` keeps the schema of TileFusion's operator verbatim
+// (include/kernels/kernel_list.hpp:25-30; registered there through
+// REGISTER_OP / KernelRegistry, include/kernel_registry.hpp:22-88, and
+// src/torch_bind.cc:8-14).  The decode operators are additions registered the
+// same way.  Differences from the reference's host operator
+// (src/kernels/flash_attn.cu:58-152): leading (batch, head) dimensions and
+// bf16 are accepted, operands may be strided views (no .contiguous() copy is
+// needed), the launch goes to torch's current stream, and there is no device
+// synchronisation.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <vector>
+
+#include "tilefusion_b200.h"
+
+namespace tilefusion_b200 {
+namespace {
+
+struct OpEntry {
+  const char* name;
+  const char* schema;
+  void (*bind)(torch::Library&, const char*);
+};
+
+std::vector<OpEntry>& op_table() {
+  static std::vector<OpEntry> table;
+  return table;
+}
+
+// Adds an operator to the table at static-initialisation time; the
+// TORCH_LIBRARY blocks below walk the table.
+#define TF_REGISTER_OP(opname, schema_str, fn)                                         \
+  static const bool opname##_added = [] {                                              \
+    op_table().push_back({#opname, schema_str, [](torch::Library& m, const char* n) {  \
+                            m.impl(n, c10::DispatchKey::CUDA, fn);                    \
+                          }});                                                         \
+    return true;                                                                       \
+  }()
+
+int dtype_code(const at::Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == at::kHalf || t.scalar_type() == at::kBFloat16,
+              "the inputs and output must be half-precision (fp16 or bf16).");
+  return t.scalar_type() == at::kHalf ? TF_F16 : TF_BF16;
+}
+
+void check_status(int rc) { TORCH_CHECK(rc == TF_OK, "tilefusion_b200: ", tf_last_error()); }
+
+// Splits leading dims of a [..., rows, cols] tensor into (batch, heads) with
+// element strides; 2-D tensors are one (batch, head).
+struct Lead {
+  int64_t batch = 1, heads = 1, stride_b = 0, stride_h = 0;
+};
+
+Lead lead_dims(const at::Tensor& t, const char* name) {
+  Lead l;
+  const int64_t nd = t.dim();
+  TORCH_CHECK(nd >= 2 && nd <= 4, name, " must have 2, 3 or 4 dimensions, got ", nd);
+  if (nd == 3) {
+    l.heads = t.size(0);
+    l.stride_h = t.stride(0);
+  } else if (nd == 4) {
+    l.batch = t.size(0);
+    l.heads = t.size(1);
+    l.stride_b = t.stride(0);
+    l.stride_h = t.stride(1);
+  }
+  return l;
+}
+
+void attention_impl(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, at::Tensor& O,
+                    at::Tensor* LSE, int64_t tile_q, int64_t tile_kv, double softmax_scale, bool causal) {
+  TORCH_CHECK(Q.is_cuda() && K.is_cuda() && V.is_cuda() && O.is_cuda(), "Q, K, V and O must be CUDA tensors");
+  TORCH_CHECK(Q.scalar_type() == K.scalar_type() && Q.scalar_type() == V.scalar_type() &&
+                  Q.scalar_type() == O.scalar_type(),
+              "Q, K, V and O must share one dtype");
+  TORCH_CHECK(Q.dim() == K.dim() && Q.dim() == V.dim() && Q.dim() == O.dim(),
+              "Q, K, V and O must have the same number of dimensions");
+  TfAttnDesc d{};
+  d.dtype = dtype_code(Q);
+  const Lead lq = lead_dims(Q, "Q"), lk = lead_dims(K, "K"), lv = lead_dims(V, "V"), lo = lead_dims(O, "O");
+  TORCH_CHECK(lq.batch == lk.batch && lq.batch == lv.batch && lq.batch == lo.batch && lq.heads == lk.heads &&
+                  lq.heads == lv.heads && lq.heads == lo.heads,
+              "leading (batch, head) dimensions of Q, K, V and O must match");
+  d.batch = (int32_t)lq.batch;
+  d.heads = (int32_t)lq.heads;
+  d.len_q = (int32_t)Q.size(-2);
+  d.head_dim = (int32_t)Q.size(-1);
+  d.len_kv = (int32_t)K.size(-2);
+  d.head_dim_v = (int32_t)O.size(-1);
+  TORCH_CHECK(K.size(-1) == d.head_dim, "K must be [..., Lk, D] with D = Q.size(-1)");
+  TORCH_CHECK(O.size(-2) == d.len_q, "O must be [..., Lq, Dv]");
+  TORCH_CHECK(Q.stride(-1) == 1 && O.stride(-1) == 1, "Q and O rows must be contiguous");
+  d.q_stride_b = lq.stride_b;
+  d.q_stride_h = lq.stride_h;
+  d.q_stride_l = Q.stride(-2);
+  d.k_stride_b = lk.stride_b;
+  d.k_stride_h = lk.stride_h;
+  d.k_stride_l = K.stride(-2);
+  d.k_stride_d = K.stride(-1);
+  d.v_stride_b = lv.stride_b;
+  d.v_stride_h = lv.stride_h;
+  // The reference operand is V^T [..., Dv, Lk]; the natural [..., Lk, Dv] form
+  // is accepted when the shape is unambiguous.
+  if (V.size(-2) == d.head_dim_v && V.size(-1) == d.len_kv) {
+    d.v_stride_d = V.stride(-2);
+    d.v_stride_l = V.stride(-1);
+  } else {
+    TORCH_CHECK(V.size(-2) == d.len_kv && V.size(-1) == d.head_dim_v,
+                "V must be [..., Dv, Lk] (or [..., Lk, Dv]) with Lk = K.size(-2), Dv = O.size(-1)");
+    d.v_stride_l = V.stride(-2);
+    d.v_stride_d = V.stride(-1);
+  }
+  d.o_stride_b = lo.stride_b;
+  d.o_stride_h = lo.stride_h;
+  d.o_stride_l = O.stride(-2);
+  d.softmax_scale = (float)softmax_scale;
+  d.causal = causal ? 1 : 0;
+  d.tile_q = (int32_t)tile_q;
+  d.tile_kv = (int32_t)tile_kv;
+  float* lse_ptr = nullptr;
+  if (LSE != nullptr) {
+    TORCH_CHECK(LSE->is_cuda() && LSE->scalar_type() == at::kFloat && LSE->is_contiguous() &&
+                    LSE->numel() == (int64_t)d.batch * d.heads * d.len_q,
+                "LSE must be a contiguous fp32 CUDA tensor with batch*heads*Lq elements");
+    lse_ptr = LSE->data_ptr<float>();
+  }
+  const c10::cuda::CUDAGuard guard(Q.device());
+  check_status(tf_attn_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse_ptr, &d,
+                           at::cuda::getCurrentCUDAStream().stream()));
+}
+
+void flash_attention(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, at::Tensor& O,
+                     int64_t tile_length_q, int64_t tile_length_kv, int64_t tile_hidden_qk,
+                     int64_t tile_hidden_v, double softmax_scale, bool causal) {
+  (void)tile_hidden_qk;  // the head dimensions are never tiled on this path
+  (void)tile_hidden_v;
+  attention_impl(Q, K, V, O, nullptr, tile_length_q, tile_length_kv, softmax_scale, causal);
+}
+
+void flash_attention_lse(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, at::Tensor& O,
+                         at::Tensor& LSE, int64_t tile_length_q, int64_t tile_length_kv, double softmax_scale,
+                         bool causal) {
+  attention_impl(Q, K, V, O, &LSE, tile_length_q, tile_length_kv, softmax_scale, causal);
+}
+
+TfDecodeDesc decode_desc(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, int64_t kv_chunk,
+                         int64_t num_splits, double softmax_scale) {
+  TORCH_CHECK(Q.is_cuda() && K.is_cuda() && V.is_cuda(), "Q, K and V must be CUDA tensors");
+  TORCH_CHECK(Q.dim() == 4 && K.dim() == 4 && V.dim() == 4,
+              "Q must be [B, H, 1, D] and K, V must be [B, H, Lk, D]");
+  TORCH_CHECK(Q.size(2) == 1, "flash_decoding takes one query row per (batch, head)");
+  TORCH_CHECK(K.sizes() == V.sizes() && K.size(0) == Q.size(0) && K.size(1) == Q.size(1) &&
+                  K.size(3) == Q.size(3),
+              "K and V must be [B, H, Lk, D] matching Q");
+  TORCH_CHECK(Q.scalar_type() == K.scalar_type() && Q.scalar_type() == V.scalar_type(),
+              "Q, K and V must share one dtype");
+  TORCH_CHECK(Q.stride(3) == 1 && K.stride(3) == 1 && V.stride(3) == 1 &&
+                  (K.size(2) <= 1 || (K.stride(2) == K.size(3) && V.stride(2) == V.size(3))),
+              "rows of Q, K and V must be contiguous and consecutive keys D elements apart");
+  TfDecodeDesc d{};
+  d.dtype = dtype_code(Q);
+  d.batch = (int32_t)Q.size(0);
+  d.heads = (int32_t)Q.size(1);
+  d.len_kv = (int32_t)K.size(2);
+  d.head_dim = (int32_t)Q.size(3);
+  d.kv_chunk = (int32_t)kv_chunk;
+  d.num_splits = (int32_t)num_splits;
+  d.softmax_scale = (float)softmax_scale;
+  d.q_stride_b = Q.stride(0);
+  d.q_stride_h = Q.stride(1);
+  d.k_stride_b = K.stride(0);
+  d.k_stride_h = K.stride(1);
+  d.v_stride_b = V.stride(0);
+  d.v_stride_h = V.stride(1);
+  return d;
+}
+
+at::Tensor decode_workspace(const TfDecodeDesc& d, const at::Tensor& like) {
+  TfDecodePlan plan;
+  check_status(tf_decode_plan(&d, &plan));
+  return at::empty({(int64_t)((plan.workspace_bytes + 3) / 4)}, like.options().dtype(at::kFloat));
+}
+
+void flash_decoding(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, at::Tensor& O,
+                    at::Tensor& LSE, int64_t kv_chunk, int64_t num_splits, double softmax_scale) {
+  TfDecodeDesc d = decode_desc(Q, K, V, kv_chunk, num_splits, softmax_scale);
+  TORCH_CHECK(O.is_cuda() && O.scalar_type() == Q.scalar_type() && O.dim() == 4 && O.size(0) == Q.size(0) &&
+                  O.size(1) == Q.size(1) && O.size(2) == 1 && O.size(3) == Q.size(3) && O.stride(3) == 1,
+              "O must be [B, H, 1, D] with contiguous rows and Q's dtype");
+  TORCH_CHECK(LSE.is_cuda() && LSE.scalar_type() == at::kFloat && LSE.is_contiguous() &&
+                  LSE.numel() == Q.size(0) * Q.size(1),
+              "LSE must be a contiguous fp32 CUDA tensor with B*H elements");
+  d.o_stride_b = O.stride(0);
+  d.o_stride_h = O.stride(1);
+  const c10::cuda::CUDAGuard guard(Q.device());
+  at::Tensor ws = decode_workspace(d, Q);
+  check_status(tf_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), LSE.data_ptr<float>(),
+                         ws.data_ptr(), (uint64_t)ws.numel() * 4, &d,
+                         at::cuda::getCurrentCUDAStream().stream()));
+}
+
+void flash_decoding_partial(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, at::Tensor& slot,
+                            int64_t kv_chunk, int64_t num_splits, double softmax_scale) {
+  TfDecodeDesc d = decode_desc(Q, K, V, kv_chunk, num_splits, softmax_scale);
+  TORCH_CHECK(slot.is_cuda() && slot.scalar_type() == at::kFloat && slot.is_contiguous() &&
+                  slot.numel() == Q.size(0) * Q.size(1) * (Q.size(3) + 2),
+              "slot must be a contiguous fp32 CUDA tensor with B*H*(D+2) elements");
+  const c10::cuda::CUDAGuard guard(Q.device());
+  at::Tensor ws = decode_workspace(d, Q);
+  check_status(tf_decode_partial(Q.data_ptr(), K.data_ptr(), V.data_ptr(), slot.data_ptr<float>(),
+                                 ws.data_ptr(), (uint64_t)ws.numel() * 4, &d,
+                                 at::cuda::getCurrentCUDAStream().stream()));
+}
+
+void flash_decoding_gathered(const at::Tensor& slots, at::Tensor& O, at::Tensor& LSE) {
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kFloat && slots.is_contiguous() && slots.dim() == 2,
+              "slots must be a contiguous fp32 CUDA tensor [n_ranks, B*H*(D+2)]");
+  TORCH_CHECK(O.is_cuda() && O.dim() == 4 && O.size(2) == 1 && O.stride(3) == 1, "O must be [B, H, 1, D]");
+  const int64_t B = O.size(0), H = O.size(1), D = O.size(3);
+  TORCH_CHECK(slots.size(1) == B * H * (D + 2), "slots has the wrong row length for O");
+  TORCH_CHECK(LSE.is_cuda() && LSE.scalar_type() == at::kFloat && LSE.is_contiguous() && LSE.numel() == B * H,
+              "LSE must be a contiguous fp32 CUDA tensor with B*H elements");
+  const c10::cuda::CUDAGuard guard(O.device());
+  check_status(tf_decode_gathered(slots.data_ptr<float>(), (int32_t)slots.size(0), (int32_t)B, (int32_t)H,
+                                  (int32_t)D, dtype_code(O), O.data_ptr(), O.stride(0), O.stride(1),
+                                  LSE.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()));
+}
+
+TF_REGISTER_OP(flash_attention,
+               "flash_attention(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, "
+               "int tile_length_q, int tile_length_kv, "
+               "int tile_hidden_qk, int tile_hidden_v, "
+               "float softmax_scale, bool causal) -> ()",
+               &flash_attention);
+
+TF_REGISTER_OP(flash_attention_lse,
+               "flash_attention_lse(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, Tensor(b!) LSE, "
+               "int tile_length_q, int tile_length_kv, float softmax_scale, bool causal) -> ()",
+               &flash_attention_lse);
+
+TF_REGISTER_OP(flash_decoding,
+               "flash_decoding(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, Tensor(b!) LSE, "
+               "int kv_chunk, int num_splits, float softmax_scale) -> ()",
+               &flash_decoding);
+
+TF_REGISTER_OP(flash_decoding_partial,
+               "flash_decoding_partial(Tensor Q, Tensor K, Tensor V, Tensor(a!) slot, "
+               "int kv_chunk, int num_splits, float softmax_scale) -> ()",
+               &flash_decoding_partial);
+
+TF_REGISTER_OP(flash_decoding_gathered,
+               "flash_decoding_gathered(Tensor slots, Tensor(a!) O, Tensor(b!) LSE) -> ()",
+               &flash_decoding_gathered);
+
+}  // namespace
+
+TORCH_LIBRARY(tilefusion, m) {
+  for (const OpEntry& e : op_table()) m.def(e.schema);
+}
+
+TORCH_LIBRARY_IMPL(tilefusion, CUDA, m) {
+  for (const OpEntry& e : op_table()) e.bind(m, e.name);
+}
+
+}  // namespace tilefusion_b200

@@ -1,0 +1,6 @@
+"""Attention operators (mirrors TileFusion's ``python/ops/__init__.py``)."""
+
+from .flash_attention import FlashAttention, flash_attention
+from .flash_decoding import FlashDecoding, flash_decoding
+
+__all__ = ["FlashAttention", "flash_attention", "FlashDecoding", "flash_decoding"]

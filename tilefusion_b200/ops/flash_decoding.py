@@ -1,0 +1,59 @@
+"""Flash decoding operator (split-KV partials + log-sum-exp combine).
+
+TileFusion has no decode operator; this one is added next to
+``flash_attention`` and registered with the dispatcher the same way.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from .._torch_ops import ensure_loaded
+
+__all__ = ["FlashDecoding", "flash_decoding"]
+
+
+class FlashDecoding:
+    """Callable holding the chunk size, split count and scale."""
+
+    def __init__(self, kv_chunk: int = 512, num_splits: int = 0,
+                 softmax_scale: Optional[float] = None) -> None:
+        self.kv_chunk = kv_chunk
+        self.num_splits = num_splits
+        self.softmax_scale = softmax_scale
+
+    def __call__(self, query: torch.Tensor, key: torch.Tensor,
+                 value: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``query [B, H, 1, D]``, ``key``/``value`` ``[B, H, Lk, D]``.
+
+        Returns ``O [B, H, 1, D]`` and ``LSE [B, H, 1]`` (fp32, natural log).
+        """
+        ensure_loaded()
+        scale = self.softmax_scale
+        if scale is None:
+            scale = 1.0 / math.sqrt(query.size(-1))
+        b, h, _, d = query.shape
+        out = torch.empty(b, h, 1, d, dtype=query.dtype, device=query.device)
+        lse = torch.empty(b, h, 1, dtype=torch.float32, device=query.device)
+        torch.ops.tilefusion.flash_decoding(
+            query, key, value, out, lse, self.kv_chunk, self.num_splits, scale
+        )
+        return out, lse
+
+
+def flash_decoding(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                   kv_chunk: int = 512, num_splits: int = 0,
+                   softmax_scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One-query-row attention over a long KV sequence.
+
+    Args:
+        query: ``[B, H, 1, D]``.
+        key, value: ``[B, H, Lk, D]``, rows contiguous.
+        kv_chunk: keys per chunk (multiple of 128, at most 1024).
+        num_splits: partial rows per (batch, head); 0 lets the registry choose.
+        softmax_scale: defaults to ``1/sqrt(D)``.
+    """
+    return FlashDecoding(kv_chunk, num_splits, softmax_scale)(query, key, value)
