@@ -56,6 +56,10 @@ WORKLOADS = {
     "decode_c4": dict(kind="decode", dtype="fp16", B=4, H=32, L=131072, D=128, seed=3, sigma=1.0,
                       scaling="strong"),
 }
+# Smaller cases of the same kernels for `ncu --set full` captures: inputs still
+# exceed the 126 MB L2, but only a few hundred MB are held on the device.
+WORKLOADS["prefill_profile"] = dict(WORKLOADS["prefill_c2"], B=4)
+WORKLOADS["decode_profile"] = dict(WORKLOADS["decode_c3"], B=4)
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)   # earlier measurement on this pool
 
 
@@ -314,6 +318,15 @@ def run_prefill(args, w, name, device, rank, world):
     per_launch_s = secs / args.steps
     local_flops = prefill_flops(b_local, h_local, w["L"], w["L"], w["D"])
 
+    pk = peaks()
+    roof = {"bound": "tensor", "achieved": local_flops / per_launch_s / 1e12, "peak": pk["bf16_tflops"],
+            "unit": "TFLOP/s", "frac": local_flops / per_launch_s / 1e12 / pk["bf16_tflops"],
+            "traffic": None, "kernel": "attn_fwd_kernel", "peak_source": pk["source"] + " (burst cuBLAS bf16)",
+            "frac_of_nominal_2250": local_flops / per_launch_s / 1e12 / 2250.0}
+    if args.profile:
+        return dict(value=value, unit="TFLOP/s", secs=secs, clocks=clocks[0], roofline=roof,
+                    launches=args.steps)
+
     # parity spot check on one (b, h) against the oracle
     from oracle import attention_oracle as orc
 
@@ -337,11 +350,6 @@ def run_prefill(args, w, name, device, rank, world):
     e2e = {"value": total_units * e2e_steps / e2e_secs / 1e12, "unit": "TFLOP/s",
            "h2d_bytes_per_step": 3 * q.numel() * q.element_size(),
            "d2h_bytes_per_step": o.numel() * o.element_size(), "steps": e2e_steps}
-    pk = peaks()
-    roof = {"bound": "tensor", "achieved": local_flops / per_launch_s / 1e12, "peak": pk["bf16_tflops"],
-            "unit": "TFLOP/s", "frac": local_flops / per_launch_s / 1e12 / pk["bf16_tflops"],
-            "traffic": None, "kernel": "attn_fwd_kernel", "peak_source": pk["source"] + " (burst cuBLAS bf16)",
-            "frac_of_nominal_2250": local_flops / per_launch_s / 1e12 / 2250.0}
     return dict(value=value, unit="TFLOP/s", secs=secs, clocks=clocks[0], parity=parity, e2e=e2e,
                 roofline=roof, launches=args.steps)
 
@@ -411,7 +419,7 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
     res = dict(value=value, unit="GB/s", secs=secs, clocks=clocks[0], roofline=roof,
                launches=launches_per_step * steps)
 
-    if not sharded:
+    if not sharded and not args.profile:
         from oracle import attention_oracle as orc
 
         ref, lse_ref = orc.decode_fp32(q[:1, :2].cpu(), k[:1, :2].cpu(), v[:1, :2].cpu(), scale)
@@ -445,8 +453,13 @@ def main():
     ap.add_argument("--impl", default="tilefusion_b200", choices=["tilefusion_b200", "reference"])
     ap.add_argument("--workload", default="prefill_c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-secondary", action="store_true", help="skip the decode line and CPU baseline")
+    ap.add_argument("--profile", action="store_true",
+                    help="device-timed steps only (no end-to-end pass, parity check, decode line or CPU "
+                         "baseline): the command to put under ncu")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.profile:
+        args.no_secondary = True
     w = WORKLOADS[args.workload]
 
     if args.impl == "reference":

@@ -91,10 +91,9 @@ def lib() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not _LIB_PATH.exists():
-        from .build import build_library
+    from .build import build_library
 
-        build_library()
+    build_library()     # no-op when the library matches the sources
     try:
         handle = C.CDLL(str(_LIB_PATH))
     except OSError as e:  # pragma: no cover - depends on the machine

@@ -23,10 +23,9 @@ def ensure_loaded() -> None:
     from . import _cabi
 
     _cabi.lib()
-    if not _BIND_PATH.exists():
-        from .build import build_torch_binding
+    from .build import build_torch_binding
 
-        build_torch_binding()
+    build_torch_binding()     # no-op when the library matches the sources
     try:
         torch.ops.load_library(str(_BIND_PATH))
     except OSError as e:  # pragma: no cover - depends on the machine

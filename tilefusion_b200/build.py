@@ -15,6 +15,8 @@ Run ``python -m tilefusion_b200.build`` to (re)build both.
 
 from __future__ import annotations
 
+import fcntl
+import hashlib
 import os
 import shutil
 import subprocess
@@ -41,11 +43,37 @@ def _nvcc() -> str:
     return exe
 
 
-def _newer(target: Path, sources: list[Path]) -> bool:
-    if not target.exists():
-        return False
-    t = target.stat().st_mtime
-    return all(s.stat().st_mtime <= t for s in sources)
+def _source_hash(sources: list[Path], extra: str = "") -> str:
+    h = hashlib.sha256(extra.encode())
+    for s in sources:
+        h.update(s.name.encode())
+        h.update(s.read_bytes())
+    return h.hexdigest()
+
+
+def _up_to_date(target: Path, digest: str) -> bool:
+    """True when `target` was built from sources with this digest (recorded in
+    a side file, so the answer does not depend on file times, which a copy of
+    the tree to another machine does not preserve)."""
+    stamp = target.with_suffix(target.suffix + ".srchash")
+    return target.exists() and stamp.exists() and stamp.read_text().strip() == digest
+
+
+def _record(target: Path, digest: str) -> None:
+    target.with_suffix(target.suffix + ".srchash").write_text(digest + "\n")
+
+
+class _BuildLock:
+    """Serialises builds between processes (ranks of one job import together)."""
+
+    def __enter__(self):
+        self._f = open(PKG_DIR / ".build.lock", "w")
+        fcntl.flock(self._f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        fcntl.flock(self._f, fcntl.LOCK_UN)
+        self._f.close()
 
 
 def _run(cmd: list[str]) -> None:
@@ -63,13 +91,20 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     deps = sources + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [
         INCLUDE / "tilefusion_b200.h"
     ]
-    if not force and _newer(out, deps):
+    digest = _source_hash(deps, " ".join(NVCC_FLAGS))
+    if not force and _up_to_date(out, digest):
         return out
-    cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "-shared", "-o", str(out)]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [str(s) for s in sources]
-    _run(cmd)
+    with _BuildLock():
+        if not force and _up_to_date(out, digest):
+            return out
+        tmp = out.with_suffix(".so.tmp")
+        cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "-shared", "-o", str(tmp)]
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
+        cmd += [str(s) for s in sources]
+        _run(cmd)
+        os.replace(tmp, out)
+        _record(out, digest)
     return out
 
 
@@ -81,7 +116,8 @@ def build_torch_binding(force: bool = False) -> Path:
     out = PKG_DIR / BIND_NAME
     src = CSRC / "torch_bind.cc"
     deps = [src, INCLUDE / "tilefusion_b200.h"]
-    if not force and _newer(out, deps):
+    digest = _source_hash(deps, torch.__version__)
+    if not force and _up_to_date(out, digest):
         return out
     torch_lib = Path(torch.__file__).resolve().parent / "lib"
     inc = []
@@ -91,12 +127,17 @@ def build_torch_binding(force: bool = False) -> Path:
     cmd = [
         cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
         f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
-        f"-I{INCLUDE}", *inc, str(src), "-o", str(out),
+        f"-I{INCLUDE}", *inc, str(src), "-o", str(out.with_suffix(".so.tmp")),
         f"-L{PKG_DIR}", "-ltilefusion_b200", f"-L{torch_lib}",
         "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
         "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}",
     ]
-    _run(cmd)
+    with _BuildLock():
+        if not force and _up_to_date(out, digest):
+            return out
+        _run(cmd)
+        os.replace(out.with_suffix(".so.tmp"), out)
+        _record(out, digest)
     return out
 
 
