@@ -193,6 +193,43 @@ TF_EXPORT int tf_decode_gathered(const float* slots, int32_t n_ranks,
                                  int32_t dtype, void* o, int64_t o_stride_b,
                                  int64_t o_stride_h, float* lse, void* stream);
 
+/*
+ * Flash decoding for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference.
+ *
+ * Some hosts of this library may not call cudaMalloc on the serving path at
+ * all: a runtime that hands out one fixed arena at start-up and forbids any
+ * later allocation, a plugin loaded into a process whose memory pool it does
+ * not own, or code running inside a region where an allocation would
+ * synchronise the device.  tf_decode needs a workspace for its split-KV
+ * partial rows, which such a caller has nowhere to get.  This variant keeps
+ * the partial rows in a fixed 4 MiB array that is part of the library image
+ * (each GPU that loads the library holds it until the process exits), so the
+ * caller passes only inputs and outputs: same arguments and results as
+ * tf_decode minus the workspace.  It calls no cudaMalloc / cudaFree and no
+ * allocating routine of any library.
+ *
+ * Limits and rules:
+ *  - the partial rows, B*H*num_splits*(D+2)*4 bytes as reported by
+ *    tf_decode_plan, must fit in tf_decode_static_capacity() bytes; a larger
+ *    problem is rejected with TF_ERR_WORKSPACE and a message that names both
+ *    sizes (pass a smaller num_splits, or use tf_decode);
+ *  - the first call on each device looks up the array's device address (with
+ *    that device current) before it launches; make that first call outside
+ *    any stream capture;
+ *  - all calls on a device share the one array, which keeps whatever the last
+ *    call left in it.  Nothing in it has to start at zero -- every row that
+ *    the combine reads is first written by the split pass of the same call --
+ *    but two calls whose kernels overlap on the GPU (different streams, or
+ *    several host threads) race on it.  Issue them on one stream, or order
+ *    them with events.
+ */
+TF_EXPORT int tf_decode_static(const void* q, const void* k, const void* v, void* o,
+                               float* lse, const TfDecodeDesc* desc, void* stream);
+
+/* Size in bytes of the built-in scratch that tf_decode_static uses. */
+TF_EXPORT uint64_t tf_decode_static_capacity(void);
+
 /* ---- diagnostics -------------------------------------------------------- */
 
 /* Text of the last error raised on the calling thread ("" if none). */

@@ -28,6 +28,7 @@ EXPORTED = (
     "tf_attn_fwd", "tf_attn_plan", "tf_decode_plan", "tf_decode_split",
     "tf_decode_combine", "tf_decode", "tf_decode_partial", "tf_decode_gathered",
     "tf_last_error", "tf_device_status", "tf_abi_version",
+    "tf_decode_static", "tf_decode_static_capacity",
 )
 
 
@@ -110,11 +111,14 @@ def lib() -> C.CDLL:
     handle.tf_decode.argtypes = [vp, vp, vp, vp, fp, vp, u64, C.POINTER(TfDecodeDesc), vp]
     handle.tf_decode_partial.argtypes = [vp, vp, vp, fp, vp, u64, C.POINTER(TfDecodeDesc), vp]
     handle.tf_decode_gathered.argtypes = [fp, i32, i32, i32, i32, i32, vp, i64, i64, fp, vp]
+    handle.tf_decode_static.argtypes = [vp, vp, vp, vp, fp, C.POINTER(TfDecodeDesc), vp]
+    handle.tf_decode_static_capacity.argtypes = []
     handle.tf_last_error.restype = C.c_char_p
     handle.tf_device_status.argtypes = [C.POINTER(C.c_int32)]
     for name in EXPORTED:
-        if name != "tf_last_error":
+        if name not in ("tf_last_error", "tf_decode_static_capacity"):
             getattr(handle, name).restype = C.c_int
+    handle.tf_decode_static_capacity.restype = C.c_uint64
     _lib = handle
     return handle
 

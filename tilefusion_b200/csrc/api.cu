@@ -284,6 +284,36 @@ int plan_and_check_decode(const void* q, const void* k, const void* v, const voi
   return TF_OK;
 }
 
+// ---- scratch for tf_decode_static -------------------------------------------
+// Partial rows of the no-allocation decode entry point live here instead of in
+// a caller-provided workspace.  Every GPU that loads the library holds these
+// 4 MiB until the process exits.  In host code the name below is only a
+// stand-in for the symbol; the device address is looked up once per device.
+constexpr uint64_t kStaticScratchBytes = 4ull << 20;
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchBytes / sizeof(float)];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+float* g_scratch_ptr[kMaxDevices] = {};
+
+// Device address of g_decode_scratch on the current device (looked up on the
+// first call for that device, with that device current).
+int static_scratch(float** out) {
+  int dev = 0;
+  TF_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(TF_ERR_UNSUPPORTED, "device index %d is out of range", dev);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_decode_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(TF_ERR_CUDA, "cudaGetSymbolAddress(g_decode_scratch) failed: %s", cudaGetErrorString(e));
+    g_scratch_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_scratch_ptr[dev];
+  return TF_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -399,6 +429,35 @@ int tf_decode_gathered(const float* slots, int32_t n_ranks, int32_t batch, int32
                            (int32_t)rows, heads, head_dim, dtype, o, o_stride_b, o_stride_h, lse, nullptr,
                            nullptr, stream);
 }
+
+int tf_decode_static(const void* q, const void* k, const void* v, void* o, float* lse,
+                     const TfDecodeDesc* desc, void* stream) {
+  if (int rc = check_decode_desc(desc)) return rc;
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr)
+    return fail(TF_ERR_BAD_ARG, "q, k, v and o must be non-null");
+  if (desc->len_kv < 1) return fail(TF_ERR_BAD_ARG, "len_kv must be positive for a full decode");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v))
+    return fail(TF_ERR_UNSUPPORTED, "q, k and v must be 16-byte aligned");
+  TfDecodePlan plan;
+  tfb::plan_decode(*desc, sm_count(), &plan);
+  if (plan.workspace_bytes > kStaticScratchBytes)
+    return fail(TF_ERR_WORKSPACE,
+                "this problem needs %llu bytes of scratch but the built-in scratch holds %llu; lower "
+                "num_splits or batch*heads, or use tf_decode with a caller-provided workspace",
+                (unsigned long long)plan.workspace_bytes, (unsigned long long)kStaticScratchBytes);
+  float* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  const int rows = desc->batch * desc->heads;
+  const int D = desc->head_dim;
+  float* part_o = scratch;
+  float* part_ml = part_o + (int64_t)rows * plan.num_splits * D;
+  if (int rc = dispatch_split(q, k, v, part_o, part_ml, desc, plan, static_cast<cudaStream_t>(stream))) return rc;
+  return tf_decode_combine(part_o, part_ml, plan.num_splits, D, (int64_t)plan.num_splits * D, 2,
+                           (int64_t)plan.num_splits * 2, rows, desc->heads, D, desc->dtype, o,
+                           desc->o_stride_b, desc->o_stride_h, lse, nullptr, nullptr, stream);
+}
+
+uint64_t tf_decode_static_capacity(void) { return kStaticScratchBytes; }
 
 const char* tf_last_error(void) { return g_err; }
 
