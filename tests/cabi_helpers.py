@@ -35,7 +35,7 @@ def attn_desc(q, k, v, o, scale, causal, tile_q=0, tile_kv=0) -> _cabi.TfAttnDes
     return d
 
 
-def attn_fwd(q, k, v, scale, causal=False, want_lse=True, poison=True):
+def attn_fwd(q, k, v, scale, causal=False, want_lse=True, poison=True, tile_q=0):
     """Runs tf_attn_fwd; returns (O, LSE).  Outputs are NaN-filled first so
     that any element the kernel fails to write is caught by the comparison."""
     lib = _cabi.lib()
@@ -45,7 +45,7 @@ def attn_fwd(q, k, v, scale, causal=False, want_lse=True, poison=True):
     if poison:
         o.fill_(float("nan"))
         lse.fill_(float("nan"))
-    d = attn_desc(q, k, v, o, scale, causal)
+    d = attn_desc(q, k, v, o, scale, causal, tile_q, 128 if tile_q else 0)
     rc = lib.tf_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                          lse.data_ptr() if want_lse else None, C.byref(d), _stream())
     _cabi.check(rc)

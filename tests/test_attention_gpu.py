@@ -36,9 +36,15 @@ def _layout(t, order):
     return t.transpose(-1, -2).contiguous().transpose(-1, -2)
 
 
+# tile_q selects the kernel variant: 128 = one Q tile per CTA, 256 = two Q tiles
+# per CTA (persistent); 0 leaves the choice to the registry.
+TILE_Q = [128, 256]
+
+
 @pytest.mark.parametrize("name", ["ref_case1", "ref_case2", "c1_head", "multi_kv"])
 @pytest.mark.parametrize("k_order,v_order", [("LD", "LD"), ("DL", "DL"), ("DL", "LD"), ("LD", "DL")])
-def test_golden_fixtures(golden, name, k_order, v_order):
+@pytest.mark.parametrize("tile_q", TILE_Q)
+def test_golden_fixtures(golden, name, k_order, v_order, tile_q):
     from cabi_helpers import attn_fwd, device_status
 
     data, meta = golden
@@ -47,7 +53,8 @@ def test_golden_fixtures(golden, name, k_order, v_order):
     k = torch.from_numpy(data[f"{name}.key_t"]).cuda().t()[None, None]
     v = torch.from_numpy(data[f"{name}.v"]).cuda()[None, None]
     ref = torch.from_numpy(data[f"{name}.out_fp32"])[None, None]
-    o, lse = attn_fwd(q.contiguous(), _layout(k, k_order), _layout(v, v_order), m["softmax_scale"], m["causal"])
+    o, lse = attn_fwd(q.contiguous(), _layout(k, k_order), _layout(v, v_order), m["softmax_scale"], m["causal"],
+                      tile_q=tile_q)
     _, lse_ref = orc.attention_fp32(q.cpu(), k.cpu(), v.cpu(), m["softmax_scale"], m["causal"])
     _check(o, lse, ref, lse_ref, torch.float16)
     if m["has_fp16"]:
@@ -99,38 +106,43 @@ SHAPES = [
     (1, 2, 300, 200, 64, True),      # causal, Lq > Lk, ragged
     (1, 2, 200, 456, 128, True),     # causal, Lq < Lk
     (3, 5, 257, 129, 64, False),
+    (1, 3, 640, 640, 128, True),     # causal, several Q-tile pairs with unequal KV counts
+    (40, 8, 256, 384, 128, False),   # more work items than SMs: persistent loop over items
 ]
 
 
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
-def test_shapes(shape, dtype):
+@pytest.mark.parametrize("tile_q", TILE_Q)
+def test_shapes(shape, dtype, tile_q):
     from cabi_helpers import attn_fwd, device_status
 
     b, h, lq, lk, d, causal = shape
     q, k, v = orc.seeded_inputs(11, (b, h, lq, d), (b, h, lk, d), (b, h, lk, d), 1.0, dtype)
     scale = 1.0 / math.sqrt(d)
-    o, lse = attn_fwd(q.cuda(), k.cuda(), v.cuda(), scale, causal)
+    o, lse = attn_fwd(q.cuda(), k.cuda(), v.cuda(), scale, causal, tile_q=tile_q)
     ref, lse_ref = orc.attention_fp32(q, k, v, scale, causal)
     _check(o, lse, ref, lse_ref, dtype)
     assert device_status() == 0
 
 
-def test_large_scores_exercise_rescale():
+@pytest.mark.parametrize("tile_q", TILE_Q)
+def test_large_scores_exercise_rescale(tile_q):
     """Row maxima that grow tile after tile force the O rescale path."""
     from cabi_helpers import attn_fwd
 
-    b, h, lq, lk, d = 1, 2, 128, 1024, 128
+    b, h, lq, lk, d = 1, 2, 256, 1024, 128
     q, k, v = orc.seeded_inputs(5, (b, h, lq, d), (b, h, lk, d), (b, h, lk, d), 1.0)
     ramp = torch.linspace(0.2, 3.0, lk).view(1, 1, lk, 1)
     k = (k.float() * ramp).half()
     scale = 1.0
-    o, lse = attn_fwd(q.cuda(), k.cuda(), v.cuda(), scale, False)
+    o, lse = attn_fwd(q.cuda(), k.cuda(), v.cuda(), scale, False, tile_q=tile_q)
     ref, lse_ref = orc.attention_fp32(q, k, v, scale, False)
     _check(o, lse, ref, lse_ref, torch.float16)
 
 
-def test_strided_views_need_no_copy():
+@pytest.mark.parametrize("tile_q", TILE_Q)
+def test_strided_views_need_no_copy(tile_q):
     """Q/K/V/O as slices of packed [B, L, 3, H, D] / [B, L, H, D] buffers."""
     from cabi_helpers import attn_fwd
 
@@ -139,7 +151,7 @@ def test_strided_views_need_no_copy():
     qkv = torch.randn(b, l, 3, h, d, generator=g).half().cuda()
     q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
     scale = 1.0 / math.sqrt(d)
-    o, lse = attn_fwd(q, k, v, scale, False)
+    o, lse = attn_fwd(q, k, v, scale, False, tile_q=tile_q)
     ref, lse_ref = orc.attention_fp32(q.cpu(), k.cpu(), v.cpu(), scale, False)
     _check(o, lse, ref, lse_ref, torch.float16)
 

@@ -62,8 +62,18 @@ def _attn_desc(**kw):
 def test_attn_plan_and_layout_detection(native_lib):
     plan = _cabi.TfAttnPlan()
     assert native_lib.tf_attn_plan(C.byref(_attn_desc()), C.byref(plan)) == 0
-    assert (plan.tile_q, plan.tile_kv, plan.ctas_per_sm) == (128, 128, 2)
-    assert plan.grid == 16 * 32 * 8
+    # big problem: two Q tiles per CTA, persistent grid of one CTA per SM
+    assert (plan.tile_q, plan.tile_kv, plan.ctas_per_sm) == (256, 128, 1)
+    assert plan.grid == 148
+    # a tile hint that names a compiled variant wins
+    assert native_lib.tf_attn_plan(C.byref(_attn_desc(tile_q=128, tile_kv=128)), C.byref(plan)) == 0
+    assert (plan.tile_q, plan.ctas_per_sm, plan.grid) == (128, 2, 16 * 32 * 8)
+    # a single Q tile, or too few tile pairs to fill the GPU: one tile per CTA
+    assert native_lib.tf_attn_plan(C.byref(_attn_desc(len_q=128)), C.byref(plan)) == 0
+    assert plan.tile_q == 128
+    assert native_lib.tf_attn_plan(C.byref(_attn_desc(batch=1, heads=8, len_q=512)), C.byref(plan)) == 0
+    assert plan.tile_q == 128
+    assert native_lib.tf_attn_plan(C.byref(_attn_desc()), C.byref(plan)) == 0
     assert (plan.k_mn_major, plan.v_mn_major) == (0, 1)     # K [Lk, D], V [Lk, Dv]
     assert 0 < plan.smem_bytes * plan.ctas_per_sm <= 227 * 1024
     # the layouts TileFusion's operator receives: K [Lk, D], V^T [Dv, Lk]

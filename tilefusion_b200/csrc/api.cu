@@ -14,6 +14,7 @@
 #include <mutex>
 
 #include "attn_fwd_sm100.cuh"
+#include "attn_fwd_pair_sm100.cuh"
 #include "decode_sm100.cuh"
 #include "registry.h"
 #include "tilefusion_b200.h"
@@ -121,37 +122,40 @@ int sm_count() {
   return n;
 }
 
-template <typename T, int D>
-int launch_attn(const void* q, const void* k, const void* v, void* o, float* lse, const TfAttnDesc* d,
-                const TfAttnPlan& plan, cudaStream_t stream) {
-  using Smem = tfb::AttnSmem<D>;
+// Tensor maps and kernel arguments shared by the prefill variants.
+struct AttnLaunch {
   CUtensorMap mq, mk, mv;
+  tfb::AttnFwdArgs args;
+};
+
+int prepare_attn(const void* q, const void* k, const void* v, void* o, float* lse, const TfAttnDesc* d,
+                 const TfAttnPlan& plan, AttnLaunch* out) {
+  const int D = d->head_dim;
   const uint64_t B = d->batch, H = d->heads;
   {
     const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->len_q, H, B};
     const int64_t str[3] = {d->q_stride_l, d->q_stride_h, d->q_stride_b};
-    if (int rc = encode_map(&mq, d->dtype, q, dims, str, 64, tfb::kAttnTile, "Q")) return rc;
+    if (int rc = encode_map(&out->mq, d->dtype, q, dims, str, 64, tfb::kAttnTile, "Q")) return rc;
   }
   if (!plan.k_mn_major) {
     const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->len_kv, H, B};
     const int64_t str[3] = {d->k_stride_l, d->k_stride_h, d->k_stride_b};
-    if (int rc = encode_map(&mk, d->dtype, k, dims, str, 64, tfb::kAttnTile, "K")) return rc;
+    if (int rc = encode_map(&out->mk, d->dtype, k, dims, str, 64, tfb::kAttnTile, "K")) return rc;
   } else {
     const uint64_t dims[4] = {(uint64_t)d->len_kv, (uint64_t)D, H, B};
     const int64_t str[3] = {d->k_stride_d, d->k_stride_h, d->k_stride_b};
-    if (int rc = encode_map(&mk, d->dtype, k, dims, str, 64, D, "K (stored [D, Lk])")) return rc;
+    if (int rc = encode_map(&out->mk, d->dtype, k, dims, str, 64, D, "K (stored [D, Lk])")) return rc;
   }
   if (plan.v_mn_major) {
     const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->len_kv, H, B};
     const int64_t str[3] = {d->v_stride_l, d->v_stride_h, d->v_stride_b};
-    if (int rc = encode_map(&mv, d->dtype, v, dims, str, 64, tfb::kAttnTile, "V")) return rc;
+    if (int rc = encode_map(&out->mv, d->dtype, v, dims, str, 64, tfb::kAttnTile, "V")) return rc;
   } else {
     const uint64_t dims[4] = {(uint64_t)d->len_kv, (uint64_t)D, H, B};
     const int64_t str[3] = {d->v_stride_d, d->v_stride_h, d->v_stride_b};
-    if (int rc = encode_map(&mv, d->dtype, v, dims, str, 64, D, "V (stored [Dv, Lk])")) return rc;
+    if (int rc = encode_map(&out->mv, d->dtype, v, dims, str, 64, D, "V (stored [Dv, Lk])")) return rc;
   }
-
-  tfb::AttnFwdArgs args;
+  tfb::AttnFwdArgs& args = out->args;
   args.o = o;
   args.lse = lse;
   args.len_q = d->len_q;
@@ -165,7 +169,13 @@ int launch_attn(const void* q, const void* k, const void* v, void* o, float* lse
   args.o_stride_l = d->o_stride_l;
   args.lse_stride_b = (long long)d->heads * d->len_q;
   args.lse_stride_h = d->len_q;
+  return TF_OK;
+}
 
+// One 128-row Q tile per CTA, two CTAs per SM.
+template <typename T, int D>
+int launch_attn(const AttnLaunch& L, const TfAttnDesc* d, cudaStream_t stream) {
+  using Smem = tfb::AttnSmem<D>;
   auto kern = tfb::attn_fwd_kernel<T, D>;
   static thread_local int configured_device = -1;
   int dev = 0;
@@ -176,9 +186,40 @@ int launch_attn(const void* q, const void* k, const void* v, void* o, float* lse
   }
   const int n_q_tiles = (d->len_q + tfb::kAttnTile - 1) / tfb::kAttnTile;
   dim3 grid(n_q_tiles, d->heads, d->batch);
-  kern<<<grid, tfb::kAttnThreads, Smem::kBytes, stream>>>(mq, mk, mv, args);
+  kern<<<grid, tfb::kAttnThreads, Smem::kBytes, stream>>>(L.mq, L.mk, L.mv, L.args);
   TF_CUDA_TRY(cudaGetLastError());
   return TF_OK;
+}
+
+// Two Q tiles per CTA, persistent grid of one CTA per SM.
+template <typename T, int D>
+int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan& plan, cudaStream_t stream) {
+  using Smem = tfb::AttnPairSmem<D>;
+  auto kern = tfb::attn_fwd_pair_kernel<T, D>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  TF_CUDA_TRY(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    TF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
+    configured_device = dev;
+  }
+  tfb::AttnPairArgs a;
+  a.base = L.args;
+  a.heads = d->heads;
+  a.batch = d->batch;
+  a.n_pairs = (d->len_q + 2 * tfb::kAttnTile - 1) / (2 * tfb::kAttnTile);
+  a.n_items = d->batch * d->heads * a.n_pairs;
+  kern<<<plan.grid, tfb::kPairThreads, Smem::kBytes, stream>>>(L.mq, L.mk, L.mv, a);
+  TF_CUDA_TRY(cudaGetLastError());
+  return TF_OK;
+}
+
+template <typename T, int D>
+int run_attn(const void* q, const void* k, const void* v, void* o, float* lse, const TfAttnDesc* d,
+             const TfAttnPlan& plan, cudaStream_t stream) {
+  AttnLaunch L;
+  if (int rc = prepare_attn(q, k, v, o, lse, d, plan, &L)) return rc;
+  return plan.tile_q == 256 ? launch_attn_pair<T, D>(L, d, plan, stream) : launch_attn<T, D>(L, d, stream);
 }
 
 int check_decode_desc(const TfDecodeDesc* d) {
@@ -322,7 +363,10 @@ int tf_attn_plan(const TfAttnDesc* desc, TfAttnPlan* plan) {
   if (plan == nullptr) return fail(TF_ERR_BAD_ARG, "plan is null");
   if (int rc = check_attn_desc(desc)) return rc;
   tfb::plan_attn(*desc, sm_count(), plan);
-  plan->smem_bytes = desc->head_dim == 128 ? tfb::AttnSmem<128>::kBytes : tfb::AttnSmem<64>::kBytes;
+  if (plan->tile_q == 256)
+    plan->smem_bytes = desc->head_dim == 128 ? tfb::AttnPairSmem<128>::kBytes : tfb::AttnPairSmem<64>::kBytes;
+  else
+    plan->smem_bytes = desc->head_dim == 128 ? tfb::AttnSmem<128>::kBytes : tfb::AttnSmem<64>::kBytes;
   return TF_OK;
 }
 
@@ -336,10 +380,10 @@ int tf_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   tfb::plan_attn(*desc, sm_count(), &plan);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (desc->head_dim == 128)
-    return desc->dtype == TF_F16 ? launch_attn<__half, 128>(q, k, v, o, lse, desc, plan, s)
-                                 : launch_attn<__nv_bfloat16, 128>(q, k, v, o, lse, desc, plan, s);
-  return desc->dtype == TF_F16 ? launch_attn<__half, 64>(q, k, v, o, lse, desc, plan, s)
-                               : launch_attn<__nv_bfloat16, 64>(q, k, v, o, lse, desc, plan, s);
+    return desc->dtype == TF_F16 ? run_attn<__half, 128>(q, k, v, o, lse, desc, plan, s)
+                                 : run_attn<__nv_bfloat16, 128>(q, k, v, o, lse, desc, plan, s);
+  return desc->dtype == TF_F16 ? run_attn<__half, 64>(q, k, v, o, lse, desc, plan, s)
+                               : run_attn<__nv_bfloat16, 64>(q, k, v, o, lse, desc, plan, s);
 }
 
 int tf_decode_plan(const TfDecodeDesc* desc, TfDecodePlan* plan) {

@@ -1,0 +1,474 @@
+// Fused attention forward for sm_100a, two Q tiles per CTA (256 query rows),
+// persistent over (head, Q-tile-pair) work items.
+//
+// Same arithmetic as attn_fwd_kernel (attn_fwd_sm100.cuh) and the same place
+// in TileFusion's path (include/kernels/flash_attention_device.cuh:130-312);
+// the difference is the schedule.  With one Q tile per CTA the tensor pipe and
+// the exp unit take turns; here one thread fixes the MMA issue order
+//     S0_0 S1_0 | PV0_0 S0_1 | PV1_0 S1_1 | PV0_1 S0_2 | ...
+// so that while the tensor pipe works for tile 0 the softmax warps of tile 1
+// run, and vice versa.  Roles (320 threads, one CTA per SM):
+//   warps 0-3  softmax + epilogue of Q tile 0   (one row per thread)
+//   warps 4-7  softmax + epilogue of Q tile 1
+//   warp  8    tcgen05.mma issuer (one thread), owns the TMEM allocation
+//   warp  9    TMA producer (one thread)
+//   warps 10-11 idle; they complete the third warpgroup so that it can hand
+//              its registers to the softmax warpgroups (setmaxnreg)
+// TMEM (512 columns): S0 | S1 | O0 | O1, each 128 fp32 columns (O: D columns);
+// P overwrites the first 64 columns of its S and is the TMEM A operand of PV.
+// Shared memory: Q0, Q1 and a ring of K/V stages (K_0 V_0 K_1 V_1 ...), each
+// stage released by a tcgen05.commit after the last MMA that reads it, so both
+// Q tiles share every K/V load.
+#pragma once
+
+#include <type_traits>
+
+#include "attn_fwd_sm100.cuh"
+
+namespace tfb {
+
+constexpr int kPairThreads = 384;     // three warpgroups; warps 10-11 only donate registers
+constexpr int kPairRegsSoftmax = 200;
+constexpr int kPairRegsIssue = 96;
+constexpr int kPairStages = 5;
+
+struct AttnPairArgs {
+  AttnFwdArgs base;
+  int heads;
+  int batch;
+  int n_pairs;        // ceil(len_q / 256)
+  int n_items;        // batch * heads * n_pairs
+};
+
+template <int D>
+struct AttnPairSmem {
+  static constexpr int kTileBytes = kAttnTile * D * 2;
+  static constexpr int kBlockBytes = kAttnTile * 128;
+  static constexpr int kOffQ = 0;                                   // Q0, Q1
+  static constexpr int kOffKV = 2 * kTileBytes;                     // ring
+  static constexpr int kOffBar = kOffKV + kPairStages * kTileBytes;
+  // barrier slots (8 bytes each)
+  static constexpr int kBarQFull = 0;      // [2]
+  static constexpr int kBarQEmpty = 2;     // [2]
+  static constexpr int kBarSFull = 4;      // [2]
+  static constexpr int kBarPFull = 6;      // [2]
+  static constexpr int kBarOFull = 8;      // [2]
+  static constexpr int kBarOEmpty = 10;    // [2]
+  static constexpr int kBarKVFull = 12;    // [kPairStages]
+  static constexpr int kBarKVEmpty = 12 + kPairStages;
+  static constexpr int kNumBars = 12 + 2 * kPairStages;
+  static constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
+  static constexpr int kOffAbort = kOffTmemSlot + 4;
+  static constexpr int kBytes = kOffAbort + 4 + 1024;               // + slack for 1024-B alignment
+};
+
+enum AttnPairWaitCode {
+  kPWaitQFull = 301, kPWaitQEmpty = 302, kPWaitKVFull = 303, kPWaitKVEmpty = 304,
+  kPWaitSFull = 305, kPWaitPFull = 306, kPWaitOFull = 307, kPWaitOEmpty = 308, kPWaitEpi = 309
+};
+
+// Work item -> (batch, head, pair).  Non-causal items of one head are adjacent
+// (their K/V stay in L2); causal items are ordered heaviest pair first so that
+// the round-robin deal over CTAs is balanced.
+__device__ __forceinline__ void pair_item(const AttnPairArgs& a, int item, int& b, int& h, int& pair) {
+  int bh;
+  if (a.base.causal) {
+    const int n_bh = a.batch * a.heads;
+    pair = a.n_pairs - 1 - item / n_bh;
+    bh = item % n_bh;
+  } else {
+    bh = item / a.n_pairs;
+    pair = item - bh * a.n_pairs;
+  }
+  b = bh / a.heads;
+  h = bh - b * a.heads;
+}
+
+// KV tiles visited by Q tile x (rows q0 .. q0+127) of a pair.
+__device__ __forceinline__ int kv_tiles_for(const AttnFwdArgs& a, int q0) {
+  if (q0 >= a.len_q) return 0;
+  int n = (a.len_kv + kAttnTile - 1) / kAttnTile;
+  if (a.causal) n = min(n, q0 / kAttnTile + 1);
+  return n;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kPairThreads, 1)
+attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
+                     const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const AttnPairArgs pargs) {
+  using S = AttnPairSmem<D>;
+  const AttnFwdArgs& args = pargs.base;
+  constexpr int kIsBf16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr int kTmemCols = 512;
+  constexpr int kBlocks = D / 64;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bars = smem_base + S::kOffBar;
+  auto bar = [&](int slot) -> uint32_t { return bars + slot * 8; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kOffTmemSlot);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(bar(S::kBarQFull + x), 1);
+      mbar_init(bar(S::kBarQEmpty + x), 1);
+      mbar_init(bar(S::kBarSFull + x), 1);
+      mbar_init(bar(S::kBarPFull + x), 128);
+      mbar_init(bar(S::kBarOFull + x), 1);
+      mbar_init(bar(S::kBarOEmpty + x), 128);
+    }
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(bar(S::kBarKVFull + s), 1);
+      mbar_init(bar(S::kBarKVEmpty + s), 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    tmem_alloc<kTmemCols>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Each role's code sits under the register re-allocation that applies to it.
+  if (warp >= 8) {
+   setmaxnreg_dec<kPairRegsIssue>();
+   if (warp == 9) {
+    // ========================================================= TMA producer ==
+    if (lane == 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      uint32_t stage = 0, phase = 0;      // ring position; phase of the stage's barriers
+      uint32_t q_uses[2] = {0, 0};        // loads issued so far into Q buffer x
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
+        int b, h, pair;
+        pair_item(pargs, item, b, h, pair);
+        const int q0 = pair * 2 * kAttnTile;
+        const int n0 = kv_tiles_for(args, q0), n1 = kv_tiles_for(args, q0 + kAttnTile);
+        const int n = max(n0, n1);
+        for (int x = 0; x < 2 && ok; ++x) {
+          if ((x == 0 ? n0 : n1) == 0) continue;
+          if (q_uses[x] > 0)
+            ok = mbar_wait(bar(S::kBarQEmpty + x), (q_uses[x] - 1) & 1, abort_flag, kPWaitQEmpty);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar(S::kBarQFull + x), S::kTileBytes);
+#pragma unroll
+          for (int blk = 0; blk < kBlocks; ++blk)
+            tma_load_4d(smem_base + S::kOffQ + x * S::kTileBytes + blk * S::kBlockBytes, &map_q,
+                        bar(S::kBarQFull + x), blk * 64, q0 + x * kAttnTile, h, b);
+          ++q_uses[x];
+        }
+        for (int j = 0; ok && j < n; ++j) {
+          for (int kv = 0; kv < 2; ++kv) {
+            ok = mbar_wait(bar(S::kBarKVEmpty + stage), phase ^ 1, abort_flag, kPWaitKVEmpty);
+            if (!ok) break;
+            const uint32_t dst = smem_base + S::kOffKV + stage * S::kTileBytes;
+            const uint32_t full = bar(S::kBarKVFull + stage);
+            mbar_arrive_expect_tx(full, S::kTileBytes);
+            const bool natural = kv == 0 ? !args.k_mn_major : (args.v_mn_major != 0);
+            const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
+            if (natural) {
+              // rows = keys, 64 head-dim elements per swizzle block
+#pragma unroll
+              for (int blk = 0; blk < kBlocks; ++blk)
+                tma_load_4d(dst + blk * S::kBlockBytes, map, full, blk * 64, j * kAttnTile, h, b);
+            } else {
+              // rows = head dim, 64 keys per swizzle block
+#pragma unroll
+              for (int blk = 0; blk < 2; ++blk)
+                tma_load_4d(dst + blk * (D * 128), map, full, j * kAttnTile + blk * 64, 0, h, b);
+            }
+            if (++stage == kPairStages) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+        }
+      }
+      if (!ok) {
+        // let copies still in flight land before the CTA gives up its shared memory
+        const unsigned long long t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+   } else if (warp == 8) {
+    // =========================================================== MMA issuer ==
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(128, 128, kIsBf16, 0, args.k_mn_major);
+      const uint32_t idesc_o = make_idesc(128, D, kIsBf16, 0, args.v_mn_major);
+      uint32_t stage = 0, phase = 0;       // ring position of the next stage to consume
+      uint32_t q_cnt[2] = {0, 0};          // Q loads consumed per buffer
+      uint32_t p_cnt[2] = {0, 0};          // P tiles consumed per Q tile
+      uint32_t items_done[2] = {0, 0};     // epilogues awaited per Q tile
+      bool ok = true;
+
+      // Operand B addressing, in 16-byte units: MMA step k (16 elements along the
+      // contraction) starts at (k >> 2) * step_hi + (k & 3) * step_lo.
+      //   K-major  (rows of 64 contraction elements): next 64-element block, 32 B within it
+      //   MN-major (one 128-B row per contraction index): 16 rows = 2048 B per step
+      const uint32_t k_step_hi = (args.k_mn_major ? 4 * 2048 : S::kBlockBytes) >> 4;
+      const uint32_t k_step_lo = (args.k_mn_major ? 2048 : 32) >> 4;
+      const uint32_t k_lbo = args.k_mn_major ? D * 128 : 16;
+      const uint32_t v_step_hi = (args.v_mn_major ? 4 * 2048 : D * 128) >> 4;
+      const uint32_t v_step_lo = (args.v_mn_major ? 2048 : 32) >> 4;
+      const uint32_t v_lbo = args.v_mn_major ? S::kBlockBytes : 16;
+
+      auto issue_s = [&](int x, uint32_t k_smem) {
+        const uint32_t a0 = desc_lo(smem_base + S::kOffQ + x * S::kTileBytes, 16);
+        const uint32_t b0 = desc_lo(k_smem, k_lbo);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          umma_ss_lohi(tmem_base + x * 128, a0 + (((k >> 2) * S::kBlockBytes + (k & 3) * 32) >> 4),
+                       b0 + (k >> 2) * k_step_hi + (k & 3) * k_step_lo, kDescHiSw128, idesc_s, k > 0);
+        }
+        umma_commit(bar(S::kBarSFull + x));
+      };
+      auto issue_pv = [&](int x, uint32_t v_smem, bool accumulate) {
+        const uint32_t b0 = desc_lo(v_smem, v_lbo);
+#pragma unroll
+        for (int k = 0; k < kAttnTile / 16; ++k) {
+          umma_ts_lohi(tmem_base + 256 + x * 128, tmem_base + x * 128 + k * 8,
+                       b0 + (k >> 2) * v_step_hi + (k & 3) * v_step_lo, kDescHiSw128, idesc_o,
+                       accumulate || (k > 0));
+        }
+        umma_commit(bar(S::kBarOFull + x));
+      };
+      // Waits for the next ring stage and returns its shared-memory address.
+      auto next_stage = [&](uint32_t& smem_addr, uint32_t& stage_idx) -> bool {
+        if (!mbar_wait(bar(S::kBarKVFull + stage), phase, abort_flag, kPWaitKVFull)) return false;
+        smem_addr = smem_base + S::kOffKV + stage * S::kTileBytes;
+        stage_idx = stage;
+        if (++stage == kPairStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+        return true;
+      };
+
+      for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
+        int b, h, pair;
+        pair_item(pargs, item, b, h, pair);
+        const int q0 = pair * 2 * kAttnTile;
+        const int nx[2] = {kv_tiles_for(args, q0), kv_tiles_for(args, q0 + kAttnTile)};
+        const int n = max(nx[0], nx[1]);
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (nx[x] == 0) continue;
+          ok = mbar_wait(bar(S::kBarQFull + x), q_cnt[x] & 1, abort_flag, kPWaitQFull);
+          ++q_cnt[x];
+        }
+        if (!ok) break;
+        uint32_t k_smem = 0, k_stage = 0, v_smem = 0, v_stage = 0;
+        ok = next_stage(k_smem, k_stage);
+        if (!ok) break;
+        tc_fence_after();
+        for (int x = 0; x < 2; ++x) {
+          if (nx[x] == 0) continue;
+          issue_s(x, k_smem);
+          if (nx[x] == 1) umma_commit(bar(S::kBarQEmpty + x));
+        }
+        umma_commit(bar(S::kBarKVEmpty + k_stage));
+
+        for (int j = 0; ok && j < n; ++j) {
+          ok = next_stage(v_smem, v_stage);
+          if (!ok) break;
+          bool have_k = false;
+          for (int x = 0; x < 2 && ok; ++x) {
+            if (j < nx[x]) {
+              ok = mbar_wait(bar(S::kBarPFull + x), p_cnt[x] & 1, abort_flag, kPWaitPFull);
+              if (!ok) break;
+              ++p_cnt[x];
+              if (j == 0 && items_done[x] > 0) {
+                // the previous item's epilogue must have read O_x out of TMEM
+                ok = mbar_wait(bar(S::kBarOEmpty + x), (items_done[x] - 1) & 1, abort_flag, kPWaitOEmpty);
+                if (!ok) break;
+              }
+              tc_fence_after();
+              issue_pv(x, v_smem, j > 0);
+            }
+            if (x == 1) umma_commit(bar(S::kBarKVEmpty + v_stage));
+            if (j + 1 < nx[x]) {
+              if (!have_k) {
+                ok = next_stage(k_smem, k_stage);
+                if (!ok) break;
+                have_k = true;
+              }
+              issue_s(x, k_smem);
+              if (j + 2 == nx[x]) umma_commit(bar(S::kBarQEmpty + x));
+            }
+            if (x == 1 && have_k) umma_commit(bar(S::kBarKVEmpty + k_stage));
+          }
+        }
+        for (int x = 0; x < 2; ++x)
+          if (nx[x] > 0) ++items_done[x];
+      }
+    }
+   }   // warps 10 and 11 only donate registers
+  } else {
+    setmaxnreg_inc<kPairRegsSoftmax>();
+    // ======================================================== softmax warps ==
+    const int x = warp >> 2;                                 // which Q tile of the pair
+    const int quarter = warp & 3;                            // TMEM lane quarter of this warp
+    const int row = quarter * 32 + lane;
+    const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
+    const uint32_t col_s = x * 128, col_p = x * 128, col_o = 256 + x * 128;
+    const uint32_t bar_s = bar(S::kBarSFull + x), bar_p = bar(S::kBarPFull + x);
+    const uint32_t bar_o = bar(S::kBarOFull + x), bar_oe = bar(S::kBarOEmpty + x);
+    uint32_t s_cnt = 0;      // S tiles consumed
+    uint32_t o_base = 0;     // PV completions of earlier items
+    bool ok = true;
+
+    for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
+      int b, h, pair;
+      pair_item(pargs, item, b, h, pair);
+      const int q0 = pair * 2 * kAttnTile + x * kAttnTile;
+      const int n_kv = kv_tiles_for(args, q0);
+      if (n_kv == 0) continue;
+      const int q_idx = q0 + row;
+      float m_used = -INFINITY;
+      float l_run = 0.f;
+
+      for (int j = 0; j < n_kv; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_s, s_cnt & 1, abort_flag, kPWaitSFull));
+        if (!ok) break;
+        ++s_cnt;
+        tc_fence_after();
+
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + col_s + c * 32, sr[c]);
+        tmem_wait_ld();
+
+        const int kv0 = j * kAttnTile;
+        const bool need_mask =
+            (kv0 + kAttnTile > args.len_kv) || (args.causal && (kv0 + kAttnTile - 1 > q0));
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = kv0 + c * 32 + i;
+              const bool masked = (col >= args.len_kv) || (args.causal && col > q_idx);
+              if (masked) sr[c][i] = 0xff800000u;  // -inf
+            }
+        }
+
+        // row maximum with four independent chains
+        float mx[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          mx[c] = __uint_as_float(sr[c][0]);
+#pragma unroll
+          for (int i = 1; i < 32; ++i) mx[c] = fmaxf(mx[c], __uint_as_float(sr[c][i]));
+        }
+        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+
+        const bool grow = (m_tile - m_used) * args.scale_log2 > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m_used, m_tile);
+          const float alpha = fast_exp2((m_used - m_new) * args.scale_log2);
+          m_used = m_new;
+          l_run *= alpha;
+          if (j > 0) {
+            ok = __all_sync(0xffffffffu,
+                            mbar_wait(bar_o, (o_base + j - 1) & 1, abort_flag, kPWaitOFull));
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 16; ++c) {
+              uint32_t orow[16];
+              tmem_ld16(t_lane + col_o + c * 16, orow);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+              tmem_st16(t_lane + col_o + c * 16, orow);
+            }
+          }
+        }
+
+        const float m_scaled = m_used * args.scale_log2;
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), args.scale_log2, -m_scaled));
+            const float p1 =
+                fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), args.scale_log2, -m_scaled));
+            ls[(i >> 1) & 3] += p0 + p1;
+            pk[i >> 1] = pack2<T>(p0, p1);
+          }
+          tmem_st16(t_lane + col_p + c * 16, pk);
+        }
+        l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p);
+      }
+      if (!ok) break;
+
+      // ---------------------------------------------------------- epilogue --
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_o, (o_base + n_kv - 1) & 1, abort_flag, kPWaitEpi));
+      if (!ok) break;
+      o_base += n_kv;
+      tc_fence_after();
+      const float inv_l = 1.0f / l_run;
+      const bool row_valid = q_idx < args.len_q;
+      T* o_row = reinterpret_cast<T*>(args.o) + (long long)b * args.o_stride_b +
+                 (long long)h * args.o_stride_h + (long long)q_idx * args.o_stride_l;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t orow[32];
+        tmem_ld32(t_lane + col_o + c * 32, orow);
+        tmem_wait_ld();
+        if (c == D / 32 - 1) {
+          // O_x has been read out: the next item's first P V may overwrite it
+          tc_fence_before();
+          mbar_arrive(bar_oe);
+        }
+        if (row_valid) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 out;
+            out.x = pack2<T>(__uint_as_float(orow[v * 8 + 0]) * inv_l,
+                             __uint_as_float(orow[v * 8 + 1]) * inv_l);
+            out.y = pack2<T>(__uint_as_float(orow[v * 8 + 2]) * inv_l,
+                             __uint_as_float(orow[v * 8 + 3]) * inv_l);
+            out.z = pack2<T>(__uint_as_float(orow[v * 8 + 4]) * inv_l,
+                             __uint_as_float(orow[v * 8 + 5]) * inv_l);
+            out.w = pack2<T>(__uint_as_float(orow[v * 8 + 6]) * inv_l,
+                             __uint_as_float(orow[v * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(o_row + c * 32 + v * 8) = out;
+          }
+        }
+      }
+      if (row_valid && args.lse != nullptr) {
+        args.lse[(long long)b * args.lse_stride_b + (long long)h * args.lse_stride_h + q_idx] =
+            0.6931471805599453f * (m_used * args.scale_log2 + log2f(l_run));
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown --
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    __syncwarp();
+    tmem_dealloc<kTmemCols>(tmem_base);
+  }
+}
+
+}  // namespace tfb

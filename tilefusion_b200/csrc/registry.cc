@@ -6,7 +6,11 @@
 namespace tfb {
 
 namespace {
+// tile_q 128: one Q tile per CTA, two CTAs per SM (attn_fwd_kernel).
+// tile_q 256: two Q tiles per CTA, persistent, one CTA per SM (attn_fwd_pair_kernel).
 constexpr AttnVariant kAttnVariants[] = {
+    {TF_F16, 128, 256, 128, 1}, {TF_BF16, 128, 256, 128, 1},
+    {TF_F16, 64, 256, 128, 1},  {TF_BF16, 64, 256, 128, 1},
     {TF_F16, 128, 128, 128, 2}, {TF_BF16, 128, 128, 128, 2},
     {TF_F16, 64, 128, 128, 2},  {TF_BF16, 64, 128, 128, 2},
     {0, 0, 0, 0, 0},
@@ -18,22 +22,28 @@ constexpr int kDecodeStages = 3;
 const AttnVariant* attn_variants() { return kAttnVariants; }
 
 void plan_attn(const TfAttnDesc& d, int sm_count, TfAttnPlan* plan) {
-  (void)sm_count;
+  // Heuristic: a single Q tile cannot use the two-tile schedule, and a problem
+  // with fewer tile pairs than SMs fills more of the GPU with one tile per CTA.
+  const int64_t bh = (int64_t)d.batch * d.heads;
+  const int64_t pairs = bh * ((d.len_q + 255) / 256);
+  const int64_t singles = bh * ((d.len_q + 127) / 128);
+  const int want_tile_q = (d.len_q <= 128 || (pairs < sm_count && singles > pairs)) ? 128 : 256;
   const AttnVariant* best = nullptr;
+  const AttnVariant* hinted = nullptr;
   for (const AttnVariant* v = kAttnVariants; v->head_dim != 0; ++v) {
     if (v->dtype != d.dtype || v->head_dim != d.head_dim) continue;
+    if (v->tile_q == want_tile_q && best == nullptr) best = v;
     // A caller's tile hint wins when it names a compiled variant.
-    if (best == nullptr) best = v;
-    if (d.tile_q == v->tile_q && d.tile_kv == v->tile_kv) {
-      best = v;
-      break;
-    }
+    if (d.tile_q == v->tile_q && d.tile_kv == v->tile_kv && hinted == nullptr) hinted = v;
   }
+  if (hinted != nullptr) best = hinted;
   plan->tile_q = best->tile_q;
   plan->tile_kv = best->tile_kv;
   plan->ctas_per_sm = best->ctas_per_sm;
   const int64_t q_tiles = (d.len_q + best->tile_q - 1) / best->tile_q;
-  plan->grid = (int32_t)std::min<int64_t>(q_tiles * d.heads * d.batch, INT32_MAX);
+  int64_t grid = q_tiles * d.heads * d.batch;
+  if (best->tile_q == 256) grid = std::min<int64_t>(grid, std::max(1, sm_count));   // persistent
+  plan->grid = (int32_t)std::min<int64_t>(grid, INT32_MAX);
   // With both strides 1 (a single key or a single head dim) either reading
   // is valid; the row-contiguous one is kept.
   plan->k_mn_major = d.k_stride_d == 1 ? 0 : 1;
