@@ -91,14 +91,16 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     deps = sources + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [
         INCLUDE / "tilefusion_b200.h"
     ]
-    digest = _source_hash(deps, " ".join(NVCC_FLAGS))
+    # TF_NVCC_EXTRA: extra compiler flags (e.g. "-DTF_PAIR_EMU_PER8=3") for tuning runs.
+    extra = os.environ.get("TF_NVCC_EXTRA", "").split()
+    digest = _source_hash(deps, " ".join(NVCC_FLAGS + extra))
     if not force and _up_to_date(out, digest):
         return out
     with _BuildLock():
         if not force and _up_to_date(out, digest):
             return out
         tmp = out.with_suffix(".so.tmp")
-        cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "-shared", "-o", str(tmp)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *extra, f"-I{INCLUDE}", f"-I{CSRC}", "-shared", "-o", str(tmp)]
         if verbose:
             cmd += ["-Xptxas", "-v"]
         cmd += [str(s) for s in sources]

@@ -520,4 +520,11 @@ int tf_device_status(int32_t* code_out) {
 
 int tf_abi_version(void) { return 1; }
 
+#ifdef TF_PAIR_TRACE
+// Debug builds only: copies the phase trace of CTA 0 (3 roles x 1024 records).
+__attribute__((visibility("default"))) int tf_debug_pair_trace(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, tfb::g_pair_trace, sizeof(unsigned long long) * 9 * 1024);
+}
+#endif
+
 }  // extern "C"

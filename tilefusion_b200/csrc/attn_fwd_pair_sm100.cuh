@@ -31,6 +31,31 @@ constexpr int kPairThreads = 384;     // three warpgroups; warps 10-11 only dona
 constexpr int kPairRegsSoftmax = 200;
 constexpr int kPairRegsIssue = 96;
 constexpr int kPairStages = 5;
+// Tuning switches (overridable with -D at build time).
+#ifndef TF_PAIR_EMU_PER8
+#define TF_PAIR_EMU_PER8 0          // of every 8 exponentials, this many run on the FMA pipe
+#endif
+#ifndef TF_PAIR_SPLIT_P
+#define TF_PAIR_SPLIT_P 1           // publish P in two halves (first P.V MMAs start earlier)
+#endif
+#ifndef TF_PAIR_LD_OVERLAP
+#define TF_PAIR_LD_OVERLAP 0        // take the row maximum chunk by chunk while S is still loading
+#endif
+constexpr int kPairEmuPer8 = TF_PAIR_EMU_PER8;
+
+// Optional phase trace of CTA 0 (debug builds only, -DTF_PAIR_TRACE): one
+// thread per role appends (event, tile, clock) records to a device array.
+#ifdef TF_PAIR_TRACE
+__device__ unsigned long long g_pair_trace[9][1024];
+__device__ __forceinline__ void pair_trace(int role, int& n, int event, int tile) {
+  if (blockIdx.x == 0 && n < 1024)
+    g_pair_trace[role][n++] = ((unsigned long long)event << 56) | ((unsigned long long)(tile & 0xFFFF) << 40) |
+                              (clock64() & 0xFFFFFFFFFFull);
+}
+#define PAIR_TRACE(role, n, event, tile) pair_trace(role, n, event, tile)
+#else
+#define PAIR_TRACE(role, n, event, tile)
+#endif
 
 struct AttnPairArgs {
   AttnFwdArgs base;
@@ -54,9 +79,10 @@ struct AttnPairSmem {
   static constexpr int kBarPFull = 6;      // [2]
   static constexpr int kBarOFull = 8;      // [2]
   static constexpr int kBarOEmpty = 10;    // [2]
-  static constexpr int kBarKVFull = 12;    // [kPairStages]
-  static constexpr int kBarKVEmpty = 12 + kPairStages;
-  static constexpr int kNumBars = 12 + 2 * kPairStages;
+  static constexpr int kBarPFullHi = 12;   // [2]  second half of P (keys 64..127)
+  static constexpr int kBarKVFull = 14;    // [kPairStages]
+  static constexpr int kBarKVEmpty = 14 + kPairStages;
+  static constexpr int kNumBars = 14 + 2 * kPairStages;
   static constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 4;
   static constexpr int kBytes = kOffAbort + 4 + 1024;               // + slack for 1024-B alignment
@@ -111,7 +137,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kOffTmemSlot);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -120,6 +146,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(bar(S::kBarQEmpty + x), 1);
       mbar_init(bar(S::kBarSFull + x), 1);
       mbar_init(bar(S::kBarPFull + x), 128);
+      mbar_init(bar(S::kBarPFullHi + x), 128);
       mbar_init(bar(S::kBarOFull + x), 1);
       mbar_init(bar(S::kBarOEmpty + x), 128);
     }
@@ -205,7 +232,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     }
    } else if (warp == 8) {
     // =========================================================== MMA issuer ==
-    if (lane == 0) {
+    // The whole warp walks the schedule (uniform control flow, uniform
+    // operands); one elected lane executes the tcgen05 instructions.
+    {
+      const bool leader = elect_one();
       const uint32_t idesc_s = make_idesc(128, 128, kIsBf16, 0, args.k_mn_major);
       const uint32_t idesc_o = make_idesc(128, D, kIsBf16, 0, args.v_mn_major);
       uint32_t stage = 0, phase = 0;       // ring position of the next stage to consume
@@ -213,6 +243,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       uint32_t p_cnt[2] = {0, 0};          // P tiles consumed per Q tile
       uint32_t items_done[2] = {0, 0};     // epilogues awaited per Q tile
       bool ok = true;
+#ifdef TF_PAIR_TRACE
+      int tn = 0;
+#endif
 
       // Operand B addressing, in 16-byte units: MMA step k (16 elements along the
       // contraction) starts at (k >> 2) * step_hi + (k & 3) * step_lo.
@@ -226,6 +259,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t v_lbo = args.v_mn_major ? S::kBlockBytes : 16;
 
       auto issue_s = [&](int x, uint32_t k_smem) {
+        if (!leader) return;
         const uint32_t a0 = desc_lo(smem_base + S::kOffQ + x * S::kTileBytes, 16);
         const uint32_t b0 = desc_lo(k_smem, k_lbo);
 #pragma unroll
@@ -235,19 +269,22 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         umma_commit(bar(S::kBarSFull + x));
       };
-      auto issue_pv = [&](int x, uint32_t v_smem, bool accumulate) {
+      // O_x += P_x V for keys [64*half, 64*half + 64) of the tile.
+      auto issue_pv_half = [&](int x, int half, uint32_t v_smem, bool accumulate) {
+        if (!leader) return;
         const uint32_t b0 = desc_lo(v_smem, v_lbo);
 #pragma unroll
-        for (int k = 0; k < kAttnTile / 16; ++k) {
+        for (int kk = 0; kk < 4; ++kk) {
+          const int k = half * 4 + kk;
           umma_ts_lohi(tmem_base + 256 + x * 128, tmem_base + x * 128 + k * 8,
                        b0 + (k >> 2) * v_step_hi + (k & 3) * v_step_lo, kDescHiSw128, idesc_o,
                        accumulate || (k > 0));
         }
-        umma_commit(bar(S::kBarOFull + x));
+        if (half == 1) umma_commit(bar(S::kBarOFull + x));
       };
       // Waits for the next ring stage and returns its shared-memory address.
       auto next_stage = [&](uint32_t& smem_addr, uint32_t& stage_idx) -> bool {
-        if (!mbar_wait(bar(S::kBarKVFull + stage), phase, abort_flag, kPWaitKVFull)) return false;
+        if (!mbar_wait_warp(bar(S::kBarKVFull + stage), phase, abort_flag, kPWaitKVFull)) return false;
         smem_addr = smem_base + S::kOffKV + stage * S::kTileBytes;
         stage_idx = stage;
         if (++stage == kPairStages) {
@@ -265,7 +302,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         const int n = max(nx[0], nx[1]);
         for (int x = 0; x < 2 && ok; ++x) {
           if (nx[x] == 0) continue;
-          ok = mbar_wait(bar(S::kBarQFull + x), q_cnt[x] & 1, abort_flag, kPWaitQFull);
+          ok = mbar_wait_warp(bar(S::kBarQFull + x), q_cnt[x] & 1, abort_flag, kPWaitQFull);
           ++q_cnt[x];
         }
         if (!ok) break;
@@ -276,9 +313,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int x = 0; x < 2; ++x) {
           if (nx[x] == 0) continue;
           issue_s(x, k_smem);
-          if (nx[x] == 1) umma_commit(bar(S::kBarQEmpty + x));
+          if (leader && (nx[x] == 1)) umma_commit(bar(S::kBarQEmpty + x));
         }
-        umma_commit(bar(S::kBarKVEmpty + k_stage));
+        if (leader) umma_commit(bar(S::kBarKVEmpty + k_stage));
 
         for (int j = 0; ok && j < n; ++j) {
           ok = next_stage(v_smem, v_stage);
@@ -286,18 +323,24 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           bool have_k = false;
           for (int x = 0; x < 2 && ok; ++x) {
             if (j < nx[x]) {
-              ok = mbar_wait(bar(S::kBarPFull + x), p_cnt[x] & 1, abort_flag, kPWaitPFull);
+              ok = mbar_wait_warp(bar(S::kBarPFull + x), p_cnt[x] & 1, abort_flag, kPWaitPFull);
               if (!ok) break;
-              ++p_cnt[x];
               if (j == 0 && items_done[x] > 0) {
                 // the previous item's epilogue must have read O_x out of TMEM
-                ok = mbar_wait(bar(S::kBarOEmpty + x), (items_done[x] - 1) & 1, abort_flag, kPWaitOEmpty);
+                ok = mbar_wait_warp(bar(S::kBarOEmpty + x), (items_done[x] - 1) & 1, abort_flag, kPWaitOEmpty);
                 if (!ok) break;
               }
               tc_fence_after();
-              issue_pv(x, v_smem, j > 0);
+              PAIR_TRACE(8, tn, 10 + x, j);
+              issue_pv_half(x, 0, v_smem, j > 0);
+              ok = mbar_wait_warp(bar(S::kBarPFullHi + x), p_cnt[x] & 1, abort_flag, kPWaitPFull);
+              if (!ok) break;
+              ++p_cnt[x];
+              tc_fence_after();
+              PAIR_TRACE(8, tn, 12 + x, j);
+              issue_pv_half(x, 1, v_smem, true);
             }
-            if (x == 1) umma_commit(bar(S::kBarKVEmpty + v_stage));
+            if (leader && (x == 1)) umma_commit(bar(S::kBarKVEmpty + v_stage));
             if (j + 1 < nx[x]) {
               if (!have_k) {
                 ok = next_stage(k_smem, k_stage);
@@ -305,9 +348,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                 have_k = true;
               }
               issue_s(x, k_smem);
-              if (j + 2 == nx[x]) umma_commit(bar(S::kBarQEmpty + x));
+              PAIR_TRACE(8, tn, 14 + x, j);
+              if (leader && (j + 2 == nx[x])) umma_commit(bar(S::kBarQEmpty + x));
             }
-            if (x == 1 && have_k) umma_commit(bar(S::kBarKVEmpty + k_stage));
+            if (leader && (x == 1 && have_k)) umma_commit(bar(S::kBarKVEmpty + k_stage));
           }
         }
         for (int x = 0; x < 2; ++x)
@@ -324,10 +368,18 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
     const uint32_t col_s = x * 128, col_p = x * 128, col_o = 256 + x * 128;
     const uint32_t bar_s = bar(S::kBarSFull + x), bar_p = bar(S::kBarPFull + x);
+    const uint32_t bar_p_hi = bar(S::kBarPFullHi + x);
     const uint32_t bar_o = bar(S::kBarOFull + x), bar_oe = bar(S::kBarOEmpty + x);
     uint32_t s_cnt = 0;      // S tiles consumed
     uint32_t o_base = 0;     // PV completions of earlier items
     bool ok = true;
+#ifdef TF_PAIR_TRACE
+    int tn = 0;
+    const bool tracer = (lane == 0);
+#define SM_TRACE(event, tile) if (tracer) PAIR_TRACE(warp, tn, event, tile)
+#else
+#define SM_TRACE(event, tile)
+#endif
 
     for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
       int b, h, pair;
@@ -344,35 +396,48 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         if (!ok) break;
         ++s_cnt;
         tc_fence_after();
+        SM_TRACE(0, j);
 
-        uint32_t sr[4][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + col_s + c * 32, sr[c]);
-        tmem_wait_ld();
-
+        // Load S in four 32-column chunks; the row maximum of a chunk is taken
+        // while the next chunk is still in flight.
         const int kv0 = j * kAttnTile;
         const bool need_mask =
             (kv0 + kAttnTile > args.len_kv) || (args.causal && (kv0 + kAttnTile - 1 > q0));
-        if (need_mask) {
+        uint32_t sr[4][32];
+        float mx[4];
+#if TF_PAIR_LD_OVERLAP
+        tmem_ld32(t_lane + col_s, sr[0]);
+#else
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + col_s + c * 32, sr[c]);
+        tmem_wait_ld();
+        SM_TRACE(4, j);
+#endif
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#if TF_PAIR_LD_OVERLAP
+          tmem_wait_ld();
+          if (c + 1 < 4) tmem_ld32(t_lane + col_s + (c + 1) * 32, sr[c + 1]);
+#endif
+          if (need_mask) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int col = kv0 + c * 32 + i;
               const bool masked = (col >= args.len_kv) || (args.causal && col > q_idx);
               if (masked) sr[c][i] = 0xff800000u;  // -inf
             }
-        }
-
-        // row maximum with four independent chains
-        float mx[4];
+          }
+          float m0 = max3(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
+          float m1 = max3(__uint_as_float(sr[c][3]), __uint_as_float(sr[c][4]), __uint_as_float(sr[c][5]));
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          mx[c] = __uint_as_float(sr[c][0]);
-#pragma unroll
-          for (int i = 1; i < 32; ++i) mx[c] = fmaxf(mx[c], __uint_as_float(sr[c][i]));
+          for (int i = 6; i + 3 < 32; i += 4) {
+            m0 = max3(m0, __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+            m1 = max3(m1, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+          }
+          mx[c] = max3(m0, m1, fmaxf(__uint_as_float(sr[c][30]), __uint_as_float(sr[c][31])));
         }
         const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        SM_TRACE(1, j);
 
         const bool grow = (m_tile - m_used) * args.scale_log2 > kRescaleThreshold;
         if (__any_sync(0xffffffffu, grow)) {
@@ -390,33 +455,55 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
               uint32_t orow[16];
               tmem_ld16(t_lane + col_o + c * 16, orow);
               tmem_wait_ld();
+              const uint64_t alpha2 = f2_pack(alpha, alpha);
 #pragma unroll
-              for (int i = 0; i < 16; ++i)
-                orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+              for (int i = 0; i < 16; i += 2) {
+                float lo, hi;
+                f2_unpack(f2_mul(f2_pack(__uint_as_float(orow[i]), __uint_as_float(orow[i + 1])), alpha2), lo, hi);
+                orow[i] = __float_as_uint(lo);
+                orow[i + 1] = __float_as_uint(hi);
+              }
               tmem_st16(t_lane + col_o + c * 16, orow);
             }
           }
         }
 
+        // P = 2^(s*scale - m): kPairEmuPer8 of every 8 exponentials run on the FMA
+        // pipe, the rest on the MUFU.  P is published in two halves so that the
+        // first four P.V MMAs start while the second half is still being computed.
         const float m_scaled = m_used * args.scale_log2;
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint64_t scale2 = f2_pack(args.scale_log2, args.scale_log2);
+        const uint64_t negm2 = f2_pack(-m_scaled, -m_scaled);
+        uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};      // four packed (even, odd) partial row sums
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), args.scale_log2, -m_scaled));
-            const float p1 =
-                fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), args.scale_log2, -m_scaled));
-            ls[(i >> 1) & 3] += p0 + p1;
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2),
+                      x0, x1);
+            const float p0 = ((i & 7) < kPairEmuPer8) ? poly_exp2(x0) : fast_exp2(x0);
+            const float p1 = (((i + 1) & 7) < kPairEmuPer8) ? poly_exp2(x1) : fast_exp2(x1);
+            ls2[(i >> 1) & 3] = f2_add(ls2[(i >> 1) & 3], f2_pack(p0, p1));
             pk[i >> 1] = pack2<T>(p0, p1);
           }
           tmem_st16(t_lane + col_p + c * 16, pk);
+          if ((TF_PAIR_SPLIT_P && c == 1) || c == 3) {
+            tmem_wait_st();
+            tc_fence_before();
+            if (c == 1 || !TF_PAIR_SPLIT_P) mbar_arrive(bar_p);
+            if (c == 3) mbar_arrive(bar_p_hi);
+            SM_TRACE(2 + (c >> 1), j);
+          }
+        }
+        float ls[4];
+        {
+          float lo, hi;
+          f2_unpack(f2_add(f2_add(ls2[0], ls2[1]), f2_add(ls2[2], ls2[3])), lo, hi);
+          ls[0] = lo; ls[1] = hi; ls[2] = 0.f; ls[3] = 0.f;
         }
         l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar_p);
       }
       if (!ok) break;
 

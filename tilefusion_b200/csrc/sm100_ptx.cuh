@@ -87,6 +87,27 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   }
 }
 
+// True in exactly one lane of a converged warp.  Code that issues TMA or MMA
+// instructions runs warp-uniformly up to this predicate, which lets the
+// compiler keep addresses and descriptors in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// Bounded wait executed by a whole converged warp; the result is warp-uniform.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_flag, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, code)) != 0;
+}
+
 // --------------------------------------------------------------------- TMA --
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -331,6 +352,52 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Packed pairs of fp32 (sm_100 executes fma/add/mul on two lanes per instruction).
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// 2^x on the FMA pipe (no MUFU): round-to-nearest split x = n + f with
+// |f| <= 0.5, a degree-3 minimax polynomial for 2^f (relative error 7.5e-5),
+// and n added into the exponent field.  Inputs below -125 (masked scores)
+// return ~2^-125, which rounds to zero in 16-bit P and is negligible in the
+// fp32 row sum.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -125.0f);
+  const float t = x + 12582912.0f;        // 1.5 * 2^23: integer part lands in the low mantissa bits
+  const float f = x - (t - 12582912.0f);
+  float p = fmaf(f, 0.0551716648f, 0.2426111251f);
+  p = fmaf(p, f, 0.6932609677f);
+  p = fmaf(p, f, 0.9999280572f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
 template <typename T>
