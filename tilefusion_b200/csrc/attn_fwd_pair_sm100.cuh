@@ -33,7 +33,7 @@ constexpr int kPairRegsIssue = 96;
 constexpr int kPairStages = 5;
 // Tuning switches (overridable with -D at build time).
 #ifndef TF_PAIR_EMU_PER8
-#define TF_PAIR_EMU_PER8 0          // of every 8 exponentials, this many run on the FMA pipe
+#define TF_PAIR_EMU_PER8 2          // of every 8 exponentials, this many run on the FMA pipe
 #endif
 #ifndef TF_PAIR_SPLIT_P
 #define TF_PAIR_SPLIT_P 1           // publish P in two halves (first P.V MMAs start earlier)
@@ -483,8 +483,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
             float x0, x1;
             f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2),
                       x0, x1);
-            const float p0 = ((i & 7) < kPairEmuPer8) ? poly_exp2(x0) : fast_exp2(x0);
-            const float p1 = (((i + 1) & 7) < kPairEmuPer8) ? poly_exp2(x1) : fast_exp2(x1);
+            // element pairs (i, i+1) with (i & 7) < kPairEmuPer8 take the polynomial
+            float p0, p1;
+            if ((i & 7) < kPairEmuPer8) {
+              poly_exp2_x2(x0, x1, p0, p1);
+            } else {
+              p0 = fast_exp2(x0);
+              p1 = fast_exp2(x1);
+            }
             ls2[(i >> 1) & 3] = f2_add(ls2[(i >> 1) & 3], f2_pack(p0, p1));
             pk[i >> 1] = pack2<T>(p0, p1);
           }

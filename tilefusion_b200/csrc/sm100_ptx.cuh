@@ -67,6 +67,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase (never suspends the thread).
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
 // Bounded wait for the phase with the given parity.  `abort_flag` is a word in
 // shared memory that any thread of the CTA sets when its own wait gave up;
 // seeing it set ends this wait as well.  `code` identifies the wait site.
@@ -398,6 +413,26 @@ __device__ __forceinline__ float poly_exp2(float x) {
   p = fmaf(p, f, 0.6932609677f);
   p = fmaf(p, f, 0.9999280572f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+// poly_exp2 on a packed pair: the additions and the polynomial run as f32x2
+// instructions (three adds and three fused multiply-adds per pair).
+__device__ __forceinline__ void poly_exp2_x2(float x0, float x1, float& r0, float& r1) {
+  const uint64_t x2 = f2_pack(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
+  const uint64_t magic = f2_pack(12582912.0f, 12582912.0f);
+  const uint64_t neg_magic = f2_pack(-12582912.0f, -12582912.0f);
+  const uint64_t t2 = f2_add(x2, magic);
+  const uint64_t n2 = f2_add(t2, neg_magic);
+  // f = x - n  (as x + (-1) * n)
+  const uint64_t f2 = f2_fma(n2, f2_pack(-1.0f, -1.0f), x2);
+  uint64_t p2 = f2_fma(f2, f2_pack(0.0551716648f, 0.0551716648f), f2_pack(0.2426111251f, 0.2426111251f));
+  p2 = f2_fma(p2, f2, f2_pack(0.6932609677f, 0.6932609677f));
+  p2 = f2_fma(p2, f2, f2_pack(0.9999280572f, 0.9999280572f));
+  float p0, p1, t0, t1;
+  f2_unpack(p2, p0, p1);
+  f2_unpack(t2, t0, t1);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
 template <typename T>
