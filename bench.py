@@ -62,6 +62,22 @@ WORKLOADS["prefill_profile"] = dict(WORKLOADS["prefill_c2"], B=4)
 WORKLOADS["decode_profile"] = dict(WORKLOADS["decode_c3"], B=4)
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)   # earlier measurement on this pool
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant
+# kernel from the ncu captures summarised under profiles/, per (batch, head)
+# problem of the captured case; traffic grows in proportion to batch x heads,
+# so a launch is scaled by the problems it processes.
+NCU_TRAFFIC_PER_HEAD = {
+    # attn_fwd_pair_kernel, B4 H32 L2048 D128 fp16: 201.5 MB read + 43.2 MB written over 128 heads
+    ("prefill", 2048, 128): (201.5e6 + 43.2e6) / 128,
+    # decode_split_kernel, B4 H32 Lk8192 D128 fp16: 536.9 MB read + 3.8 MB written over 128 heads
+    ("decode", 8192, 128): (536.9e6 + 3.8e6) / 128,
+}
+
+
+def ncu_traffic(w, heads_in_launch):
+    per_head = NCU_TRAFFIC_PER_HEAD.get((w["kind"], w["L"], w["D"]))
+    return None if per_head is None else per_head * heads_in_launch
+
 
 def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
@@ -76,8 +92,9 @@ def torch_dtype(name):
     return {"fp16": torch.float16, "bf16": torch.bfloat16}[name]
 
 
-def prefill_flops(b, h, lq, lk, d):
-    return 4.0 * b * h * lq * lk * d
+def prefill_flops(b, h, lq, lk, d, causal=False):
+    pairs = lq * lk if not causal else sum(min(lk, r + 1) for r in range(lq))
+    return 4.0 * b * h * pairs * d
 
 
 def decode_bytes(b, h, lk, d):
@@ -191,11 +208,14 @@ def cpu_baseline(w, budget_s=12.0):
     t1 = cpu_attention_sample(w, 1, threads)
     total = w["B"] * w["H"]
     n = int(max(1, min(total, budget_s / max(t1, 1e-6))))
-    t = cpu_attention_sample(w, n, threads)
+    passes, t = 0, 0.0
+    while t < budget_s and passes < 64:        # whole passes until about budget_s of CPU work
+        t += cpu_attention_sample(w, n, threads)
+        passes += 1
     unit = "TFLOP/s" if w["kind"] == "prefill" else "GB/s"
-    return {"value": unit_per_head(w) * n / t, "unit": unit, "cores": threads, "kind": "port",
-            "sample": f"{n} of {total} (batch, head) problems of the workload, oracle fp32 torch expression, "
-                      f"{t:.2f} s"}
+    return {"value": unit_per_head(w) * n * passes / t, "unit": unit, "cores": threads, "kind": "port",
+            "sample": f"{passes} pass(es) over {n} of {total} (batch, head) problems of the workload, "
+                      f"oracle fp32 torch expression, {t:.1f} s"}
 
 
 def run_reference_arm(args, w, name):
@@ -233,10 +253,10 @@ def metric_name(w):
     return "prefill_tflops" if w["kind"] == "prefill" else "decode_hbm_gbs"
 
 
-def workload_config(w, name, n_gpus):
-    return {"workload": name, "batch_per_step": w["B"] * (n_gpus if w["scaling"] == "weak" else 1),
+def workload_config(w, name, n_gpus, causal=False):
+    return {"workload": name + ("+causal" if causal else ""), "batch_per_step": w["B"] * (n_gpus if w["scaling"] == "weak" else 1),
             "heads": w["H"], "len_q": w["L"] if w["kind"] == "prefill" else 1, "len_kv": w["L"],
-            "head_dim": w["D"], "causal": False, "softmax_scale": "1/sqrt(D)",
+            "head_dim": w["D"], "causal": bool(causal), "softmax_scale": "1/sqrt(D)",
             "sharding": ("batch x heads, no collective" if w["kind"] == "prefill" or w["scaling"] == "weak"
                          else "KV length + NCCL all-gather of (m,l,O) rows"),
             "l2": "inputs larger than L2 (126 MB); no flush between steps"}
@@ -283,15 +303,16 @@ def run_prefill(args, w, name, device, rank, world):
 
     lib = _cabi.lib()
     # local batch: weak scaling keeps B per rank; strong scaling splits batch x heads
+    causal = bool(getattr(args, "causal", False))
     if w["scaling"] == "weak":
         b_local, h_local = w["B"], w["H"]
-        total_units = prefill_flops(w["B"] * world, w["H"], w["L"], w["L"], w["D"])
+        total_units = prefill_flops(w["B"] * world, w["H"], w["L"], w["L"], w["D"], causal)
     else:
         from tilefusion_b200.shard import head_slice
 
         h0, h1 = head_slice(w["B"] * w["H"], rank, world)
         b_local, h_local = (h1 - h0), 1         # flattened heads as the batch axis
-        total_units = prefill_flops(w["B"], w["H"], w["L"], w["L"], w["D"])
+        total_units = prefill_flops(w["B"], w["H"], w["L"], w["L"], w["D"], causal)
     wl = dict(w, H=h_local, seed=w["seed"] + 1000 * rank)
     q, k, v = make_inputs(wl, device, b=b_local)
     o = torch.empty_like(q)
@@ -300,6 +321,7 @@ def run_prefill(args, w, name, device, rank, world):
     d.dtype = _cabi.TF_F16 if w["dtype"] == "fp16" else _cabi.TF_BF16
     d.batch, d.heads, d.len_q, d.len_kv, d.head_dim, d.head_dim_v = b_local, h_local, w["L"], w["L"], w["D"], w["D"]
     d.softmax_scale = scale
+    d.causal = int(causal)
     d.q_stride_b, d.q_stride_h, d.q_stride_l = q.stride(0), q.stride(1), q.stride(2)
     d.k_stride_b, d.k_stride_h, d.k_stride_l, d.k_stride_d = k.stride()
     d.v_stride_b, d.v_stride_h, d.v_stride_l, d.v_stride_d = v.stride()
@@ -316,12 +338,21 @@ def run_prefill(args, w, name, device, rank, world):
     secs = time_steps(step, args.steps, args.warmup, device, world, clocks)
     value = total_units * args.steps / secs / 1e12
     per_launch_s = secs / args.steps
-    local_flops = prefill_flops(b_local, h_local, w["L"], w["L"], w["D"])
+    local_flops = prefill_flops(b_local, h_local, w["L"], w["L"], w["D"], causal)
 
     pk = peaks()
-    roof = {"bound": "tensor", "achieved": local_flops / per_launch_s / 1e12, "peak": pk["bf16_tflops"],
-            "unit": "TFLOP/s", "frac": local_flops / per_launch_s / 1e12 / pk["bf16_tflops"],
-            "traffic": None, "kernel": "attn_fwd_kernel", "peak_source": pk["source"] + " (burst cuBLAS bf16)",
+    # A kernel timed alone in a short region is held against the burst cuBLAS figure;
+    # when the timed region is long enough to run into the power cap (seconds-long
+    # loops, sw_power_cap active) the sustained figure is the like-for-like peak.
+    sustained = ("sw_power_cap" in clocks[0]["reasons"] or secs > 0.5) and pk.get("bf16_tflops_sustained", 0) > 0
+    peak_tf = pk["bf16_tflops_sustained"] if sustained else pk["bf16_tflops"]
+    roof = {"bound": "tensor", "achieved": local_flops / per_launch_s / 1e12, "peak": peak_tf,
+            "unit": "TFLOP/s", "frac": local_flops / per_launch_s / 1e12 / peak_tf,
+            "traffic": ncu_traffic(w, b_local * h_local), "kernel": "attn_fwd_pair_kernel",
+            "algorithmic_bytes": 4.0 * b_local * h_local * w["L"] * w["D"] * 2,
+            "peak_source": pk["source"] + (" (sustained cuBLAS bf16, power-capped loop)" if sustained
+                                           else " (burst cuBLAS bf16)"),
+            "frac_of_burst": local_flops / per_launch_s / 1e12 / pk["bf16_tflops"],
             "frac_of_nominal_2250": local_flops / per_launch_s / 1e12 / 2250.0}
     if args.profile:
         return dict(value=value, unit="TFLOP/s", secs=secs, clocks=clocks[0], roofline=roof,
@@ -330,7 +361,7 @@ def run_prefill(args, w, name, device, rank, world):
     # parity spot check on one (b, h) against the oracle
     from oracle import attention_oracle as orc
 
-    ref, _ = orc.attention_fp32(q[0, 0].cpu(), k[0, 0].cpu(), v[0, 0].cpu(), scale)
+    ref, _ = orc.attention_fp32(q[0, 0].cpu(), k[0, 0].cpu(), v[0, 0].cpu(), scale, causal)
     parity = {"max_abs": orc.max_abs(o[0, 0].cpu(), ref), "rel_l2": orc.rel_l2(o[0, 0].cpu(), ref),
               "checked": "one (batch, head) of the timed output vs the fp32 oracle"}
 
@@ -343,7 +374,7 @@ def run_prefill(args, w, name, device, rank, world):
         dq = hq.to(device, non_blocking=True)
         dk = hk.to(device, non_blocking=True)
         dv = hv.to(device, non_blocking=True)
-        out = tilefusion.ops.flash_attention(dq, dk.transpose(-1, -2), dv, 0, 0, 0, 0, scale, False)
+        out = tilefusion.ops.flash_attention(dq, dk.transpose(-1, -2), dv, 0, 0, 0, 0, scale, causal)
         ho.copy_(out, non_blocking=True)
 
     e2e_secs = time_steps(e2e_step, e2e_steps, 3, device, world)
@@ -414,7 +445,8 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
     pk = peaks()
     ach = local_units * steps / secs / 1e9
     roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-            "frac": ach / pk["hbm_gbs"], "traffic": None, "kernel": "decode_split_kernel (+ combine)",
+            "frac": ach / pk["hbm_gbs"], "traffic": ncu_traffic(w, w["B"] * w["H"]) if not sharded else None,
+            "algorithmic_bytes": local_units, "kernel": "decode_split_kernel (+ combine)",
             "peak_source": pk["source"] + " (torch copy, read+write)", "frac_of_nominal_8000": ach / 8000.0}
     res = dict(value=value, unit="GB/s", secs=secs, clocks=clocks[0], roofline=roof,
                launches=launches_per_step * steps)
@@ -452,6 +484,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="tilefusion_b200", choices=["tilefusion_b200", "reference"])
     ap.add_argument("--workload", default="prefill_c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--causal", action="store_true",
+                    help="prefill workloads: mask key index > query index (FLOPs counted over unmasked pairs)")
     ap.add_argument("--no-secondary", action="store_true", help="skip the decode line and CPU baseline")
     ap.add_argument("--profile", action="store_true",
                     help="device-timed steps only (no end-to-end pass, parity check, decode line or CPU "
@@ -487,7 +521,7 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["secs"] / args.steps * 1e3,
         "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None,
         "dtype": "f16" if w["dtype"] == "fp16" else "bf16", "data": "synthetic",
-        "config": workload_config(w, args.workload, world),
+        "config": workload_config(w, args.workload, world, args.causal and w["kind"] == "prefill"),
         "value_per_gpu": res["value"] / world,
         "clocks": res["clocks"], "gpu_launches": res["launches"],
         "roofline": res["roofline"],
