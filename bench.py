@@ -403,14 +403,14 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
         wq = dict(w)
         q = make_inputs(dict(wq, L=128), device)[0]                # replicated Q (same seed on every rank)
         _, k, v = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), device, l=k1 - k0)
-        dec = ShardedDecoder(w["B"], w["H"], w["D"], q.dtype, device)
+        dec = ShardedDecoder(w["B"], w["H"], w["D"], q.dtype, device, transport=getattr(args, "transport", None))
 
         def step():
             dec(q, k, v, scale)
 
         total_units = decode_bytes(w["B"], w["H"], w["L"], w["D"])
         local_units = decode_bytes(w["B"], w["H"], k1 - k0, w["D"])
-        launches_per_step = 4      # split, local merge, (NCCL all-gather), gathered combine
+        launches_per_step = 3      # split, merge (+ peer scatter), combine; the nccl transport adds one collective
     else:
         q, k, v = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), device)
         o = torch.empty_like(q)
@@ -450,6 +450,8 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
             "peak_source": pk["source"] + " (torch copy, read+write)", "frac_of_nominal_8000": ach / 8000.0}
     res = dict(value=value, unit="GB/s", secs=secs, clocks=clocks[0], roofline=roof,
                launches=launches_per_step * steps)
+    if sharded:
+        res["transport"] = dec.transport
 
     if not sharded and not args.profile:
         from oracle import attention_oracle as orc
@@ -486,6 +488,8 @@ def main():
     ap.add_argument("--workload", default="prefill_c2", choices=sorted(WORKLOADS))
     ap.add_argument("--causal", action="store_true",
                     help="prefill workloads: mask key index > query index (FLOPs counted over unmasked pairs)")
+    ap.add_argument("--transport", default=None, choices=["p2p", "nccl"],
+                    help="KV-sharded decode: fused peer-memory gather (default) or NCCL all-gather")
     ap.add_argument("--no-secondary", action="store_true", help="skip the decode line and CPU baseline")
     ap.add_argument("--profile", action="store_true",
                     help="device-timed steps only (no end-to-end pass, parity check, decode line or CPU "
@@ -530,6 +534,8 @@ def main():
         line["e2e"] = res["e2e"]
     if "parity" in res:
         line["parity"] = res["parity"]
+    if "transport" in res:
+        line["config"]["transport"] = res["transport"]
 
     if not args.no_secondary and w["kind"] == "prefill":
         # the other half of the metric: decode GB/s (config 3 on one GPU per rank;
@@ -541,7 +547,7 @@ def main():
                           "value_per_gpu": dres["value"] / world,
                           "ms_per_step": dres["secs"] / max(10, min(args.steps, 50)) * 1e3,
                           "roofline": dres["roofline"], "clocks": dres["clocks"]}
-        for key in ("e2e", "parity"):
+        for key in ("e2e", "parity", "transport"):
             if key in dres:
                 line["decode"][key] = dres[key]
 

@@ -194,6 +194,37 @@ TF_EXPORT int tf_decode_gathered(const float* slots, int32_t n_ranks,
                                  int64_t o_stride_h, float* lse, void* stream);
 
 /*
+ * KV-sharded decode with the all-gather fused into the kernels (no library
+ * collective): tf_decode_partial_scatter is tf_decode_partial whose merge
+ * kernel stores its row straight into the gather buffer of EVERY rank through
+ * peer-mapped pointers and then raises a flag there; tf_decode_gathered_wait
+ * is tf_decode_gathered preceded by a bounded wait on those flags.  No
+ * counterpart in the reference (it has no multi-GPU code).
+ *
+ * `peer_table` is a device array of n_ranks pointers, entry p = base of rank
+ * p's symmetric buffer as mapped into this process (for example
+ * torch.distributed._symmetric_memory's buffer_ptrs_dev).  Rank r's row block
+ * lands at base + slot_offset_floats (the caller adds r * B*H*(D+2) and
+ * alternates two buffer halves between consecutive steps); the flag word of
+ * sender r is ((uint32_t*)(base + flag_offset_floats))[r] and receives `step`,
+ * which must grow by one per step.  One sharded decode may be in flight per
+ * device.  Plain peer stores and system-scope release/acquire only -- no TMA
+ * and no multicast touch peer memory.
+ */
+TF_EXPORT int tf_decode_partial_scatter(const void* q, const void* k, const void* v,
+                                        void* workspace, uint64_t workspace_bytes,
+                                        const TfDecodeDesc* desc, const void* peer_table,
+                                        int32_t rank, int32_t n_ranks,
+                                        int64_t slot_offset_floats, int64_t flag_offset_floats,
+                                        uint32_t step, void* stream);
+
+TF_EXPORT int tf_decode_gathered_wait(const float* slots, const uint32_t* flags,
+                                      int32_t n_ranks, uint32_t step, int32_t batch,
+                                      int32_t heads, int32_t head_dim, int32_t dtype, void* o,
+                                      int64_t o_stride_b, int64_t o_stride_h, float* lse,
+                                      void* stream);
+
+/*
  * Flash decoding for callers that cannot allocate device memory.  It has no
  * counterpart in the reference.
  *

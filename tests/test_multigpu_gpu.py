@@ -31,12 +31,17 @@ dist.init_process_group("nccl", device_id=dev)
 b, h, lk, d = 2, 4, 6000, 128
 q, k, v = orc.seeded_inputs(51, (b, h, 1, d), (b, h, lk, d), (b, h, lk, d), 1.0)
 k0, k1 = kv_slice(lk, rank, world)
-dec = ShardedDecoder(b, h, d, torch.float16, dev)
-for _ in range(2):      # twice: the gather buffer is reused between steps
-    o, lse = dec(q.to(dev), k[:, :, k0:k1].contiguous().to(dev), v[:, :, k0:k1].contiguous().to(dev))
 ref, lse_ref = orc.decode_fp32(q, k, v)
-assert orc.max_abs(o.cpu(), ref) <= 2e-2 and orc.rel_l2(o.cpu(), ref) <= 1e-3, "decode O"
-assert orc.max_abs(lse.cpu(), lse_ref) <= 1e-3, "decode LSE"
+qd, kd, vd = q.to(dev), k[:, :, k0:k1].contiguous().to(dev), v[:, :, k0:k1].contiguous().to(dev)
+for transport in ("p2p", "nccl"):
+    dec = ShardedDecoder(b, h, d, torch.float16, dev, transport=transport)
+    assert dec.transport == transport, (transport, getattr(dec, "transport_fallback_reason", ""))
+    for _ in range(5):      # several steps: gather areas and flags are reused between steps
+        o, lse = dec(qd, kd, vd)
+    assert orc.max_abs(o.cpu(), ref) <= 2e-2 and orc.rel_l2(o.cpu(), ref) <= 1e-3, "decode O " + transport
+    assert orc.max_abs(lse.cpu(), lse_ref) <= 1e-3, "decode LSE " + transport
+    torch.cuda.synchronize()
+    dist.barrier()
 # prefill sharded by heads: no collective
 n, l = 12, 384
 q2, k2, v2 = orc.seeded_inputs(52, (n, l, d), (n, l, d), (n, l, d), 0.5)

@@ -428,7 +428,77 @@ int tf_decode_combine(const float* part_o, const float* part_ml, int32_t n_parts
   a.lse = lse;
   a.out_part_o = out_part_o;
   a.out_part_ml = out_part_ml;
+  a.peer_bases = nullptr;
+  a.n_peers = a.my_rank = a.rows_total = 0;
+  a.scatter_offset = a.flag_offset = 0;
+  a.step = 0;
+  a.wait_flags = nullptr;
+  a.wait_n = 0;
+  a.wait_step = 0;
   return dispatch_combine(a, rows, head_dim, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int tf_decode_partial_scatter(const void* q, const void* k, const void* v, void* workspace,
+                              uint64_t workspace_bytes, const TfDecodeDesc* desc, const void* peer_table,
+                              int32_t rank, int32_t n_ranks, int64_t slot_offset_floats,
+                              int64_t flag_offset_floats, uint32_t step, void* stream) {
+  TfDecodePlan plan;
+  if (int rc = plan_and_check_decode(q, k, v, workspace, workspace_bytes, desc, &plan)) return rc;
+  if (peer_table == nullptr) return fail(TF_ERR_BAD_ARG, "peer_table is null");
+  if (n_ranks < 1 || n_ranks > 64 || rank < 0 || rank >= n_ranks)
+    return fail(TF_ERR_BAD_ARG, "rank %d / n_ranks %d out of range (at most 64 ranks)", rank, n_ranks);
+  if (slot_offset_floats < 0 || flag_offset_floats < 0) return fail(TF_ERR_BAD_ARG, "negative buffer offset");
+  const int rows = desc->batch * desc->heads;
+  const int D = desc->head_dim;
+  float* part_o = static_cast<float*>(workspace);
+  float* part_ml = part_o + (int64_t)rows * plan.num_splits * D;
+  if (int rc = dispatch_split(q, k, v, part_o, part_ml, desc, plan, static_cast<cudaStream_t>(stream))) return rc;
+  tfb::DecodeCombineArgs a{};
+  a.part_o = part_o;
+  a.part_ml = part_ml;
+  a.n_parts = plan.num_splits;
+  a.part_stride_o = D;
+  a.row_stride_o = (int64_t)plan.num_splits * D;
+  a.part_stride_ml = 2;
+  a.row_stride_ml = (int64_t)plan.num_splits * 2;
+  a.heads = desc->heads;
+  a.peer_bases = static_cast<float* const*>(peer_table);
+  a.n_peers = n_ranks;
+  a.my_rank = rank;
+  a.rows_total = rows;
+  a.scatter_offset = slot_offset_floats;
+  a.flag_offset = flag_offset_floats;
+  a.step = step;
+  return dispatch_combine(a, rows, D, desc->dtype, static_cast<cudaStream_t>(stream));
+}
+
+int tf_decode_gathered_wait(const float* slots, const uint32_t* flags, int32_t n_ranks, uint32_t step,
+                            int32_t batch, int32_t heads, int32_t head_dim, int32_t dtype, void* o,
+                            int64_t o_stride_b, int64_t o_stride_h, float* lse, void* stream) {
+  if (slots == nullptr || o == nullptr || flags == nullptr)
+    return fail(TF_ERR_BAD_ARG, "slots, flags and o must be non-null");
+  if (n_ranks < 1 || n_ranks > 64 || batch < 1 || heads < 1)
+    return fail(TF_ERR_BAD_ARG, "n_ranks (<= 64), batch and heads must be positive");
+  if (dtype != TF_F16 && dtype != TF_BF16) return fail(TF_ERR_UNSUPPORTED, "dtype code %d is not fp16 or bf16", dtype);
+  const int64_t rows = (int64_t)batch * heads;
+  const int64_t slot_floats = rows * (head_dim + 2);
+  tfb::DecodeCombineArgs a{};
+  a.part_o = slots;
+  a.part_ml = slots + rows * head_dim;
+  a.n_parts = n_ranks;
+  a.part_stride_o = slot_floats;
+  a.row_stride_o = head_dim;
+  a.part_stride_ml = slot_floats;
+  a.row_stride_ml = 2;
+  a.heads = heads;
+  a.o = o;
+  a.o_stride_b = o_stride_b;
+  a.o_stride_h = o_stride_h;
+  a.lse = lse;
+  a.wait_flags = flags;
+  a.wait_n = n_ranks;
+  a.wait_step = step;
+  return dispatch_combine(a, (int)rows, head_dim, dtype, static_cast<cudaStream_t>(stream));
 }
 
 int tf_decode(const void* q, const void* k, const void* v, void* o, float* lse, void* workspace,

@@ -371,7 +371,39 @@ struct DecodeCombineArgs {
   float* lse;              // [rows] or null
   float* out_part_o;       // merged partial [rows][D] or null
   float* out_part_ml;      // merged partial [rows][2]
+  // Fused all-gather over peer memory (merged form only).  When peer_bases is
+  // non-null the merged row is stored straight into the gather buffer of every
+  // rank (peer_bases[p] + scatter_offset floats; rows*D of O, then rows*2 of
+  // (m, l)), and the CTA that finishes last publishes `step` in word my_rank of
+  // every rank's flag array (peer_bases[p] + flag_offset floats).
+  float* const* peer_bases;
+  int n_peers;
+  int my_rank;
+  int rows_total;
+  long long scatter_offset;
+  long long flag_offset;
+  unsigned step;
+  // Final form only: wait until wait_flags[r] has reached wait_step for every r
+  // (the slots of all ranks have landed) before reading the partials.
+  const unsigned* wait_flags;
+  int wait_n;
+  unsigned wait_step;
 };
+
+// CTAs of the scatter kernel that have stored their rows (one sharded decode
+// may be in flight per device).
+__device__ unsigned int g_scatter_done = 0;
+
+enum CombineWaitCode { kWaitGatherFlag = 401 };
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 constexpr int kCombineGroups = 4;
 
@@ -389,6 +421,21 @@ __global__ void __launch_bounds__(D * kCombineGroups) decode_combine_kernel(cons
   const int n_threads = D * kCombineGroups;
   const float* ml = a.part_ml + (long long)row * a.row_stride_ml;
   const float* po = a.part_o + (long long)row * a.row_stride_o;
+
+  if (a.wait_flags != nullptr) {
+    // Bounded wait for the peers' stores (flags are written with release
+    // semantics after a system-scope fence on the sending GPU).
+    if (tid < a.wait_n) {
+      const unsigned long long t0 = global_timer_ns();
+      while ((int)(ld_acquire_sys(a.wait_flags + tid) - a.wait_step) < 0) {
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+          atomicCAS(&g_status_word, 0, (int)kWaitGatherFlag);
+          break;
+        }
+      }
+    }
+    __syncthreads();
+  }
 
   // pass 1: global maximum
   float m = -INFINITY;
@@ -420,7 +467,17 @@ __global__ void __launch_bounds__(D * kCombineGroups) decode_combine_kernel(cons
       o += s_red[q][d];
       lt += s_l[q];
     }
-    if (a.out_part_o != nullptr) {
+    if (a.peer_bases != nullptr) {
+      for (int p = 0; p < a.n_peers; ++p) {
+        float* base = a.peer_bases[p] + a.scatter_offset;
+        base[(long long)row * D + d] = o;
+        if (d == 0) {
+          float* mlp = base + (long long)a.rows_total * D + (long long)row * 2;
+          mlp[0] = m;
+          mlp[1] = lt;
+        }
+      }
+    } else if (a.out_part_o != nullptr) {
       a.out_part_o[(long long)row * D + d] = o;
       if (d == 0) {
         a.out_part_ml[(long long)row * 2 + 0] = m;
@@ -436,6 +493,21 @@ __global__ void __launch_bounds__(D * kCombineGroups) decode_combine_kernel(cons
         op[d] = __float2bfloat16_rn(val);
       }
       if (d == 0 && a.lse != nullptr) a.lse[row] = 0.6931471805599453f * (m + log2f(lt));
+    }
+  }
+  if (a.peer_bases != nullptr) {
+    // Publish: every CTA fences its peer stores; the last one to finish raises
+    // the flag on every rank and re-arms the counter for the next step.
+    __shared__ int s_last;
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(&g_scatter_done, 1u) == gridDim.x - 1) ? 1 : 0;
+    __syncthreads();
+    if (s_last) {
+      __threadfence_system();
+      if (tid < a.n_peers)
+        st_release_sys(reinterpret_cast<unsigned*>(a.peer_bases[tid] + a.flag_offset) + a.my_rank, a.step);
+      if (tid == 0) g_scatter_done = 0;
     }
   }
 }

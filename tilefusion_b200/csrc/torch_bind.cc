@@ -233,6 +233,38 @@ void flash_decoding_gathered(const at::Tensor& slots, at::Tensor& O, at::Tensor&
                                   LSE.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()));
 }
 
+void flash_decoding_partial_scatter(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V,
+                                    int64_t peer_table, int64_t rank, int64_t world, int64_t slot_offset,
+                                    int64_t flag_offset, int64_t step, int64_t kv_chunk, int64_t num_splits,
+                                    double softmax_scale) {
+  TfDecodeDesc d = decode_desc(Q, K, V, kv_chunk, num_splits, softmax_scale);
+  const c10::cuda::CUDAGuard guard(Q.device());
+  at::Tensor ws = decode_workspace(d, Q);
+  check_status(tf_decode_partial_scatter(Q.data_ptr(), K.data_ptr(), V.data_ptr(), ws.data_ptr(),
+                                         (uint64_t)ws.numel() * 4, &d, reinterpret_cast<const void*>(peer_table),
+                                         (int32_t)rank, (int32_t)world, slot_offset, flag_offset, (uint32_t)step,
+                                         at::cuda::getCurrentCUDAStream().stream()));
+}
+
+void flash_decoding_gathered_wait(const at::Tensor& slots, const at::Tensor& flags, int64_t step, at::Tensor& O,
+                                  at::Tensor& LSE) {
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kFloat && slots.is_contiguous() && slots.dim() == 2,
+              "slots must be a contiguous fp32 CUDA tensor [n_ranks, B*H*(D+2)]");
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.is_contiguous() &&
+                  flags.numel() >= slots.size(0),
+              "flags must be a contiguous int32 CUDA tensor with one word per rank");
+  TORCH_CHECK(O.is_cuda() && O.dim() == 4 && O.size(2) == 1 && O.stride(3) == 1, "O must be [B, H, 1, D]");
+  const int64_t B = O.size(0), H = O.size(1), D = O.size(3);
+  TORCH_CHECK(slots.size(1) == B * H * (D + 2), "slots has the wrong row length for O");
+  TORCH_CHECK(LSE.is_cuda() && LSE.scalar_type() == at::kFloat && LSE.is_contiguous() && LSE.numel() == B * H,
+              "LSE must be a contiguous fp32 CUDA tensor with B*H elements");
+  const c10::cuda::CUDAGuard guard(O.device());
+  check_status(tf_decode_gathered_wait(slots.data_ptr<float>(), reinterpret_cast<const uint32_t*>(flags.data_ptr<int>()),
+                                       (int32_t)slots.size(0), (uint32_t)step, (int32_t)B, (int32_t)H, (int32_t)D,
+                                       dtype_code(O), O.data_ptr(), O.stride(0), O.stride(1), LSE.data_ptr<float>(),
+                                       at::cuda::getCurrentCUDAStream().stream()));
+}
+
 TF_REGISTER_OP(flash_attention,
                "flash_attention(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, "
                "int tile_length_q, int tile_length_kv, "
@@ -258,6 +290,17 @@ TF_REGISTER_OP(flash_decoding_partial,
 TF_REGISTER_OP(flash_decoding_gathered,
                "flash_decoding_gathered(Tensor slots, Tensor(a!) O, Tensor(b!) LSE) -> ()",
                &flash_decoding_gathered);
+
+TF_REGISTER_OP(flash_decoding_partial_scatter,
+               "flash_decoding_partial_scatter(Tensor Q, Tensor K, Tensor V, int peer_table, int rank, int world, "
+               "int slot_offset, int flag_offset, int step, int kv_chunk, int num_splits, "
+               "float softmax_scale) -> ()",
+               &flash_decoding_partial_scatter);
+
+TF_REGISTER_OP(flash_decoding_gathered_wait,
+               "flash_decoding_gathered_wait(Tensor slots, Tensor flags, int step, Tensor(a!) O, "
+               "Tensor(b!) LSE) -> ()",
+               &flash_decoding_gathered_wait);
 
 }  // namespace
 
