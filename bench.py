@@ -60,6 +60,8 @@ WORKLOADS = {
 # exceed the 126 MB L2, but only a few hundred MB are held on the device.
 WORKLOADS["prefill_profile"] = dict(WORKLOADS["prefill_c2"], B=4)
 WORKLOADS["decode_profile"] = dict(WORKLOADS["decode_c3"], B=4)
+# One rank's share of decode_c4 when the KV length is sharded over 8 GPUs.
+WORKLOADS["decode_c4_shard8"] = dict(WORKLOADS["decode_c4"], L=131072 // 8, scaling="weak")
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)   # earlier measurement on this pool
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant
