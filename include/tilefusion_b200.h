@@ -136,6 +136,22 @@ TF_EXPORT int tf_attn_fwd(const void* q, const void* k, const void* v, void* o,
  */
 TF_EXPORT int tf_attn_plan(const TfAttnDesc* desc, TfAttnPlan* plan);
 
+/*
+ * D[m, p] = (A[m, k] * B[n, k]^T) * C[p, n]^T with the intermediate product
+ * rounded to the 16-bit dtype and fp32 accumulation in both products: the
+ * attention kernel with its softmax stage replaced by a conversion.  Replaces
+ * tilefusion::kernels::fused_two_gemms (include/kernels/ops.hpp:47-52,
+ * src/kernels/fused_two_gemms.cu:66-144; kernel
+ * include/kernels/fused_two_gemms_device.cuh:114-214) with the operand layouts
+ * of that operator: A and D row-major, B given as [n, k] and C as [p, n]
+ * ("column-major" B and C).  ld* are row strides in elements.  This variant
+ * requires k == p in {64, 128}; m and n are arbitrary.
+ */
+TF_EXPORT int tf_fused_two_gemms(const void* a, const void* b, const void* c, void* d,
+                                 int32_t m, int32_t n, int32_t k, int32_t p, int32_t dtype,
+                                 int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd,
+                                 void* stream);
+
 /* ---- flash decoding (no counterpart in the reference: it has no decode
  *      op; registered in the style of include/kernels/kernel_list.hpp:25-30) */
 

@@ -152,6 +152,16 @@ def decode_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     return attention_fp32(q, k, v, scale, causal=False)
 
 
+def fused_two_gemms_fp32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
+    """``(A @ B^T) @ C^T`` as TileFusion's test states it
+    (``tests/python/test_fused_two_gemms.py:100``: ``input_a @ input_b.t() @ input_c.t()``
+    on 16-bit tensors): fp32 accumulation, the intermediate product rounded to
+    the input dtype as a 16-bit matmul returns it.  a ``[M, K]``, b ``[N, K]``,
+    c ``[P, N]``; returns fp32 ``[M, P]`` (not rounded)."""
+    inter = (a.float() @ b.float().t()).to(a.dtype)
+    return inter.float() @ c.float().t()
+
+
 # ---------------------------------------------------------------- tolerances --
 def max_abs(a: torch.Tensor, b: torch.Tensor) -> float:
     return (a.float() - b.float()).abs().max().item()

@@ -173,7 +173,12 @@ def test_torch_operator_schema_matches_tilefusion():
                 "int tile_length_q, int tile_length_kv, int tile_hidden_qk, int tile_hidden_v, "
                 "float softmax_scale, bool causal) -> ()")
     assert schema == expected
-    for op in ("flash_attention_lse", "flash_decoding", "flash_decoding_partial", "flash_decoding_gathered"):
+    # include/kernels/kernel_list.hpp:20-23
+    assert str(torch.ops.tilefusion.fused_two_gemms.default._schema) == (
+        "tilefusion::fused_two_gemms(Tensor A, Tensor B, Tensor C, Tensor(a!) D, "
+        "int tm, int tn, int tk, int tp) -> ()")
+    for op in ("flash_attention_lse", "flash_decoding", "flash_decoding_partial", "flash_decoding_gathered",
+               "flash_decoding_partial_scatter", "flash_decoding_gathered_wait"):
         assert hasattr(torch.ops.tilefusion, op)
 
 

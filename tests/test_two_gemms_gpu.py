@@ -1,0 +1,69 @@
+"""fused_two_gemms (the attention kernel without its softmax) against the oracle.
+
+TileFusion's own test (tests/python/test_fused_two_gemms.py:55-108) draws
+N(0.05, 0.01) fp16 matrices of size M=256, N=128, K=64, P=64 and accepts
+allclose(rtol=1e-3, atol=1e-3) against ``input_a @ input_b.t() @ input_c.t()``;
+that case and tolerance are reproduced here, with more shapes beside it.
+"""
+
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _normal(shape, mean, std, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.normal(mean=torch.full(shape, mean), std=torch.full(shape, std), generator=g).to(dtype)
+
+
+def test_reference_case_through_python_api():
+    import tilefusion_b200 as tilefusion
+
+    m, n, k, p = 256, 128, 64, 64
+    a = _normal((m, k), 5e-2, 1e-2, torch.float16, 1).cuda()
+    b = _normal((n, k), 5e-2, 1e-2, torch.float16, 2).cuda()
+    c = _normal((p, n), 5e-2, 1e-2, torch.float16, 3).cuda()
+    out = torch.zeros(m, p, dtype=torch.float16, device="cuda")
+    tilefusion.ops.fused_two_gemms(a, b, c, out, 64, 64, 64, 64)
+    ref = orc.fused_two_gemms_fp32(a.cpu(), b.cpu(), c.cpu())
+    assert torch.allclose(out.float().cpu(), ref, rtol=1e-3, atol=1e-3)
+    # and against the 16-bit torch expression TileFusion's test uses, on the GPU
+    assert torch.allclose(out, a @ b.t() @ c.t(), rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("m,n,k,p", [(128, 128, 128, 128), (300, 200, 64, 64), (1, 1, 128, 128),
+                                     (1000, 1024, 128, 128), (64, 77, 64, 64)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+def test_shapes_through_cabi(m, n, k, p, dtype):
+    from cabi_helpers import device_status
+    from tilefusion_b200 import _cabi
+
+    if n % 8 != 0:
+        pytest.skip("C rows ([P, N]) must be 16-byte aligned for TMA: N a multiple of 8")
+    a = _normal((m, k), 0.0, 1.0, dtype, 4).cuda()
+    b = _normal((n, k), 0.0, 0.125, dtype, 5).cuda()
+    c = _normal((p, n), 0.0, 0.125, dtype, 6).cuda()
+    d = torch.full((m, p), float("nan"), dtype=dtype, device="cuda")
+    code = _cabi.TF_F16 if dtype == torch.float16 else _cabi.TF_BF16
+    rc = _cabi.lib().tf_fused_two_gemms(a.data_ptr(), b.data_ptr(), c.data_ptr(), d.data_ptr(), m, n, k, p, code,
+                                        a.stride(0), b.stride(0), c.stride(0), d.stride(0),
+                                        torch.cuda.current_stream().cuda_stream)
+    _cabi.check(rc)
+    ref = orc.fused_two_gemms_fp32(a.cpu(), b.cpu(), c.cpu())
+    assert torch.isfinite(d.float()).all()
+    # output rounding: 2^-11 (fp16) / 2^-8 (bf16) relative
+    tol = 1e-3 if dtype == torch.float16 else 4e-3
+    assert orc.rel_l2(d.cpu(), ref) <= tol
+    assert device_status() == 0
+
+
+def test_unsupported_widths_are_reported():
+    from tilefusion_b200 import _cabi
+
+    x = torch.zeros(64, 96, dtype=torch.float16, device="cuda")
+    rc = _cabi.lib().tf_fused_two_gemms(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), 64, 64, 96, 96,
+                                        _cabi.TF_F16, 96, 96, 96, 96, None)
+    assert rc == _cabi.TF_ERR_UNSUPPORTED and "k == p" in _cabi.lib().tf_last_error().decode()

@@ -29,7 +29,7 @@ EXPORTED = (
     "tf_decode_combine", "tf_decode", "tf_decode_partial", "tf_decode_gathered",
     "tf_last_error", "tf_device_status", "tf_abi_version",
     "tf_decode_static", "tf_decode_static_capacity",
-    "tf_decode_partial_scatter", "tf_decode_gathered_wait",
+    "tf_decode_partial_scatter", "tf_decode_gathered_wait", "tf_fused_two_gemms",
 )
 
 
@@ -115,6 +115,7 @@ def lib() -> C.CDLL:
     handle.tf_decode_partial_scatter.argtypes = [vp, vp, vp, vp, u64, C.POINTER(TfDecodeDesc), vp, i32, i32,
                                                  i64, i64, C.c_uint32, vp]
     handle.tf_decode_gathered_wait.argtypes = [fp, vp, i32, C.c_uint32, i32, i32, i32, i32, vp, i64, i64, fp, vp]
+    handle.tf_fused_two_gemms.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i64, vp]
     handle.tf_decode_static.argtypes = [vp, vp, vp, vp, fp, C.POINTER(TfDecodeDesc), vp]
     handle.tf_decode_static_capacity.argtypes = []
     handle.tf_last_error.restype = C.c_char_p

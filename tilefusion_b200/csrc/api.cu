@@ -191,6 +191,24 @@ int launch_attn(const AttnLaunch& L, const TfAttnDesc* d, cudaStream_t stream) {
   return TF_OK;
 }
 
+// fused_two_gemms: the one-tile kernel with the softmax stage replaced by a cast.
+template <typename T, int D>
+int launch_two_gemms(const AttnLaunch& L, const TfAttnDesc* d, cudaStream_t stream) {
+  using Smem = tfb::AttnSmem<D>;
+  auto kern = tfb::attn_fwd_kernel<T, D, true>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  TF_CUDA_TRY(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    TF_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
+    configured_device = dev;
+  }
+  dim3 grid((d->len_q + tfb::kAttnTile - 1) / tfb::kAttnTile, 1, 1);
+  kern<<<grid, tfb::kAttnThreads, Smem::kBytes, stream>>>(L.mq, L.mk, L.mv, L.args);
+  TF_CUDA_TRY(cudaGetLastError());
+  return TF_OK;
+}
+
 // Two Q tiles per CTA, persistent grid of one CTA per SM.
 template <typename T, int D>
 int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan& plan, cudaStream_t stream) {
@@ -384,6 +402,43 @@ int tf_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
                                  : run_attn<__nv_bfloat16, 128>(q, k, v, o, lse, desc, plan, s);
   return desc->dtype == TF_F16 ? run_attn<__half, 64>(q, k, v, o, lse, desc, plan, s)
                                : run_attn<__nv_bfloat16, 64>(q, k, v, o, lse, desc, plan, s);
+}
+
+int tf_fused_two_gemms(const void* a, const void* b, const void* c, void* d, int32_t m, int32_t n, int32_t k,
+                       int32_t p, int32_t dtype, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldd,
+                       void* stream) {
+  if (a == nullptr || b == nullptr || c == nullptr || d == nullptr)
+    return fail(TF_ERR_BAD_ARG, "a, b, c and d must be non-null");
+  if (m < 1 || n < 1 || k < 1 || p < 1) return fail(TF_ERR_BAD_ARG, "m, n, k and p must be positive");
+  if (dtype != TF_F16 && dtype != TF_BF16)
+    return fail(TF_ERR_UNSUPPORTED, "the inputs and output must be half-precision (fp16 or bf16); got dtype code %d", dtype);
+  if (k != p || (k != 64 && k != 128))
+    return fail(TF_ERR_UNSUPPORTED, "fused_two_gemms needs k == p in {64, 128} (got k=%d, p=%d)", k, p);
+  if (lda < k || ldb < k || ldc < n || ldd < p) return fail(TF_ERR_BAD_ARG, "a leading dimension is smaller than its row");
+  if (!aligned16(d) || ldd % 8 != 0) return fail(TF_ERR_UNSUPPORTED, "d must be 16-byte aligned with ldd a multiple of 8");
+  TfAttnDesc desc{};
+  desc.dtype = dtype;
+  desc.batch = desc.heads = 1;
+  desc.len_q = m;
+  desc.len_kv = n;
+  desc.head_dim = desc.head_dim_v = k;
+  desc.softmax_scale = 1.f;
+  desc.tile_q = 128;
+  desc.tile_kv = 128;
+  desc.q_stride_l = lda;
+  desc.k_stride_l = ldb;
+  desc.k_stride_d = 1;
+  desc.v_stride_d = ldc;      // C is stored [P, N]: the row-per-output-column form
+  desc.v_stride_l = 1;
+  desc.o_stride_l = ldd;
+  TfAttnPlan plan;
+  tfb::plan_attn(desc, sm_count(), &plan);
+  AttnLaunch L;
+  if (int rc = prepare_attn(a, b, c, d, nullptr, &desc, plan, &L)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (k == 128)
+    return dtype == TF_F16 ? launch_two_gemms<__half, 128>(L, &desc, s) : launch_two_gemms<__nv_bfloat16, 128>(L, &desc, s);
+  return dtype == TF_F16 ? launch_two_gemms<__half, 64>(L, &desc, s) : launch_two_gemms<__nv_bfloat16, 64>(L, &desc, s);
 }
 
 int tf_decode_plan(const TfDecodeDesc* desc, TfDecodePlan* plan) {

@@ -62,7 +62,12 @@ enum AttnWaitCode {
   kWaitSoftS = 111, kWaitSoftO = 112, kWaitEpiO = 113, kWaitDrain = 114
 };
 
-template <typename T, int D>
+// kNoSoftmax = true turns the kernel into TileFusion's fused_two_gemms
+// (include/kernels/fused_two_gemms_device.cuh:114-214): D = (A B^T) C^T with
+// the intermediate product rounded to 16 bits, i.e. the same two MMAs with the
+// softmax stage replaced by a conversion.  Q = A [M, K], K = B [N, K],
+// V = C stored [P, N], O = D [M, P]; K == P == the template's D.
+template <typename T, int D, bool kNoSoftmax = false>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
                 const __grid_constant__ CUtensorMap map_k,
@@ -261,6 +266,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + kColS + c * 32, sr[c]);
       tmem_wait_ld();
+
+      if constexpr (kNoSoftmax) {
+        // P = S rounded to 16 bits (columns beyond len_kv are zero: TMA zero-fills K)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            pk[i >> 1] = pack2<T>(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+          tmem_st16(t_lane + kColP + c * 16, pk);
+        }
+        l_run = 1.f;
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p);
+        continue;
+      }
 
       const int kv0 = j * kAttnTile;
       const bool need_mask =

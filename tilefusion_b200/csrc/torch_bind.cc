@@ -265,6 +265,28 @@ void flash_decoding_gathered_wait(const at::Tensor& slots, const at::Tensor& fla
                                        at::cuda::getCurrentCUDAStream().stream()));
 }
 
+// Same schema and operand conventions as TileFusion's fused_two_gemms
+// (include/kernels/kernel_list.hpp:20-23, src/kernels/fused_two_gemms.cu:66-144):
+// A [M, K] and D [M, P] row-major, B given as [N, K], C given as [P, N].
+void fused_two_gemms(const at::Tensor& A, const at::Tensor& B, const at::Tensor& C, at::Tensor& D, int64_t tm,
+                     int64_t tn, int64_t tk, int64_t tp) {
+  (void)tm; (void)tn; (void)tk; (void)tp;      // tile hints: the registry's tiles are used
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && C.is_cuda() && D.is_cuda(), "A, B, C and D must be CUDA tensors");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && C.dim() == 2 && D.dim() == 2, "A, B, C and D must be matrices");
+  TORCH_CHECK(A.scalar_type() == B.scalar_type() && A.scalar_type() == C.scalar_type() &&
+                  A.scalar_type() == D.scalar_type(),
+              "A, B, C and D must share one dtype");
+  TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && C.stride(1) == 1 && D.stride(1) == 1,
+              "rows of A, B, C and D must be contiguous");
+  const int64_t m = A.size(0), k = A.size(1), n = B.size(0), p = C.size(0);
+  TORCH_CHECK(B.size(1) == k && C.size(1) == n && D.size(0) == m && D.size(1) == p,
+              "expected A [M, K], B [N, K], C [P, N], D [M, P]");
+  const c10::cuda::CUDAGuard guard(A.device());
+  check_status(tf_fused_two_gemms(A.data_ptr(), B.data_ptr(), C.data_ptr(), D.data_ptr(), (int32_t)m, (int32_t)n,
+                                  (int32_t)k, (int32_t)p, dtype_code(A), A.stride(0), B.stride(0), C.stride(0),
+                                  D.stride(0), at::cuda::getCurrentCUDAStream().stream()));
+}
+
 TF_REGISTER_OP(flash_attention,
                "flash_attention(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, "
                "int tile_length_q, int tile_length_kv, "
@@ -301,6 +323,11 @@ TF_REGISTER_OP(flash_decoding_gathered_wait,
                "flash_decoding_gathered_wait(Tensor slots, Tensor flags, int step, Tensor(a!) O, "
                "Tensor(b!) LSE) -> ()",
                &flash_decoding_gathered_wait);
+
+TF_REGISTER_OP(fused_two_gemms,
+               "fused_two_gemms(Tensor A, Tensor B, Tensor C, Tensor(a!) D, "
+               "int tm, int tn, int tk, int tp) ->()",
+               &fused_two_gemms);
 
 }  // namespace
 

@@ -2,5 +2,6 @@
 
 from .flash_attention import FlashAttention, flash_attention
 from .flash_decoding import FlashDecoding, flash_decoding
+from .fused_two_gemms import fused_two_gemms
 
-__all__ = ["FlashAttention", "flash_attention", "FlashDecoding", "flash_decoding"]
+__all__ = ["FlashAttention", "flash_attention", "FlashDecoding", "flash_decoding", "fused_two_gemms"]
