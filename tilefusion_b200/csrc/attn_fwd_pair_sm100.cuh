@@ -38,9 +38,6 @@ constexpr int kPairStages = 5;
 #ifndef TF_PAIR_SPLIT_P
 #define TF_PAIR_SPLIT_P 1           // publish P in two halves (first P.V MMAs start earlier)
 #endif
-#ifndef TF_PAIR_LD_OVERLAP
-#define TF_PAIR_LD_OVERLAP 0        // take the row maximum chunk by chunk while S is still loading
-#endif
 constexpr int kPairEmuPer8 = TF_PAIR_EMU_PER8;
 
 // Optional phase trace of CTA 0 (debug builds only, -DTF_PAIR_TRACE): one
@@ -405,20 +402,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
             (kv0 + kAttnTile > args.len_kv) || (args.causal && (kv0 + kAttnTile - 1 > q0));
         uint32_t sr[4][32];
         float mx[4];
-#if TF_PAIR_LD_OVERLAP
-        tmem_ld32(t_lane + col_s, sr[0]);
-#else
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + col_s + c * 32, sr[c]);
         tmem_wait_ld();
         SM_TRACE(4, j);
-#endif
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-#if TF_PAIR_LD_OVERLAP
-          tmem_wait_ld();
-          if (c + 1 < 4) tmem_ld32(t_lane + col_s + (c + 1) * 32, sr[c + 1]);
-#endif
           if (need_mask) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {

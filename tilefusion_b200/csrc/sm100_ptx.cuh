@@ -67,21 +67,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Non-blocking test of a phase (never suspends the thread).
-__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-
 // Bounded wait for the phase with the given parity.  `abort_flag` is a word in
 // shared memory that any thread of the CTA sets when its own wait gave up;
 // seeing it set ends this wait as well.  `code` identifies the wait site.
@@ -400,23 +385,12 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
-// 2^x on the FMA pipe (no MUFU): round-to-nearest split x = n + f with
-// |f| <= 0.5, a degree-3 minimax polynomial for 2^f (relative error 7.5e-5),
-// and n added into the exponent field.  Inputs below -125 (masked scores)
-// return ~2^-125, which rounds to zero in 16-bit P and is negligible in the
-// fp32 row sum.
-__device__ __forceinline__ float poly_exp2(float x) {
-  x = fmaxf(x, -125.0f);
-  const float t = x + 12582912.0f;        // 1.5 * 2^23: integer part lands in the low mantissa bits
-  const float f = x - (t - 12582912.0f);
-  float p = fmaf(f, 0.0551716648f, 0.2426111251f);
-  p = fmaf(p, f, 0.6932609677f);
-  p = fmaf(p, f, 0.9999280572f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
-// poly_exp2 on a packed pair: the additions and the polynomial run as f32x2
-// instructions (three adds and three fused multiply-adds per pair).
+// 2^x on the FMA pipe (no MUFU) for a packed pair: round-to-nearest split
+// x = n + f with |f| <= 0.5 (adding 1.5 * 2^23 leaves n in the low mantissa
+// bits), a degree-3 minimax polynomial for 2^f (relative error 7.5e-5), and n
+// added into the exponent field.  Inputs below -125 (masked scores) return
+// ~2^-125, which rounds to zero in 16-bit P and is negligible in the fp32 row
+// sum.  The additions and the polynomial run as f32x2 instructions.
 __device__ __forceinline__ void poly_exp2_x2(float x0, float x1, float& r0, float& r1) {
   const uint64_t x2 = f2_pack(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
   const uint64_t magic = f2_pack(12582912.0f, 12582912.0f);
