@@ -56,6 +56,8 @@ WORKLOADS = {
     "decode_c4": dict(kind="decode", dtype="fp16", B=4, H=32, L=131072, D=128, seed=3, sigma=1.0,
                       scaling="strong"),
 }
+# Grouped-query decoding (beyond the reference's configs): 32 query heads on 8 KV heads.
+WORKLOADS["decode_gqa"] = dict(WORKLOADS["decode_c3"], B=64, Hkv=8)
 # Smaller cases of the same kernels for `ncu --set full` captures: inputs still
 # exceed the 126 MB L2, but only a few hundred MB are held on the device.
 WORKLOADS["prefill_profile"] = dict(WORKLOADS["prefill_c2"], B=4)
@@ -171,26 +173,43 @@ def make_inputs(w, device, b=None, l=None):
     g = torch.Generator(device=device).manual_seed(w["seed"])
     lq = l if w["kind"] == "prefill" else 1
     q = (torch.randn(b, w["H"], lq, w["D"], generator=g, device=device) * w["sigma"]).to(dt)
-    k = torch.empty(b, w["H"], l, w["D"], dtype=dt, device=device)
+    hkv = w.get("Hkv", w["H"])
+    k = torch.empty(b, hkv, l, w["D"], dtype=dt, device=device)
     v = torch.empty_like(k)
     for t in (k, v):            # per-batch draws keep the fp32 staging buffer small
         for i in range(b):
-            t[i] = (torch.randn(w["H"], l, w["D"], generator=g, device=device) * w["sigma"]).to(dt)
+            t[i] = (torch.randn(hkv, l, w["D"], generator=g, device=device) * w["sigma"]).to(dt)
     return q, k, v
 
 
 # -------------------------------------------------------------- CPU oracle ---
+_CPU_INPUTS = {}
+
+
+def cpu_inputs(w, n_heads):
+    """Seeded CPU inputs for `n_heads` (batch, head) problems (generated once, reused)."""
+    key = (w["kind"], w["L"], w["D"], w["dtype"], w["seed"], n_heads)
+    if key not in _CPU_INPUTS:
+        dt = torch_dtype(w["dtype"])
+        g = torch.Generator().manual_seed(w["seed"])
+        lq = w["L"] if w["kind"] == "prefill" else 1
+        _CPU_INPUTS.clear()
+        _CPU_INPUTS[key] = tuple(
+            (torch.randn(n_heads, rows, w["D"], generator=g) * w["sigma"]).to(dt) for rows in (lq, w["L"], w["L"]))
+    return _CPU_INPUTS[key]
+
+
+def cpu_heads_cap(w):
+    """Largest sample (in (batch, head) problems) whose K and V stay below 256 MiB each."""
+    return max(1, (256 << 20) // (w["L"] * w["D"] * 2))
+
+
 def cpu_attention_sample(w, n_heads, threads):
     """Times the fp32 torch expression on `n_heads` (b,h) problems of workload w."""
     from oracle import attention_oracle as orc
 
     torch.set_num_threads(threads)
-    dt = torch_dtype(w["dtype"])
-    g = torch.Generator().manual_seed(w["seed"])
-    lq = w["L"] if w["kind"] == "prefill" else 1
-    q = (torch.randn(n_heads, lq, w["D"], generator=g) * w["sigma"]).to(dt)
-    k = (torch.randn(n_heads, w["L"], w["D"], generator=g) * w["sigma"]).to(dt)
-    v = (torch.randn(n_heads, w["L"], w["D"], generator=g) * w["sigma"]).to(dt)
+    q, k, v = cpu_inputs(w, n_heads)
     scale = 1.0 / math.sqrt(w["D"])
     t0 = time.perf_counter()
     for i in range(n_heads):
@@ -201,7 +220,8 @@ def cpu_attention_sample(w, n_heads, threads):
 def unit_per_head(w):
     if w["kind"] == "prefill":
         return prefill_flops(1, 1, w["L"], w["L"], w["D"]) / 1e12      # TFLOP
-    return decode_bytes(1, 1, w["L"], w["D"]) / 1e9                    # GB
+    # GB of K+V per query head; query heads of a group share one KV head
+    return decode_bytes(1, 1, w["L"], w["D"]) * w.get("Hkv", w["H"]) / w["H"] / 1e9
 
 
 def cpu_baseline(w, budget_s=12.0):
@@ -209,9 +229,9 @@ def cpu_baseline(w, budget_s=12.0):
     t1 = cpu_attention_sample(w, 1, threads)        # also warms the thread pool
     t1 = cpu_attention_sample(w, 1, threads)
     total = w["B"] * w["H"]
-    n = int(max(1, min(total, budget_s / max(t1, 1e-6))))
+    n = int(max(1, min(total, cpu_heads_cap(w), budget_s / max(t1, 1e-6))))
     passes, t = 0, 0.0
-    while t < budget_s and passes < 64:        # whole passes until about budget_s of CPU work
+    while t < budget_s and passes < 4096:      # whole passes until about budget_s of CPU work
         t += cpu_attention_sample(w, n, threads)
         passes += 1
     unit = "TFLOP/s" if w["kind"] == "prefill" else "GB/s"
@@ -230,7 +250,7 @@ def run_reference_arm(args, w, name):
     t1 = cpu_attention_sample(w, 1, threads)
     total = w["B"] * w["H"]
     steps, warm = args.steps, max(args.warmup, 1)
-    n = int(max(1, min(total, 120.0 / max(t1 * (steps + warm), 1e-6))))
+    n = int(max(1, min(total, cpu_heads_cap(w), 120.0 / max(t1 * (steps + warm), 1e-6))))
     for _ in range(warm):
         cpu_attention_sample(w, n, threads)
     t0 = time.perf_counter()
@@ -437,8 +457,10 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
                 _cabi.check(rc)
 
         mult = world if w["scaling"] == "weak" else 1
-        total_units = decode_bytes(w["B"] * mult, w["H"], w["L"], w["D"])
-        local_units = decode_bytes(w["B"], w["H"], w["L"], w["D"])
+        hkv = w.get("Hkv", w["H"])
+        total_units = decode_bytes(w["B"] * mult, hkv, w["L"], w["D"])
+        local_units = decode_bytes(w["B"], hkv, w["L"], w["D"])
+        d.heads_kv = hkv
         launches_per_step = 2
 
     clocks = []
@@ -448,7 +470,8 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
     ach = local_units * steps / secs / 1e9
     roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
             "frac": ach / pk["hbm_gbs"], "traffic": ncu_traffic(w, w["B"] * w["H"]) if not sharded else None,
-            "algorithmic_bytes": local_units, "kernel": "decode_split_kernel (+ combine)",
+            "algorithmic_bytes": local_units, "kernel": ("attn_fwd_pair_kernel in split-KV mode (+ combine)" if "Hkv" in w
+                                                   else "decode_split_kernel (+ combine)"),
             "peak_source": pk["source"] + " (torch copy, read+write)", "frac_of_nominal_8000": ach / 8000.0}
     res = dict(value=value, unit="GB/s", secs=secs, clocks=clocks[0], roofline=roof,
                launches=launches_per_step * steps)
@@ -458,7 +481,9 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
     if not sharded and not args.profile:
         from oracle import attention_oracle as orc
 
-        ref, lse_ref = orc.decode_fp32(q[:1, :2].cpu(), k[:1, :2].cpu(), v[:1, :2].cpu(), scale)
+        grp = w["H"] // w.get("Hkv", w["H"])
+        ref, lse_ref = orc.decode_fp32(q[:1, :2].cpu(), k[:1, :1].cpu().expand(-1, 2, -1, -1) if grp > 1 else k[:1, :2].cpu(),
+                                       v[:1, :1].cpu().expand(-1, 2, -1, -1) if grp > 1 else v[:1, :2].cpu(), scale)
         res["parity"] = {"max_abs": orc.max_abs(o[:1, :2].cpu(), ref),
                          "lse_abs": orc.max_abs(lse[:1, :2].cpu(), lse_ref),
                          "checked": "two (batch, head) rows of the timed output vs the fp32 oracle"}

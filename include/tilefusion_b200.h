@@ -73,6 +73,9 @@ typedef struct TfAttnDesc {
 
 /*
  * Flash-decoding problem: one query row per (batch, head) against Lk keys.
+ * With heads_kv < heads (grouped-query attention) the query heads of a group
+ * are processed together on the tensor cores as the rows of one small
+ * attention problem per KV head, so K/V are still read from HBM once.
  * Q[B,H,D], K[B,H,Lk,D], V[B,H,Lk,D], O[B,H,D]; rows of K and V are
  * contiguous with stride D between consecutive keys.  Strides in elements.
  */
@@ -90,6 +93,12 @@ typedef struct TfDecodeDesc {
   int64_t k_stride_b, k_stride_h;
   int64_t v_stride_b, v_stride_h;
   int64_t o_stride_b, o_stride_h;
+  int32_t heads_kv;     /* KV heads; 0 or == heads: one KV head per query head.
+                           Otherwise grouped-query decoding: heads % heads_kv
+                           == 0, K/V are [B, heads_kv, Lk, D] (k/v_stride_h
+                           step over KV heads) and query head h reads KV head
+                           h / (heads / heads_kv).                            */
+  int32_t reserved;
 } TfDecodeDesc;
 
 /* What the registry chose for a decode problem (tf_decode_plan). */

@@ -57,6 +57,7 @@ def decode_desc(q, k, v, o=None, scale=None, kv_chunk=512, num_splits=0) -> _cab
     d = _cabi.TfDecodeDesc()
     d.dtype = _dtype_code(q)
     d.batch, d.heads = q.size(0), q.size(1)
+    d.heads_kv = k.size(1)
     d.len_kv = k.size(2)
     d.head_dim = q.size(3)
     d.kv_chunk, d.num_splits = kv_chunk, num_splits

@@ -22,13 +22,13 @@ def test_library_exports_every_declared_symbol(native_lib):
     assert sorted(declared) == sorted(_cabi.EXPORTED)
     for name in declared:
         assert hasattr(native_lib, name), f"{name} is declared but not exported"
-    assert native_lib.tf_abi_version() == 1
+    assert native_lib.tf_abi_version() == 2
 
 
 def test_struct_layouts_match_header():
     # field order and types are mirrored by hand; sizes catch a drift
     assert C.sizeof(_cabi.TfAttnDesc) == 12 * 4 + 14 * 8
-    assert C.sizeof(_cabi.TfDecodeDesc) == 8 * 4 + 8 * 8
+    assert C.sizeof(_cabi.TfDecodeDesc) == 8 * 4 + 8 * 8 + 2 * 4
     assert C.sizeof(_cabi.TfDecodePlan) == 6 * 4 + 8
     assert C.sizeof(_cabi.TfAttnPlan) == 6 * 4 + 8
     for struct, cname in [(_cabi.TfAttnDesc, "TfAttnDesc"), (_cabi.TfDecodeDesc, "TfDecodeDesc"),
@@ -133,6 +133,21 @@ def test_decode_plan_covers_every_key(native_lib, b, h, lk):
     if items >= 4 * plan.grid:
         span = -(-items // plan.grid) * plan.chunks_per_split
         assert span * plan.grid <= 1.02 * b * h * n_chunks + plan.grid * plan.chunks_per_split
+
+
+def test_grouped_query_decode_plan(native_lib):
+    d = _decode_desc(32, 32, 8192)
+    d.heads_kv = 8
+    plan = _cabi.TfDecodePlan()
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == 0
+    n_tiles = 8192 // 128
+    assert plan.kv_chunk == 128 and plan.num_splits * plan.chunks_per_split >= n_tiles
+    assert (plan.num_splits - 1) * plan.chunks_per_split < n_tiles
+    items = 32 * 8 * plan.num_splits
+    assert -(-items // 148) * plan.chunks_per_split <= 1.05 * 32 * 8 * n_tiles / 148 + plan.chunks_per_split
+    assert plan.workspace_bytes == 32 * 32 * plan.num_splits * 130 * 4
+    d.heads_kv = 5
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_BAD_ARG
 
 
 def test_decode_plan_honours_requested_splits(native_lib):

@@ -105,6 +105,40 @@ def test_empty_shard_contributes_nothing():
     _check(o, lse, ref, lse_ref, torch.float16)
 
 
+GQA_CASES = [
+    # B, Hq, Hkv, Lk, D
+    (2, 8, 2, 1000, 128),      # group of 4, ragged last tile
+    (1, 8, 1, 4096, 128),      # multi-query: all 8 heads share one KV head
+    (3, 6, 3, 130, 64),        # group of 2, D = 64
+    (2, 32, 8, 8192, 128),
+    (1, 16, 2, 1, 128),        # a single key
+]
+
+
+@pytest.mark.parametrize("case", GQA_CASES, ids=lambda c: "x".join(map(str, c)))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+def test_grouped_query_decode(case, dtype):
+    """Query heads that share a KV head (K/V are [B, H_kv, Lk, D])."""
+    from cabi_helpers import decode, device_status
+
+    b, hq, hkv, lk, d = case
+    q, k, v = orc.seeded_inputs(27, (b, hq, 1, d), (b, hkv, lk, d), (b, hkv, lk, d), 1.0, dtype)
+    o, lse = decode(q.cuda(), k.cuda(), v.cuda())
+    g = hq // hkv
+    ref, lse_ref = orc.decode_fp32(q, k.repeat_interleave(g, dim=1), v.repeat_interleave(g, dim=1))
+    _check(o, lse, ref, lse_ref, dtype)
+    assert device_status() == 0
+
+
+def test_grouped_query_python_api():
+    import tilefusion_b200 as tilefusion
+
+    q, k, v = orc.seeded_inputs(28, (2, 16, 1, 128), (2, 4, 3000, 128), (2, 4, 3000, 128), 1.0)
+    o, lse = tilefusion.ops.flash_decoding(q.cuda(), k.cuda(), v.cuda())
+    ref, lse_ref = orc.decode_fp32(q, k.repeat_interleave(4, dim=1), v.repeat_interleave(4, dim=1))
+    _check(o, lse, ref, lse_ref, torch.float16)
+
+
 def test_python_api_matches_oracle():
     import tilefusion_b200 as tilefusion
 

@@ -58,6 +58,7 @@ class TfDecodeDesc(C.Structure):
         ("k_stride_b", C.c_int64), ("k_stride_h", C.c_int64),
         ("v_stride_b", C.c_int64), ("v_stride_h", C.c_int64),
         ("o_stride_b", C.c_int64), ("o_stride_h", C.c_int64),
+        ("heads_kv", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

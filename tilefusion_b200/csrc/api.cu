@@ -7,6 +7,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -211,7 +212,9 @@ int launch_two_gemms(const AttnLaunch& L, const TfAttnDesc* d, cudaStream_t stre
 
 // Two Q tiles per CTA, persistent grid of one CTA per SM.
 template <typename T, int D>
-int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan& plan, cudaStream_t stream) {
+int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan& plan, cudaStream_t stream,
+                     int kv_splits = 0, int tiles_per_split = 0, float* part_o = nullptr,
+                     float* part_ml = nullptr) {
   using Smem = tfb::AttnPairSmem<D>;
   auto kern = tfb::attn_fwd_pair_kernel<T, D>;
   static thread_local int configured_device = -1;
@@ -226,8 +229,12 @@ int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan&
   a.heads = d->heads;
   a.batch = d->batch;
   a.n_pairs = (d->len_q + 2 * tfb::kAttnTile - 1) / (2 * tfb::kAttnTile);
-  a.n_items = d->batch * d->heads * a.n_pairs;
-  kern<<<plan.grid, tfb::kPairThreads, Smem::kBytes, stream>>>(L.mq, L.mk, L.mv, a);
+  a.n_items = d->batch * d->heads * a.n_pairs * (kv_splits > 0 ? kv_splits : 1);
+  a.kv_splits = kv_splits;
+  a.tiles_per_split = tiles_per_split;
+  a.part_o = part_o;
+  a.part_ml = part_ml;
+  kern<<<kv_splits > 0 ? std::min(plan.grid, a.n_items) : plan.grid, tfb::kPairThreads, Smem::kBytes, stream>>>(L.mq, L.mk, L.mv, a);
   TF_CUDA_TRY(cudaGetLastError());
   return TF_OK;
 }
@@ -255,6 +262,10 @@ int check_decode_desc(const TfDecodeDesc* d) {
   if (chunk < 128 || chunk % 128 != 0 || chunk > tfb::kDecMaxChunk)
     return fail(TF_ERR_UNSUPPORTED, "kv_chunk must be a multiple of 128 in [128, %d] (got %d)", tfb::kDecMaxChunk, chunk);
   if (d->num_splits < 0) return fail(TF_ERR_BAD_ARG, "num_splits must be >= 0");
+  if (d->heads_kv < 0 || (d->heads_kv > 0 && d->heads % d->heads_kv != 0))
+    return fail(TF_ERR_BAD_ARG, "heads (%d) must be a multiple of heads_kv (%d)", d->heads, d->heads_kv);
+  if (d->heads_kv > 0 && d->heads / d->heads_kv > 128)
+    return fail(TF_ERR_UNSUPPORTED, "at most 128 query heads per KV head");
   const int64_t s[] = {d->q_stride_b, d->q_stride_h, d->k_stride_b, d->k_stride_h,
                        d->v_stride_b, d->v_stride_h};
   for (int64_t x : s)
@@ -320,8 +331,53 @@ int dispatch_combine(const tfb::DecodeCombineArgs& a, int rows, int head_dim, in
   return fail(TF_ERR_UNSUPPORTED, "head_dim %d has no compiled variant (64 and 128 do)", head_dim);
 }
 
+// Grouped-query decoding: the query heads that share a KV head become the rows
+// of one attention problem per (batch, KV head), run by the two-tile kernel in
+// split-KV mode (tensor cores; K/V streamed once through its TMA ring).
+int launch_gqa_split(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
+                     const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream) {
+  if (d->len_kv < 1) return fail(TF_ERR_UNSUPPORTED, "grouped-query decoding needs at least one key per call");
+  const int group = d->heads / d->heads_kv;
+  const int D = d->head_dim;
+  TfAttnDesc ad{};
+  ad.dtype = d->dtype;
+  ad.batch = d->batch;
+  ad.heads = d->heads_kv;
+  ad.len_q = group;
+  ad.len_kv = d->len_kv;
+  ad.head_dim = ad.head_dim_v = D;
+  ad.softmax_scale = d->softmax_scale;
+  ad.tile_q = 256;
+  ad.tile_kv = 128;
+  ad.q_stride_b = d->q_stride_b;
+  ad.q_stride_h = (int64_t)group * d->q_stride_h;
+  ad.q_stride_l = d->q_stride_h;
+  ad.k_stride_b = d->k_stride_b;
+  ad.k_stride_h = d->k_stride_h;
+  ad.k_stride_l = D;
+  ad.k_stride_d = 1;
+  ad.v_stride_b = d->v_stride_b;
+  ad.v_stride_h = d->v_stride_h;
+  ad.v_stride_l = D;
+  ad.v_stride_d = 1;
+  ad.o_stride_l = D;      // unused in split-KV mode
+  TfAttnPlan ap;
+  tfb::plan_attn(ad, sm_count(), &ap);
+  ap.grid = plan.grid;
+  AttnLaunch L;
+  if (int rc = prepare_attn(q, k, v, part_o, nullptr, &ad, ap, &L)) return rc;
+  if (D == 128)
+    return d->dtype == TF_F16
+               ? launch_attn_pair<__half, 128>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml)
+               : launch_attn_pair<__nv_bfloat16, 128>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml);
+  return d->dtype == TF_F16
+             ? launch_attn_pair<__half, 64>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml)
+             : launch_attn_pair<__nv_bfloat16, 64>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml);
+}
+
 int dispatch_split(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
                    const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream) {
+  if (d->heads_kv > 0 && d->heads_kv != d->heads) return launch_gqa_split(q, k, v, part_o, part_ml, d, plan, stream);
   if (d->head_dim == 128)
     return d->dtype == TF_F16 ? launch_decode_split<__half, 128>(q, k, v, part_o, part_ml, d, plan, stream)
                               : launch_decode_split<__nv_bfloat16, 128>(q, k, v, part_o, part_ml, d, plan, stream);
@@ -643,7 +699,7 @@ int tf_device_status(int32_t* code_out) {
   return TF_OK;
 }
 
-int tf_abi_version(void) { return 1; }
+int tf_abi_version(void) { return 2; }
 
 #ifdef TF_PAIR_TRACE
 // Debug builds only: copies the phase trace of CTA 0 (3 roles x 1024 records).

@@ -58,8 +58,18 @@ struct AttnPairArgs {
   AttnFwdArgs base;
   int heads;
   int batch;
-  int n_pairs;        // ceil(len_q / 256)
-  int n_items;        // batch * heads * n_pairs
+  int n_pairs;          // ceil(len_q / 256)
+  int n_items;          // batch * heads * n_pairs * max(kv_splits, 1)
+  // Split-KV mode (kv_splits > 0; used for grouped-query decoding, where the
+  // "query rows" of a head are the query heads that share one KV head): an item
+  // covers KV tiles [split * tiles_per_split, ...), and instead of the final
+  // output it writes one partial row per (query row, split): D fp32 of
+  // normalised output to part_o and (log2-sum-exp, 1) to part_ml, in the layout
+  // decode_combine_kernel reads ([row][split], row = (b * heads + h) * len_q + q).
+  int kv_splits;
+  int tiles_per_split;
+  float* part_o;
+  float* part_ml;
 };
 
 template <int D>
@@ -93,7 +103,13 @@ enum AttnPairWaitCode {
 // Work item -> (batch, head, pair).  Non-causal items of one head are adjacent
 // (their K/V stay in L2); causal items are ordered heaviest pair first so that
 // the round-robin deal over CTAs is balanced.
-__device__ __forceinline__ void pair_item(const AttnPairArgs& a, int item, int& b, int& h, int& pair) {
+__device__ __forceinline__ void pair_item(const AttnPairArgs& a, int item, int& b, int& h, int& pair,
+                                          int& split) {
+  split = 0;
+  if (a.kv_splits > 0) {
+    split = item % a.kv_splits;
+    item /= a.kv_splits;
+  }
   int bh;
   if (a.base.causal) {
     const int n_bh = a.batch * a.heads;
@@ -107,11 +123,18 @@ __device__ __forceinline__ void pair_item(const AttnPairArgs& a, int item, int& 
   h = bh - b * a.heads;
 }
 
-// KV tiles visited by Q tile x (rows q0 .. q0+127) of a pair.
-__device__ __forceinline__ int kv_tiles_for(const AttnFwdArgs& a, int q0) {
+// Number of KV tiles visited by Q tile x (rows q0 .. q0+127) of a pair; the
+// first one is tile `first` (non-zero only in split-KV mode).
+__device__ __forceinline__ int kv_tiles_for(const AttnPairArgs& p, int q0, int split, int& first) {
+  const AttnFwdArgs& a = p.base;
+  first = 0;
   if (q0 >= a.len_q) return 0;
   int n = (a.len_kv + kAttnTile - 1) / kAttnTile;
   if (a.causal) n = min(n, q0 / kAttnTile + 1);
+  if (p.kv_splits > 0) {
+    first = split * p.tiles_per_split;
+    n = max(0, min(p.tiles_per_split, n - first));
+  }
   return n;
 }
 
@@ -176,10 +199,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       uint32_t q_uses[2] = {0, 0};        // loads issued so far into Q buffer x
       bool ok = true;
       for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
-        int b, h, pair;
-        pair_item(pargs, item, b, h, pair);
+        int b, h, pair, split, j0, j0_unused;
+        pair_item(pargs, item, b, h, pair, split);
         const int q0 = pair * 2 * kAttnTile;
-        const int n0 = kv_tiles_for(args, q0), n1 = kv_tiles_for(args, q0 + kAttnTile);
+        const int n0 = kv_tiles_for(pargs, q0, split, j0);          // tile 0 always exists; it sets j0
+        const int n1 = kv_tiles_for(pargs, q0 + kAttnTile, split, j0_unused);
         const int n = max(n0, n1);
         for (int x = 0; x < 2 && ok; ++x) {
           if ((x == 0 ? n0 : n1) == 0) continue;
@@ -206,12 +230,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
               // rows = keys, 64 head-dim elements per swizzle block
 #pragma unroll
               for (int blk = 0; blk < kBlocks; ++blk)
-                tma_load_4d(dst + blk * S::kBlockBytes, map, full, blk * 64, j * kAttnTile, h, b);
+                tma_load_4d(dst + blk * S::kBlockBytes, map, full, blk * 64, (j0 + j) * kAttnTile, h, b);
             } else {
               // rows = head dim, 64 keys per swizzle block
 #pragma unroll
               for (int blk = 0; blk < 2; ++blk)
-                tma_load_4d(dst + blk * (D * 128), map, full, j * kAttnTile + blk * 64, 0, h, b);
+                tma_load_4d(dst + blk * (D * 128), map, full, (j0 + j) * kAttnTile + blk * 64, 0, h, b);
             }
             if (++stage == kPairStages) {
               stage = 0;
@@ -292,10 +316,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       };
 
       for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
-        int b, h, pair;
-        pair_item(pargs, item, b, h, pair);
+        int b, h, pair, split, j0_unused;
+        pair_item(pargs, item, b, h, pair, split);
         const int q0 = pair * 2 * kAttnTile;
-        const int nx[2] = {kv_tiles_for(args, q0), kv_tiles_for(args, q0 + kAttnTile)};
+        const int nx[2] = {kv_tiles_for(pargs, q0, split, j0_unused),
+                           kv_tiles_for(pargs, q0 + kAttnTile, split, j0_unused)};
         const int n = max(nx[0], nx[1]);
         for (int x = 0; x < 2 && ok; ++x) {
           if (nx[x] == 0) continue;
@@ -379,10 +404,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
 #endif
 
     for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
-      int b, h, pair;
-      pair_item(pargs, item, b, h, pair);
+      int b, h, pair, split, j0;
+      pair_item(pargs, item, b, h, pair, split);
       const int q0 = pair * 2 * kAttnTile + x * kAttnTile;
-      const int n_kv = kv_tiles_for(args, q0);
+      const int n_kv = kv_tiles_for(pargs, q0, split, j0);
       if (n_kv == 0) continue;
       const int q_idx = q0 + row;
       float m_used = -INFINITY;
@@ -397,7 +422,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
 
         // Load S in four 32-column chunks; the row maximum of a chunk is taken
         // while the next chunk is still in flight.
-        const int kv0 = j * kAttnTile;
+        const int kv0 = (j0 + j) * kAttnTile;
         const bool need_mask =
             (kv0 + kAttnTile > args.len_kv) || (args.causal && (kv0 + kAttnTile - 1 > q0));
         uint32_t sr[4][32];
@@ -509,6 +534,34 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       tc_fence_after();
       const float inv_l = 1.0f / l_run;
       const bool row_valid = q_idx < args.len_q;
+      if (pargs.kv_splits > 0) {
+        // split-KV mode: one fp32 partial row (normalised O, log2-sum-exp) per split
+        const long long prow =
+            (((long long)b * pargs.heads + h) * args.len_q + q_idx) * pargs.kv_splits + split;
+        float* p_row = pargs.part_o + prow * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t orow[32];
+          tmem_ld32(t_lane + col_o + c * 32, orow);
+          tmem_wait_ld();
+          if (c == D / 32 - 1) {
+            tc_fence_before();
+            mbar_arrive(bar_oe);
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<float4*>(p_row + c * 32 + v * 4) =
+                  make_float4(__uint_as_float(orow[v * 4 + 0]) * inv_l, __uint_as_float(orow[v * 4 + 1]) * inv_l,
+                              __uint_as_float(orow[v * 4 + 2]) * inv_l, __uint_as_float(orow[v * 4 + 3]) * inv_l);
+          }
+        }
+        if (row_valid) {
+          pargs.part_ml[prow * 2 + 0] = m_used * args.scale_log2 + log2f(l_run);
+          pargs.part_ml[prow * 2 + 1] = 1.0f;
+        }
+        continue;
+      }
       T* o_row = reinterpret_cast<T*>(args.o) + (long long)b * args.o_stride_b +
                  (long long)h * args.o_stride_h + (long long)q_idx * args.o_stride_l;
 #pragma unroll

@@ -52,6 +52,39 @@ void plan_attn(const TfAttnDesc& d, int sm_count, TfAttnPlan* plan) {
 }
 
 void plan_decode(const TfDecodeDesc& d, int sm_count, TfDecodePlan* plan) {
+  if (d.heads_kv > 0 && d.heads_kv != d.heads) {
+    // Grouped-query decoding runs on the two-tile attention kernel in split-KV
+    // mode: work item = (batch, KV head, split), a split walks whole 128-key
+    // tiles.  Enough splits for about two items per SM, never an empty one.
+    const int64_t groups = (int64_t)d.batch * d.heads_kv;
+    const int n_tiles = std::max(1, (d.len_kv + 127) / 128);
+    const int grid = std::max(1, sm_count);
+    int want = d.num_splits;
+    if (want <= 0) {
+      // Items are dealt round-robin to one persistent CTA per SM; take the fewest
+      // splits whose makespan ceil(items / grid) * tiles_per_split is within 3 %
+      // of the best over all split counts (fewer partial rows to combine).
+      auto span = [&](int splits) {
+        const int t = (n_tiles + splits - 1) / splits;
+        const int64_t items = groups * ((n_tiles + t - 1) / t);
+        return ((items + grid - 1) / grid) * (int64_t)t;
+      };
+      int64_t best = INT64_MAX;
+      for (int sp = 1; sp <= n_tiles; ++sp) best = std::min(best, span(sp));
+      want = 1;
+      while (want < n_tiles && span(want) * 100 > best * 103) ++want;
+    }
+    const int tps = (n_tiles + want - 1) / want;
+    const int splits = (n_tiles + tps - 1) / tps;
+    plan->num_splits = splits;
+    plan->chunks_per_split = tps;
+    plan->kv_chunk = 128;
+    plan->grid = (int32_t)std::min<int64_t>(grid, groups * splits);
+    plan->stages = 5;
+    plan->reserved = 0;
+    plan->workspace_bytes = (uint64_t)d.batch * d.heads * splits * (d.head_dim + 2) * sizeof(float);
+    return;
+  }
   const int chunk = d.kv_chunk == 0 ? 512 : d.kv_chunk;
   const int64_t bh = (int64_t)d.batch * d.heads;
   const int n_chunks = std::max(1, (d.len_kv + chunk - 1) / chunk);

@@ -156,9 +156,9 @@ TfDecodeDesc decode_desc(const at::Tensor& Q, const at::Tensor& K, const at::Ten
   TORCH_CHECK(Q.dim() == 4 && K.dim() == 4 && V.dim() == 4,
               "Q must be [B, H, 1, D] and K, V must be [B, H, Lk, D]");
   TORCH_CHECK(Q.size(2) == 1, "flash_decoding takes one query row per (batch, head)");
-  TORCH_CHECK(K.sizes() == V.sizes() && K.size(0) == Q.size(0) && K.size(1) == Q.size(1) &&
-                  K.size(3) == Q.size(3),
-              "K and V must be [B, H, Lk, D] matching Q");
+  TORCH_CHECK(K.sizes() == V.sizes() && K.size(0) == Q.size(0) && K.size(3) == Q.size(3) && K.size(1) >= 1 &&
+                  Q.size(1) % K.size(1) == 0,
+              "K and V must be [B, H_kv, Lk, D] with H_kv dividing Q's head count");
   TORCH_CHECK(Q.scalar_type() == K.scalar_type() && Q.scalar_type() == V.scalar_type(),
               "Q, K and V must share one dtype");
   TORCH_CHECK(Q.stride(3) == 1 && K.stride(3) == 1 && V.stride(3) == 1 &&
@@ -168,6 +168,7 @@ TfDecodeDesc decode_desc(const at::Tensor& Q, const at::Tensor& K, const at::Ten
   d.dtype = dtype_code(Q);
   d.batch = (int32_t)Q.size(0);
   d.heads = (int32_t)Q.size(1);
+  d.heads_kv = (int32_t)K.size(1);
   d.len_kv = (int32_t)K.size(2);
   d.head_dim = (int32_t)Q.size(3);
   d.kv_chunk = (int32_t)kv_chunk;
