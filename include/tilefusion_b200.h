@@ -98,7 +98,18 @@ typedef struct TfDecodeDesc {
                            == 0, K/V are [B, heads_kv, Lk, D] (k/v_stride_h
                            step over KV heads) and query head h reads KV head
                            h / (heads / heads_kv).                            */
-  int32_t reserved;
+  int32_t page_size;    /* paged KV cache: keys per page, a multiple of 128;
+                           0 = K/V are contiguous per (batch, KV head)        */
+  const int32_t* block_table; /* device pointer, [batch][max_pages]: page holding
+                           keys [i*page_size, (i+1)*page_size) of a batch entry;
+                           used only when page_size > 0                       */
+  int32_t max_pages;    /* row length of block_table                          */
+  int32_t num_pages;    /* pages in the pool (extent of K and V)              */
+  int64_t k_stride_page, v_stride_page; /* elements between consecutive pages;
+                           with paging K/V are [num_pages][H_kv][page_size][D]
+                           addressed by (k/v_stride_page, k/v_stride_h) and
+                           k/v_stride_b are ignored.  Rows of a sequence's last
+                           page beyond len_kv must hold finite values.        */
 } TfDecodeDesc;
 
 /* What the registry chose for a decode problem (tf_decode_plan). */

@@ -22,13 +22,13 @@ def test_library_exports_every_declared_symbol(native_lib):
     assert sorted(declared) == sorted(_cabi.EXPORTED)
     for name in declared:
         assert hasattr(native_lib, name), f"{name} is declared but not exported"
-    assert native_lib.tf_abi_version() == 2
+    assert native_lib.tf_abi_version() == 3
 
 
 def test_struct_layouts_match_header():
     # field order and types are mirrored by hand; sizes catch a drift
     assert C.sizeof(_cabi.TfAttnDesc) == 12 * 4 + 14 * 8
-    assert C.sizeof(_cabi.TfDecodeDesc) == 8 * 4 + 8 * 8 + 2 * 4
+    assert C.sizeof(_cabi.TfDecodeDesc) == 8 * 4 + 8 * 8 + 2 * 4 + 8 + 2 * 4 + 2 * 8
     assert C.sizeof(_cabi.TfDecodePlan) == 6 * 4 + 8
     assert C.sizeof(_cabi.TfAttnPlan) == 6 * 4 + 8
     for struct, cname in [(_cabi.TfAttnDesc, "TfAttnDesc"), (_cabi.TfDecodeDesc, "TfDecodeDesc"),
@@ -40,7 +40,7 @@ def test_struct_layouts_match_header():
             decl = decl.strip()
             if not decl:
                 continue
-            decl = re.sub(r"^(u?int\d+_t|float)\s+", "", decl)
+            decl = re.sub(r"^(const\s+)?(u?int\d+_t|float)\s*\*?\s*", "", decl)
             names += [n.strip() for n in decl.split(",")]
         assert names == [f[0] for f in struct._fields_], cname
 

@@ -139,6 +139,43 @@ def test_grouped_query_python_api():
     _check(o, lse, ref, lse_ref, torch.float16)
 
 
+def _paginate(k, v, page_size, seed):
+    """Scatters contiguous K/V [B, H, Lk, D] into a shuffled page pool; returns
+    (k_pages, v_pages, block_table).  Unused rows of the last page are zero."""
+    b, h, lk, d = k.shape
+    per_seq = -(-lk // page_size)
+    n_pages = b * per_seq + 3                        # a few pages nobody uses
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g)[: b * per_seq].view(b, per_seq)
+    kp = torch.zeros(n_pages, h, page_size, d, dtype=k.dtype)
+    vp = torch.zeros_like(kp)
+    for bi in range(b):
+        for i in range(per_seq):
+            n = min(page_size, lk - i * page_size)
+            kp[perm[bi, i], :, :n] = k[bi, :, i * page_size:i * page_size + n]
+            vp[perm[bi, i], :, :n] = v[bi, :, i * page_size:i * page_size + n]
+    return kp, vp, perm.to(torch.int32)
+
+
+@pytest.mark.parametrize("case", [
+    # B, Hq, Hkv, Lk, D, page_size
+    (2, 4, 4, 1000, 128, 256),      # MHA, ragged last page
+    (3, 4, 4, 4096, 128, 512),
+    (2, 8, 2, 1500, 128, 128),      # grouped-query, one tile per page
+    (2, 8, 2, 3000, 64, 1024),
+], ids=lambda c: "x".join(map(str, c)))
+def test_paged_kv_cache(case):
+    import tilefusion_b200 as tilefusion
+
+    b, hq, hkv, lk, d, page = case
+    q, k, v = orc.seeded_inputs(29, (b, hq, 1, d), (b, hkv, lk, d), (b, hkv, lk, d), 1.0)
+    kp, vp, table = _paginate(k, v, page, 5)
+    o, lse = tilefusion.ops.flash_decoding(q.cuda(), kp.cuda(), vp.cuda(), block_table=table.cuda(), kv_len=lk)
+    g = hq // hkv
+    ref, lse_ref = orc.decode_fp32(q, k.repeat_interleave(g, dim=1), v.repeat_interleave(g, dim=1))
+    _check(o, lse, ref, lse_ref, torch.float16)
+
+
 def test_python_api_matches_oracle():
     import tilefusion_b200 as tilefusion
 

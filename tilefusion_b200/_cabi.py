@@ -58,7 +58,9 @@ class TfDecodeDesc(C.Structure):
         ("k_stride_b", C.c_int64), ("k_stride_h", C.c_int64),
         ("v_stride_b", C.c_int64), ("v_stride_h", C.c_int64),
         ("o_stride_b", C.c_int64), ("o_stride_h", C.c_int64),
-        ("heads_kv", C.c_int32), ("reserved", C.c_int32),
+        ("heads_kv", C.c_int32), ("page_size", C.c_int32),
+        ("block_table", C.c_void_p), ("max_pages", C.c_int32), ("num_pages", C.c_int32),
+        ("k_stride_page", C.c_int64), ("v_stride_page", C.c_int64),
     ]
 
 

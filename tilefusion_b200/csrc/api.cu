@@ -214,7 +214,8 @@ int launch_two_gemms(const AttnLaunch& L, const TfAttnDesc* d, cudaStream_t stre
 template <typename T, int D>
 int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan& plan, cudaStream_t stream,
                      int kv_splits = 0, int tiles_per_split = 0, float* part_o = nullptr,
-                     float* part_ml = nullptr) {
+                     float* part_ml = nullptr, const int* block_table = nullptr, int page_size = 0,
+                     int max_pages = 0) {
   using Smem = tfb::AttnPairSmem<D>;
   auto kern = tfb::attn_fwd_pair_kernel<T, D>;
   static thread_local int configured_device = -1;
@@ -234,6 +235,9 @@ int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan&
   a.tiles_per_split = tiles_per_split;
   a.part_o = part_o;
   a.part_ml = part_ml;
+  a.block_table = block_table;
+  a.page_size = page_size;
+  a.max_pages = max_pages;
   kern<<<kv_splits > 0 ? std::min(plan.grid, a.n_items) : plan.grid, tfb::kPairThreads, Smem::kBytes, stream>>>(L.mq, L.mk, L.mv, a);
   TF_CUDA_TRY(cudaGetLastError());
   return TF_OK;
@@ -266,6 +270,17 @@ int check_decode_desc(const TfDecodeDesc* d) {
     return fail(TF_ERR_BAD_ARG, "heads (%d) must be a multiple of heads_kv (%d)", d->heads, d->heads_kv);
   if (d->heads_kv > 0 && d->heads / d->heads_kv > 128)
     return fail(TF_ERR_UNSUPPORTED, "at most 128 query heads per KV head");
+  if (d->page_size != 0) {
+    if (d->page_size < 128 || d->page_size % 128 != 0)
+      return fail(TF_ERR_UNSUPPORTED, "page_size must be a multiple of 128 keys (got %d)", d->page_size);
+    if (d->block_table == nullptr) return fail(TF_ERR_BAD_ARG, "block_table is null although page_size > 0");
+    if ((int64_t)d->max_pages * d->page_size < d->len_kv)
+      return fail(TF_ERR_BAD_ARG, "block_table rows (%d pages of %d keys) do not cover len_kv %d", d->max_pages,
+                  d->page_size, d->len_kv);
+    if (d->num_pages < 1) return fail(TF_ERR_BAD_ARG, "num_pages must be positive for a paged cache");
+    if (d->k_stride_page % 8 != 0 || d->v_stride_page % 8 != 0 || d->k_stride_page <= 0 || d->v_stride_page <= 0)
+      return fail(TF_ERR_UNSUPPORTED, "page strides must be positive multiples of 8 elements (16 bytes)");
+  }
   const int64_t s[] = {d->q_stride_b, d->q_stride_h, d->k_stride_b, d->k_stride_h,
                        d->v_stride_b, d->v_stride_h};
   for (int64_t x : s)
@@ -299,6 +314,11 @@ int launch_decode_split(const void* q, const void* k, const void* v, float* part
   a.k_stride_h = d->k_stride_h;
   a.v_stride_b = d->v_stride_b;
   a.v_stride_h = d->v_stride_h;
+  a.block_table = d->page_size > 0 ? d->block_table : nullptr;
+  a.page_size = d->page_size;
+  a.max_pages = d->max_pages;
+  a.k_stride_page = d->k_stride_page;
+  a.v_stride_page = d->v_stride_page;
   auto kern = tfb::decode_split_kernel<T, D, kStages>;
   static thread_local int configured_device = -1;
   int dev = 0;
@@ -352,11 +372,13 @@ int launch_gqa_split(const void* q, const void* k, const void* v, float* part_o,
   ad.q_stride_b = d->q_stride_b;
   ad.q_stride_h = (int64_t)group * d->q_stride_h;
   ad.q_stride_l = d->q_stride_h;
-  ad.k_stride_b = d->k_stride_b;
+  // (with a paged cache the batch strides are placeholders: the K and V maps
+  // are rebuilt over the page pool below)
+  ad.k_stride_b = d->page_size > 0 ? d->k_stride_page : d->k_stride_b;
   ad.k_stride_h = d->k_stride_h;
   ad.k_stride_l = D;
   ad.k_stride_d = 1;
-  ad.v_stride_b = d->v_stride_b;
+  ad.v_stride_b = d->page_size > 0 ? d->v_stride_page : d->v_stride_b;
   ad.v_stride_h = d->v_stride_h;
   ad.v_stride_l = D;
   ad.v_stride_d = 1;
@@ -366,13 +388,22 @@ int launch_gqa_split(const void* q, const void* k, const void* v, float* part_o,
   ap.grid = plan.grid;
   AttnLaunch L;
   if (int rc = prepare_attn(q, k, v, part_o, nullptr, &ad, ap, &L)) return rc;
+  if (d->page_size > 0) {
+    // K and V maps over the page pool: (D, page_size, H_kv, num_pages)
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->page_size, (uint64_t)d->heads_kv, (uint64_t)d->num_pages};
+    const int64_t ks[3] = {D, d->k_stride_h, d->k_stride_page};
+    const int64_t vs[3] = {D, d->v_stride_h, d->v_stride_page};
+    if (int rc = encode_map(&L.mk, d->dtype, k, dims, ks, 64, tfb::kAttnTile, "K pages")) return rc;
+    if (int rc = encode_map(&L.mv, d->dtype, v, dims, vs, 64, tfb::kAttnTile, "V pages")) return rc;
+  }
+  const int* table = d->page_size > 0 ? d->block_table : nullptr;
   if (D == 128)
     return d->dtype == TF_F16
-               ? launch_attn_pair<__half, 128>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml)
-               : launch_attn_pair<__nv_bfloat16, 128>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml);
+               ? launch_attn_pair<__half, 128>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages)
+               : launch_attn_pair<__nv_bfloat16, 128>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages);
   return d->dtype == TF_F16
-             ? launch_attn_pair<__half, 64>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml)
-             : launch_attn_pair<__nv_bfloat16, 64>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml);
+             ? launch_attn_pair<__half, 64>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages)
+             : launch_attn_pair<__nv_bfloat16, 64>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages);
 }
 
 int dispatch_split(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
@@ -699,7 +730,7 @@ int tf_device_status(int32_t* code_out) {
   return TF_OK;
 }
 
-int tf_abi_version(void) { return 2; }
+int tf_abi_version(void) { return 3; }
 
 #ifdef TF_PAIR_TRACE
 // Debug builds only: copies the phase trace of CTA 0 (3 roles x 1024 records).

@@ -70,6 +70,11 @@ struct AttnPairArgs {
   int tiles_per_split;
   float* part_o;
   float* part_ml;
+  // Paged KV cache (split-KV mode only; page_size > 0): the K and V tensor maps
+  // cover [pages][heads][page_size][D] and a tile's page comes from the table.
+  const int* block_table;   // [batch][max_pages]
+  int page_size;
+  int max_pages;
 };
 
 template <int D>
@@ -226,7 +231,15 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
             mbar_arrive_expect_tx(full, S::kTileBytes);
             const bool natural = kv == 0 ? !args.k_mn_major : (args.v_mn_major != 0);
             const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
-            if (natural) {
+            if (pargs.page_size > 0) {
+              // paged cache (always the row-per-key layout): outer coordinate = page
+              const int key0 = (j0 + j) * kAttnTile;
+              const int pg = key0 / pargs.page_size;
+              const int page = pargs.block_table[(long long)b * pargs.max_pages + pg];
+#pragma unroll
+              for (int blk = 0; blk < kBlocks; ++blk)
+                tma_load_4d(dst + blk * S::kBlockBytes, map, full, blk * 64, key0 - pg * pargs.page_size, h, page);
+            } else if (natural) {
               // rows = keys, 64 head-dim elements per swizzle block
 #pragma unroll
               for (int blk = 0; blk < kBlocks; ++blk)

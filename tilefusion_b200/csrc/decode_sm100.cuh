@@ -53,6 +53,11 @@ struct DecodeSplitArgs {
   long long q_stride_b, q_stride_h;
   long long k_stride_b, k_stride_h;
   long long v_stride_b, v_stride_h;
+  // paged KV cache (page_size > 0): K/V are [pages][heads][page_size][D]
+  const int* block_table;   // [batch][max_pages]
+  int page_size;
+  int max_pages;
+  long long k_stride_page, v_stride_page;
 };
 
 template <int D, int kStages>
@@ -121,8 +126,10 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
         const int bh = item / args.num_splits;
         const int split = item - bh * args.num_splits;
         const int b = bh / args.heads, h = bh - b * args.heads;
-        const T* kbase = reinterpret_cast<const T*>(args.k) + b * args.k_stride_b + h * args.k_stride_h;
-        const T* vbase = reinterpret_cast<const T*>(args.v) + b * args.v_stride_b + h * args.v_stride_h;
+        const bool paged = args.page_size > 0;
+        const T* kbase = reinterpret_cast<const T*>(args.k) + (paged ? 0 : b * args.k_stride_b) + h * args.k_stride_h;
+        const T* vbase = reinterpret_cast<const T*>(args.v) + (paged ? 0 : b * args.v_stride_b) + h * args.v_stride_h;
+        const int* pages = paged ? args.block_table + (long long)b * args.max_pages : nullptr;
         const int key_begin = split * keys_per_split;
         const int key_end = min(args.len_kv, key_begin + keys_per_split);
         for (int c0 = key_begin; ok && c0 < key_end; c0 += chunk) {
@@ -137,8 +144,15 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
               }
               const uint32_t bytes = uint32_t(n) * D * 2;
               mbar_arrive_expect_tx(bar_full + stage * 8, bytes);
-              tma_load_1d(smem_base + S::kOffStages + stage * S::kStageBytes,
-                          base + (long long)s0 * D, bytes, bar_full + stage * 8, policy);
+              // a 128-key stage never straddles a page (page_size is a multiple of 128)
+              const T* src = base + (long long)s0 * D;
+              if (paged) {
+                const int pg = s0 / args.page_size;
+                src = base + (long long)pages[pg] * (pass == 0 ? args.k_stride_page : args.v_stride_page) +
+                      (long long)(s0 - pg * args.page_size) * D;
+              }
+              tma_load_1d(smem_base + S::kOffStages + stage * S::kStageBytes, src, bytes,
+                          bar_full + stage * 8, policy);
               ++issued;
               if (++stage == kStages) {
                 stage = 0;

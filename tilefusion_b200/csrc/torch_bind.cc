@@ -207,6 +207,56 @@ void flash_decoding(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& 
                          at::cuda::getCurrentCUDAStream().stream()));
 }
 
+// Paged KV cache: K/V pages [num_pages, H_kv, page_size, D], block_table int32 [B, max_pages].
+void flash_decoding_paged(const at::Tensor& Q, const at::Tensor& Kp, const at::Tensor& Vp,
+                          const at::Tensor& block_table, int64_t kv_len, at::Tensor& O, at::Tensor& LSE,
+                          int64_t kv_chunk, int64_t num_splits, double softmax_scale) {
+  TORCH_CHECK(Q.is_cuda() && Kp.is_cuda() && Vp.is_cuda() && block_table.is_cuda(), "inputs must be CUDA tensors");
+  TORCH_CHECK(Q.dim() == 4 && Q.size(2) == 1, "Q must be [B, H, 1, D]");
+  TORCH_CHECK(Kp.dim() == 4 && Kp.sizes() == Vp.sizes() && Kp.size(3) == Q.size(3) && Q.size(1) % Kp.size(1) == 0,
+              "K and V pages must be [num_pages, H_kv, page_size, D] with H_kv dividing Q's head count");
+  TORCH_CHECK(Q.scalar_type() == Kp.scalar_type() && Q.scalar_type() == Vp.scalar_type(),
+              "Q, K and V must share one dtype");
+  TORCH_CHECK(Q.stride(3) == 1 && Kp.stride(3) == 1 && Vp.stride(3) == 1 && Kp.stride(2) == Kp.size(3) &&
+                  Vp.stride(2) == Vp.size(3),
+              "rows of Q, K and V must be contiguous and consecutive keys of a page D elements apart");
+  TORCH_CHECK(block_table.scalar_type() == at::kInt && block_table.dim() == 2 && block_table.is_contiguous() &&
+                  block_table.size(0) == Q.size(0),
+              "block_table must be a contiguous int32 tensor [B, max_pages]");
+  TORCH_CHECK(O.is_cuda() && O.scalar_type() == Q.scalar_type() && O.dim() == 4 && O.size(0) == Q.size(0) &&
+                  O.size(1) == Q.size(1) && O.size(2) == 1 && O.size(3) == Q.size(3) && O.stride(3) == 1,
+              "O must be [B, H, 1, D] with contiguous rows and Q's dtype");
+  TORCH_CHECK(LSE.is_cuda() && LSE.scalar_type() == at::kFloat && LSE.is_contiguous() &&
+                  LSE.numel() == Q.size(0) * Q.size(1),
+              "LSE must be a contiguous fp32 CUDA tensor with B*H elements");
+  TfDecodeDesc d{};
+  d.dtype = dtype_code(Q);
+  d.batch = (int32_t)Q.size(0);
+  d.heads = (int32_t)Q.size(1);
+  d.heads_kv = (int32_t)Kp.size(1);
+  d.len_kv = (int32_t)kv_len;
+  d.head_dim = (int32_t)Q.size(3);
+  d.kv_chunk = (int32_t)kv_chunk;
+  d.num_splits = (int32_t)num_splits;
+  d.softmax_scale = (float)softmax_scale;
+  d.q_stride_b = Q.stride(0);
+  d.q_stride_h = Q.stride(1);
+  d.k_stride_h = Kp.stride(1);
+  d.v_stride_h = Vp.stride(1);
+  d.o_stride_b = O.stride(0);
+  d.o_stride_h = O.stride(1);
+  d.page_size = (int32_t)Kp.size(2);
+  d.block_table = block_table.data_ptr<int>();
+  d.max_pages = (int32_t)block_table.size(1);
+  d.num_pages = (int32_t)Kp.size(0);
+  d.k_stride_page = Kp.stride(0);
+  d.v_stride_page = Vp.stride(0);
+  const c10::cuda::CUDAGuard guard(Q.device());
+  at::Tensor ws = decode_workspace(d, Q);
+  check_status(tf_decode(Q.data_ptr(), Kp.data_ptr(), Vp.data_ptr(), O.data_ptr(), LSE.data_ptr<float>(),
+                         ws.data_ptr(), (uint64_t)ws.numel() * 4, &d, at::cuda::getCurrentCUDAStream().stream()));
+}
+
 void flash_decoding_partial(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, at::Tensor& slot,
                             int64_t kv_chunk, int64_t num_splits, double softmax_scale) {
   TfDecodeDesc d = decode_desc(Q, K, V, kv_chunk, num_splits, softmax_scale);
@@ -304,6 +354,11 @@ TF_REGISTER_OP(flash_decoding,
                "flash_decoding(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, Tensor(b!) LSE, "
                "int kv_chunk, int num_splits, float softmax_scale) -> ()",
                &flash_decoding);
+
+TF_REGISTER_OP(flash_decoding_paged,
+               "flash_decoding_paged(Tensor Q, Tensor K_pages, Tensor V_pages, Tensor block_table, int kv_len, "
+               "Tensor(a!) O, Tensor(b!) LSE, int kv_chunk, int num_splits, float softmax_scale) -> ()",
+               &flash_decoding_paged);
 
 TF_REGISTER_OP(flash_decoding_partial,
                "flash_decoding_partial(Tensor Q, Tensor K, Tensor V, Tensor(a!) slot, "

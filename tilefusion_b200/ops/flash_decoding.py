@@ -25,9 +25,14 @@ class FlashDecoding:
         self.num_splits = num_splits
         self.softmax_scale = softmax_scale
 
-    def __call__(self, query: torch.Tensor, key: torch.Tensor,
-                 value: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        """``query [B, H, 1, D]``, ``key``/``value`` ``[B, H, Lk, D]``.
+    def __call__(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                 block_table: Optional[torch.Tensor] = None,
+                 kv_len: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``query [B, H, 1, D]``; ``key``/``value`` ``[B, H_kv, Lk, D]`` with ``H_kv``
+        dividing ``H`` (grouped-query attention when smaller), or -- with
+        ``block_table`` (int32 ``[B, max_pages]``) and ``kv_len`` -- a paged cache
+        ``[num_pages, H_kv, page_size, D]`` whose page ``block_table[b, i]`` holds keys
+        ``[i * page_size, (i + 1) * page_size)`` of batch entry ``b``.
 
         Returns ``O [B, H, 1, D]`` and ``LSE [B, H, 1]`` (fp32, natural log).
         """
@@ -38,6 +43,13 @@ class FlashDecoding:
         b, h, _, d = query.shape
         out = torch.empty(b, h, 1, d, dtype=query.dtype, device=query.device)
         lse = torch.empty(b, h, 1, dtype=torch.float32, device=query.device)
+        if block_table is not None:
+            if kv_len is None:
+                raise ValueError("kv_len is required with a block_table")
+            torch.ops.tilefusion.flash_decoding_paged(
+                query, key, value, block_table, kv_len, out, lse, self.kv_chunk, self.num_splits, scale
+            )
+            return out, lse
         torch.ops.tilefusion.flash_decoding(
             query, key, value, out, lse, self.kv_chunk, self.num_splits, scale
         )
@@ -46,14 +58,17 @@ class FlashDecoding:
 
 def flash_decoding(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                    kv_chunk: int = 512, num_splits: int = 0,
-                   softmax_scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                   softmax_scale: Optional[float] = None, block_table: Optional[torch.Tensor] = None,
+                   kv_len: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """One-query-row attention over a long KV sequence.
 
     Args:
         query: ``[B, H, 1, D]``.
-        key, value: ``[B, H, Lk, D]``, rows contiguous.
+        key, value: ``[B, H_kv, Lk, D]``, rows contiguous (``H_kv`` divides ``H``); or
+            pages ``[num_pages, H_kv, page_size, D]`` when ``block_table`` is given.
         kv_chunk: keys per chunk (multiple of 128, at most 1024).
         num_splits: partial rows per (batch, head); 0 lets the registry choose.
         softmax_scale: defaults to ``1/sqrt(D)``.
+        block_table, kv_len: paged KV cache (``page_size`` a multiple of 128).
     """
-    return FlashDecoding(kv_chunk, num_splits, softmax_scale)(query, key, value)
+    return FlashDecoding(kv_chunk, num_splits, softmax_scale)(query, key, value, block_table, kv_len)
