@@ -392,17 +392,35 @@ def run_prefill(args, w, name, device, rank, world):
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     ho = torch.empty(o.shape, dtype=o.dtype).pin_memory()
 
-    def e2e_step():
-        dq = hq.to(device, non_blocking=True)
-        dk = hk.to(device, non_blocking=True)
-        dv = hv.to(device, non_blocking=True)
-        out = tilefusion.ops.flash_attention(dq, dk.transpose(-1, -2), dv, 0, 0, 0, 0, scale, causal)
-        ho.copy_(out, non_blocking=True)
+    pipe = tilefusion.HostPipeline(
+        lambda dq, dk, dv: tilefusion.ops.flash_attention(dq, dk.transpose(-1, -2), dv, 0, 0, 0, 0, scale, causal),
+        device)
 
-    e2e_secs = time_steps(e2e_step, e2e_steps, 3, device, world)
+    def e2e_step():
+        # pinned host Q, K, V in, O back into pinned host memory; copies of neighbouring
+        # steps overlap with the kernel (tilefusion_b200.HostPipeline)
+        pipe.submit((hq, hk, hv), ho)
+
+    def e2e_steps_timed(n):
+        torch.cuda.synchronize(device)
+        t0 = time.perf_counter()
+        for _ in range(n):
+            e2e_step()
+        pipe.flush()
+        return time.perf_counter() - t0
+
+    e2e_steps_timed(3)
+    e2e_secs = e2e_steps_timed(e2e_steps)
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([e2e_secs], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_secs = t.item()
     e2e = {"value": total_units * e2e_steps / e2e_secs / 1e12, "unit": "TFLOP/s",
            "h2d_bytes_per_step": 3 * q.numel() * q.element_size(),
-           "d2h_bytes_per_step": o.numel() * o.element_size(), "steps": e2e_steps}
+           "d2h_bytes_per_step": o.numel() * o.element_size(), "steps": e2e_steps,
+           "timing": "host wall clock around submit..flush (three streams), max over ranks"}
     return dict(value=value, unit="TFLOP/s", secs=secs, clocks=clocks[0], parity=parity, e2e=e2e,
                 roofline=roof, launches=args.steps)
 

@@ -203,3 +203,24 @@ def test_unsupported_inputs_report_errors():
     with pytest.raises(TileFusionError) as e:
         attn_fwd(q, q, q, 1.0)
     assert e.value.code == TF_ERR_UNSUPPORTED and "head_dim" in str(e.value)
+
+
+def test_host_pipeline_matches_direct_calls():
+    """Overlapped host->device->host steps give the same outputs as plain calls."""
+    import tilefusion_b200 as tilefusion
+
+    b, h, l, d = 2, 4, 512, 128
+    scale = 1.0 / math.sqrt(d)
+    fn = lambda q, k, v: tilefusion.ops.flash_attention(q, k.transpose(-1, -2), v, 0, 0, 0, 0, scale, False)
+    pipe = tilefusion.HostPipeline(fn, torch.device("cuda", 0))
+    steps = []
+    for i in range(5):
+        q, k, v = orc.seeded_inputs(60 + i, (b, h, l, d), (b, h, l, d), (b, h, l, d), 0.5)
+        host = [t.pin_memory() for t in (q, k, v)]
+        out = torch.empty(b, h, l, d, dtype=torch.float16).pin_memory()
+        pipe.submit(host, out)
+        steps.append((q, k, v, out))
+    pipe.flush()
+    for q, k, v, out in steps:
+        ref, _ = orc.attention_fp32(q, k, v, scale)
+        _check(out, None, ref, None, torch.float16)

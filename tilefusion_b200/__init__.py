@@ -15,8 +15,9 @@ import of the operator layer raises.
 
 from . import _cabi  # noqa: F401  (loads libtilefusion_b200.so)
 from . import ops  # noqa: F401
+from .host_pipeline import HostPipeline  # noqa: F401
 
-__all__ = ["ops", "load_torch_ops"]
+__all__ = ["ops", "load_torch_ops", "HostPipeline"]
 
 
 def load_torch_ops() -> None:

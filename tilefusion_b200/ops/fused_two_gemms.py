@@ -19,13 +19,6 @@ from .._torch_ops import ensure_loaded
 __all__ = ["fused_two_gemms"]
 
 
-def _validate_tensor(tensor: torch.Tensor, name: str, expected_device: str = "cuda") -> None:
-    if tensor.device.type != expected_device:
-        raise ValueError(f"{name} must be a {expected_device} tensor")
-    if tensor.dtype not in (torch.float16, torch.bfloat16):
-        raise TypeError(f"{name} must be of type torch.float16 or torch.bfloat16, got {tensor.dtype}")
-
-
 def fused_two_gemms(
     input_a: torch.Tensor,
     input_b: torch.Tensor,
@@ -37,7 +30,12 @@ def fused_two_gemms(
     tp: int = 64,
 ) -> None:
     """``output[M, P] = input_a[M, K] @ input_b[N, K].T @ input_c[P, N].T`` (in place)."""
-    for t, name in ((input_a, "input_a"), (input_b, "input_b"), (input_c, "input_c"), (output, "output")):
-        _validate_tensor(t, name)
+    operands = {"input_a": input_a, "input_b": input_b, "input_c": input_c, "output": output}
+    off_device = [n for n, t in operands.items() if t.device.type != "cuda"]
+    if off_device:
+        raise ValueError(f"{', '.join(off_device)} must be cuda tensor(s)")
+    wrong_type = [n for n, t in operands.items() if t.dtype not in (torch.float16, torch.bfloat16)]
+    if wrong_type:
+        raise TypeError(f"{', '.join(wrong_type)} must be torch.float16 or torch.bfloat16")
     ensure_loaded()
     torch.ops.tilefusion.fused_two_gemms(input_a, input_b, input_c, output, tm, tn, tk, tp)
