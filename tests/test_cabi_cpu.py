@@ -167,6 +167,34 @@ def test_decode_validation(native_lib, kw, needle):
     assert rc == _cabi.TF_ERR_UNSUPPORTED and needle in native_lib.tf_last_error().decode()
 
 
+def test_paged_cache_validation(native_lib):
+    plan = _cabi.TfDecodePlan()
+    table = (C.c_int32 * 64)()
+    d = _decode_desc(2, 4, 4096)
+    d.page_size, d.max_pages, d.num_pages = 512, 8, 32
+    d.block_table = C.cast(table, C.c_void_p)
+    d.k_stride_page = d.v_stride_page = 4 * 512 * 128
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == 0
+    d.page_size = 100
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_UNSUPPORTED
+    assert "page_size" in native_lib.tf_last_error().decode()
+    d.page_size, d.max_pages = 512, 4                        # 4 pages of 512 keys < 4096 keys
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_BAD_ARG
+    d.max_pages, d.block_table = 8, None
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_BAD_ARG
+    assert "block_table" in native_lib.tf_last_error().decode()
+
+
+def test_fused_two_gemms_validation(native_lib):
+    buf = (C.c_char * 64)()
+    p = C.addressof(buf)
+    p += (-p) % 16
+    rc = native_lib.tf_fused_two_gemms(p, p, p, p, 64, 64, 96, 96, _cabi.TF_F16, 96, 96, 96, 96, None)
+    assert rc == _cabi.TF_ERR_UNSUPPORTED and "k == p" in native_lib.tf_last_error().decode()
+    rc = native_lib.tf_fused_two_gemms(p, p, p, p, 64, 64, 64, 64, _cabi.TF_F16, 32, 64, 64, 64, None)
+    assert rc == _cabi.TF_ERR_BAD_ARG and "leading dimension" in native_lib.tf_last_error().decode()
+
+
 def test_workspace_too_small_is_reported(native_lib):
     d = _decode_desc(2, 2, 4096)
     buf = (C.c_char * 64)()           # host memory: never dereferenced, the size check comes first
