@@ -1,9 +1,9 @@
 """Generates ``tests/golden/flash_attention_ref.npz``.
 
-Run where TileFusion's source tree is available (its path is the first
-argument, default ``/root/reference``)::
+Run where TileFusion's source tree is available (its path is the only
+argument)::
 
-    python tests/golden/make_golden.py [path-to-TileFusion]
+    python tests/golden/make_golden.py <path-to-TileFusion>
 
 The script imports TileFusion's own test oracle, the ``FlashAttentionRef`` class
 of ``tests/python/test_flash_attn.py:21-134`` (a stub stands in for the
@@ -69,7 +69,9 @@ def run_ref(cls, q, k_t, v, tiles, scale, causal, dtype):
 
 
 def main() -> None:
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path-to-TileFusion-source-tree>")
+    root = Path(sys.argv[1])
     cls = load_reference_class(root)
     cases = [
         # name, Lq, Lk, D, Dv, tiles(tq, tkv, thqk, thv), scale, causal, seed, sigma

@@ -7,10 +7,11 @@
 // the exp unit take turns; here one thread fixes the MMA issue order
 //     S0_0 S1_0 | PV0_0 S0_1 | PV1_0 S1_1 | PV0_1 S0_2 | ...
 // so that while the tensor pipe works for tile 0 the softmax warps of tile 1
-// run, and vice versa.  Roles (320 threads, one CTA per SM):
+// run, and vice versa.  Roles (384 threads, one CTA per SM):
 //   warps 0-3  softmax + epilogue of Q tile 0   (one row per thread)
 //   warps 4-7  softmax + epilogue of Q tile 1
-//   warp  8    tcgen05.mma issuer (one thread), owns the TMEM allocation
+//   warp  8    tcgen05.mma issuer (the warp walks the schedule, one elected
+//              lane issues), owns the TMEM allocation
 //   warp  9    TMA producer (one thread)
 //   warps 10-11 idle; they complete the third warpgroup so that it can hand
 //              its registers to the softmax warpgroups (setmaxnreg)
@@ -19,6 +20,10 @@
 // Shared memory: Q0, Q1 and a ring of K/V stages (K_0 V_0 K_1 V_1 ...), each
 // stage released by a tcgen05.commit after the last MMA that reads it, so both
 // Q tiles share every K/V load.
+//
+// The same kernel serves grouped-query decoding in split-KV mode (see
+// AttnPairArgs): the query heads of a group are the rows of Q tile 0, an item
+// covers a range of KV tiles, and the epilogue writes fp32 partial rows.
 #pragma once
 
 #include <type_traits>
