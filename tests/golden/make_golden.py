@@ -54,18 +54,24 @@ def load_reference_class(root: Path):
 
 
 def run_ref(cls, q, k_t, v, tiles, scale, causal, dtype):
-    """Calls the class the way TileFusion's test does: key is [D, Lk]."""
+    """Calls the class the way TileFusion's test does: key is [D, Lk].
+
+    The class allocates its output with ``torch.empty`` and multiplies that
+    uninitialised buffer by a zero row-sum on the first tile; whatever the
+    allocator hands back (inf or NaN bit patterns included) would survive as
+    NaN.  ``torch.empty`` is therefore served by ``torch.zeros`` for the duration
+    of the call, which leaves the computed values exactly as the class defines
+    them."""
     ref = cls(*tiles, scale, causal)
-    for _ in range(8):
-        # The class multiplies an uninitialised buffer (torch.empty) by zero.
-        # Free a zero-filled block of the same size right before the call so
-        # that the allocator hands that block back, and retry if it did not.
-        scratch = torch.zeros(q.size(0), v.size(1), dtype=dtype)
-        del scratch
+    real_empty = torch.empty
+    torch.empty = lambda *a, **kw: torch.zeros(*a, **kw)
+    try:
         out = ref(q.to(dtype), k_t.to(dtype), v.to(dtype))
-        if torch.isfinite(out).all():
-            return out
-    raise RuntimeError("reference produced non-finite output")
+    finally:
+        torch.empty = real_empty
+    if not torch.isfinite(out).all():
+        raise RuntimeError("reference produced non-finite output")
+    return out
 
 
 def main() -> None:
