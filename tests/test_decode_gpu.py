@@ -224,3 +224,36 @@ def test_bad_arguments_report_errors():
     with pytest.raises(TileFusionError) as e:
         decode(q.cuda(), k.cuda(), v.cuda(), None, 100, 0)
     assert e.value.code == TF_ERR_UNSUPPORTED and "kv_chunk" in str(e.value)
+
+
+def test_missing_peer_is_reported_not_hung():
+    """Failure detection: the combine of a KV-sharded decode waits for a flag per
+    sending rank.  Here one sender never shows up (its flag stays 0); the bounded
+    wait must give up, the kernel must return, the device status word must name
+    the wait, and the context must stay usable."""
+    import ctypes as C
+
+    from cabi_helpers import decode, device_status
+    from tilefusion_b200 import _cabi
+
+    lib = _cabi.lib()
+    b, h, d, n_ranks = 1, 2, 128, 2
+    slots = torch.zeros(n_ranks, b * h * (d + 2), dtype=torch.float32, device="cuda")
+    flags = torch.zeros(n_ranks, dtype=torch.int32, device="cuda")
+    flags[0] = 1                                   # rank 0 "arrived", rank 1 never does
+    o = torch.zeros(b, h, 1, d, dtype=torch.float16, device="cuda")
+    lse = torch.zeros(b, h, 1, dtype=torch.float32, device="cuda")
+    rc = lib.tf_decode_gathered_wait(slots.data_ptr(), flags.data_ptr(), n_ranks, 1, b, h, d, _cabi.TF_F16,
+                                     o.data_ptr(), o.stride(0), o.stride(1), lse.data_ptr(),
+                                     torch.cuda.current_stream().cuda_stream)
+    assert rc == 0                                 # the launch itself succeeds
+    code = C.c_int32(0)
+    rc = lib.tf_device_status(C.byref(code))       # synchronises; the wait has run out by now
+    assert rc == _cabi.TF_ERR_DEVICE_TIMEOUT and code.value == 401
+    assert "wait gave up" in lib.tf_last_error().decode()
+    assert device_status() == 0                    # the word is cleared by the read
+    # the context is intact: an ordinary decode still runs and is correct
+    q, k, v = _inputs(30, 1, 2, 512, 128)
+    out, l2 = decode(q.cuda(), k.cuda(), v.cuda())
+    ref, lse_ref = orc.decode_fp32(q, k, v)
+    _check(out, l2, ref, lse_ref, torch.float16)
