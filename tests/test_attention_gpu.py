@@ -195,6 +195,44 @@ def test_config2_size_properties_and_subset():
     assert (lse2 - lse[:1]).abs().max().item() <= LSE_ABS
 
 
+def test_config5_size_bf16_subset_and_properties():
+    """Large bf16 prefill config (B16 H64 L8192 D128, sigma 0.5, seed 4): the
+    kernel runs on the full 8 GiB problem; a sample of heads is checked against
+    the fp32 expression evaluated on the GPU, one of them also against the CPU
+    oracle, and V = 1 must give O = 1."""
+    from cabi_helpers import attn_fwd, device_status
+
+    free, _ = torch.cuda.mem_get_info()
+    if free < 14 << 30:
+        pytest.skip("needs 14 GiB of free device memory")
+    b, h, l, d = 16, 64, 8192, 128
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q = torch.empty(b, h, l, d, dtype=torch.bfloat16, device="cuda")
+    k, v = torch.empty_like(q), torch.empty_like(q)
+    for t in (q, k, v):
+        for bi in range(b):
+            t[bi] = (torch.randn(h, l, d, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    o, lse = attn_fwd(q, k, v, scale, False, poison=False)
+    assert device_status() == 0
+    sample = [(0, 0), (3, 17), (7, 63), (15, 31), (9, 5), (12, 40), (1, 62), (15, 63)]
+    num = den = 0.0
+    for bi, hi in sample:
+        ref, lse_ref = orc.attention_fp32(q[bi, hi], k[bi, hi], v[bi, hi], scale)
+        diff = o[bi, hi].float() - ref
+        assert diff.abs().max().item() <= MAX_ABS
+        assert (lse[bi, hi] - lse_ref).abs().max().item() <= LSE_ABS
+        num += diff.double().pow(2).sum().item()
+        den += ref.double().pow(2).sum().item()
+    assert math.sqrt(num / den) <= REL_L2[torch.bfloat16]
+    bi, hi = sample[1]
+    ref, lse_ref = orc.attention_fp32(q[bi, hi].cpu(), k[bi, hi].cpu(), v[bi, hi].cpu(), scale)
+    _check(o[bi, hi], lse[bi, hi], ref, lse_ref, torch.bfloat16)
+    del o, lse
+    o1, _ = attn_fwd(q[:1, :8], k[:1, :8], torch.ones_like(v[:1, :8]), scale, False)
+    assert (o1.float() - 1.0).abs().max().item() <= 1e-2          # bf16 output spacing near 1 is 2^-8
+
+
 def test_unsupported_inputs_report_errors():
     from cabi_helpers import attn_fwd
     from tilefusion_b200._cabi import TileFusionError, TF_ERR_UNSUPPORTED

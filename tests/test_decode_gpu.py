@@ -216,6 +216,50 @@ def test_config3_size_properties_and_subset():
     assert (o1.float() - 1.0).abs().max().item() <= 2e-3
 
 
+def test_config4_size_subset_sharded_and_properties():
+    """Long-context decode config (B4 H32 Lk131072 D128, seed 3): the full 8 GiB
+    problem on one GPU against the fp32 expression on the GPU for every (b, h),
+    the CPU oracle on one of them, and the same problem through the KV-sharded
+    path (8 shards written into slots, then the gathered combine)."""
+    from cabi_helpers import decode, decode_gathered, decode_partial_into, device_status
+    from tilefusion_b200.shard import kv_slice
+
+    free, _ = torch.cuda.mem_get_info()
+    if free < 12 << 30:
+        pytest.skip("needs 12 GiB of free device memory")
+    b, h, lk, d = 4, 32, 131072, 128
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn(b, h, 1, d, generator=g, device="cuda").half()
+    k = torch.empty(b, h, lk, d, dtype=torch.float16, device="cuda")
+    v = torch.empty_like(k)
+    for t in (k, v):
+        for bi in range(b):
+            t[bi] = torch.randn(h, lk, d, generator=g, device="cuda").half()
+    o, lse = decode(q, k, v)
+    assert device_status() == 0
+    worst, num, den = 0.0, 0.0, 0.0
+    for bi in range(b):
+        for h0 in range(0, h, 8):
+            ref, lse_ref = orc.decode_fp32(q[bi:bi + 1, h0:h0 + 8], k[bi:bi + 1, h0:h0 + 8], v[bi:bi + 1, h0:h0 + 8])
+            diff = o[bi:bi + 1, h0:h0 + 8].float() - ref
+            worst = max(worst, diff.abs().max().item())
+            num += diff.double().pow(2).sum().item()
+            den += ref.double().pow(2).sum().item()
+            assert (lse[bi:bi + 1, h0:h0 + 8] - lse_ref).abs().max().item() <= LSE_ABS
+    assert worst <= MAX_ABS and math.sqrt(num / den) <= REL_L2[torch.float16]
+    ref, lse_ref = orc.decode_fp32(q[2:3, 5:6].cpu(), k[2:3, 5:6].cpu(), v[2:3, 5:6].cpu())
+    _check(o[2:3, 5:6], lse[2:3, 5:6], ref, lse_ref, torch.float16)
+    # the sharded path on the same tensors (views of the shards, no copies)
+    n_shards = 8
+    slots = torch.full((n_shards, b * h * (d + 2)), float("nan"), dtype=torch.float32, device="cuda")
+    for r in range(n_shards):
+        k0, k1 = kv_slice(lk, r, n_shards)
+        decode_partial_into(q, k[:, :, k0:k1], v[:, :, k0:k1], slots[r])
+    o2, lse2 = decode_gathered(slots, b, h, d, torch.float16)
+    assert (o2.float() - o.float()).abs().max().item() <= 2e-3
+    assert (lse2 - lse).abs().max().item() <= 1e-4
+
+
 def test_bad_arguments_report_errors():
     from cabi_helpers import decode
     from tilefusion_b200._cabi import TileFusionError, TF_ERR_UNSUPPORTED
