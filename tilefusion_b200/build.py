@@ -91,7 +91,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     deps = sources + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [
         INCLUDE / "tilefusion_b200.h"
     ]
-    # TF_NVCC_EXTRA: extra compiler flags (e.g. "-DTF_PAIR_EMU_PER8=3") for tuning runs.
+    # TF_NVCC_EXTRA: extra compiler flags (e.g. "-DTF_PAIR_SPLIT_P=0") for tuning runs.
     extra = os.environ.get("TF_NVCC_EXTRA", "").split()
     digest = _source_hash(deps, " ".join(NVCC_FLAGS + extra))
     if not force and _up_to_date(out, digest):

@@ -126,6 +126,8 @@ int sm_count() {
 // Tensor maps and kernel arguments shared by the prefill variants.
 struct AttnLaunch {
   CUtensorMap mq, mk, mv;
+  CUtensorMap mo;        // output map for the TMA-store epilogue; valid when has_mo
+  bool has_mo = false;
   tfb::AttnFwdArgs args;
 };
 
@@ -155,6 +157,22 @@ int prepare_attn(const void* q, const void* k, const void* v, void* o, float* ls
     const uint64_t dims[4] = {(uint64_t)d->len_kv, (uint64_t)D, H, B};
     const int64_t str[3] = {d->v_stride_d, d->v_stride_h, d->v_stride_b};
     if (int rc = encode_map(&out->mv, d->dtype, v, dims, str, 64, D, "V (stored [Dv, Lk])")) return rc;
+  }
+  {
+    // The output leaves through a TMA store when its layout can be described
+    // by a tensor map (16-byte aligned base, positive strides); otherwise the
+    // kernels fall back to per-row stores.
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->len_q, H, B};
+    const int64_t str[3] = {d->o_stride_l, d->o_stride_h, d->o_stride_b};
+    bool ok = reinterpret_cast<uintptr_t>(o) % 16 == 0;
+    for (int i = 0; i < 3; ++i) ok = ok && (dims[i + 1] == 1 || (str[i] > 0 && str[i] % 8 == 0));
+    out->has_mo = false;
+    if (ok) {
+      if (int rc = encode_map(&out->mo, d->dtype, o, dims, str, 64, tfb::kAttnTile, "O")) return rc;
+      out->has_mo = true;
+    } else {
+      out->mo = out->mq;
+    }
   }
   tfb::AttnFwdArgs& args = out->args;
   args.o = o;
@@ -231,6 +249,7 @@ int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan&
   a.batch = d->batch;
   a.n_pairs = (d->len_q + 2 * tfb::kAttnTile - 1) / (2 * tfb::kAttnTile);
   a.n_items = d->batch * d->heads * a.n_pairs * (kv_splits > 0 ? kv_splits : 1);
+  a.tma_store = (kv_splits == 0 && L.has_mo) ? 1 : 0;
   a.kv_splits = kv_splits;
   a.tiles_per_split = tiles_per_split;
   a.part_o = part_o;
@@ -238,7 +257,7 @@ int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan&
   a.block_table = block_table;
   a.page_size = page_size;
   a.max_pages = max_pages;
-  kern<<<kv_splits > 0 ? std::min(plan.grid, a.n_items) : plan.grid, tfb::kPairThreads, Smem::kBytes, stream>>>(L.mq, L.mk, L.mv, a);
+  kern<<<kv_splits > 0 ? std::min(plan.grid, a.n_items) : plan.grid, tfb::kPairThreads, Smem::kBytes, stream>>>(L.mq, L.mk, L.mv, L.mo, a);
   TF_CUDA_TRY(cudaGetLastError());
   return TF_OK;
 }

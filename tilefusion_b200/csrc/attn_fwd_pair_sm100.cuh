@@ -17,9 +17,12 @@
 //              its registers to the softmax warpgroups (setmaxnreg)
 // TMEM (512 columns): S0 | S1 | O0 | O1, each 128 fp32 columns (O: D columns);
 // P overwrites the first 64 columns of its S and is the TMEM A operand of PV.
-// Shared memory: Q0, Q1 and a ring of K/V stages (K_0 V_0 K_1 V_1 ...), each
+// Shared memory: Q0, Q1, a ring of three K/V stages (K_0 V_0 K_1 V_1 ...), each
 // stage released by a tcgen05.commit after the last MMA that reads it, so both
-// Q tiles share every K/V load.
+// Q tiles share every K/V load, and one output staging tile per Q tile: the
+// epilogue writes the 16-bit O tile there (swizzled) and one thread sends it
+// to global memory with a TMA store.  While an item runs, the producer brings
+// the next item's Q tiles and first K/V tiles into L2.
 //
 // The same kernel serves grouped-query decoding in split-KV mode (see
 // AttnPairArgs): the query heads of a group are the rows of Q tile 0, an item
@@ -33,17 +36,18 @@
 namespace tfb {
 
 constexpr int kPairThreads = 384;     // three warpgroups; warps 10-11 only donate registers
-constexpr int kPairRegsSoftmax = 200;
-constexpr int kPairRegsIssue = 96;
-constexpr int kPairStages = 5;
-// Tuning switches (overridable with -D at build time).
-#ifndef TF_PAIR_EMU_PER8
-#define TF_PAIR_EMU_PER8 2          // of every 8 exponentials, this many run on the FMA pipe
-#endif
+constexpr int kPairRegsSoftmax = 208;
+constexpr int kPairRegsIssue = 88;
+// setmaxnreg only moves registers between the warpgroups of the CTA: the CTA is
+// launched with 168 registers per thread (65536 / 384, rounded down to 8), and a
+// raise that does not fit into what the other warpgroups gave up blocks forever.
+static_assert(2 * kPairRegsSoftmax + kPairRegsIssue <= 3 * 168, "register split exceeds the CTA's allocation");
+constexpr int kPairStages = 3;        // K/V ring (a deeper ring measured slower)
+// Publish P in two halves: the first four P.V MMAs start while the second
+// half of the exponentials is still being computed.
 #ifndef TF_PAIR_SPLIT_P
-#define TF_PAIR_SPLIT_P 1           // publish P in two halves (first P.V MMAs start earlier)
+#define TF_PAIR_SPLIT_P 1
 #endif
-constexpr int kPairEmuPer8 = TF_PAIR_EMU_PER8;
 
 // Optional phase trace of CTA 0 (debug builds only, -DTF_PAIR_TRACE): one
 // thread per role appends (event, tile, clock) records to a device array.
@@ -65,6 +69,7 @@ struct AttnPairArgs {
   int batch;
   int n_pairs;          // ceil(len_q / 256)
   int n_items;          // batch * heads * n_pairs * max(kv_splits, 1)
+  int tma_store;        // 1: O leaves through shared memory and a TMA store (map_o is valid)
   // Split-KV mode (kv_splits > 0; used for grouped-query decoding, where the
   // "query rows" of a head are the query heads that share one KV head): an item
   // covers KV tiles [split * tiles_per_split, ...), and instead of the final
@@ -88,7 +93,8 @@ struct AttnPairSmem {
   static constexpr int kBlockBytes = kAttnTile * 128;
   static constexpr int kOffQ = 0;                                   // Q0, Q1
   static constexpr int kOffKV = 2 * kTileBytes;                     // ring
-  static constexpr int kOffBar = kOffKV + kPairStages * kTileBytes;
+  static constexpr int kOffOut = kOffKV + kPairStages * kTileBytes; // output staging, one tile per Q tile
+  static constexpr int kOffBar = kOffOut + 2 * kTileBytes;
   // barrier slots (8 bytes each)
   static constexpr int kBarQFull = 0;      // [2]
   static constexpr int kBarQEmpty = 2;     // [2]
@@ -97,9 +103,11 @@ struct AttnPairSmem {
   static constexpr int kBarOFull = 8;      // [2]
   static constexpr int kBarOEmpty = 10;    // [2]
   static constexpr int kBarPFullHi = 12;   // [2]  second half of P (keys 64..127)
-  static constexpr int kBarKVFull = 14;    // [kPairStages]
-  static constexpr int kBarKVEmpty = 14 + kPairStages;
-  static constexpr int kNumBars = 14 + 2 * kPairStages;
+  static constexpr int kBarOutFree = 14;   // [2]  output staging of tile x may be overwritten
+  static constexpr int kBarOutFull = 16;   // [2]  all 128 rows of tile x are in the staging buffer
+  static constexpr int kBarKVFull = 18;    // [kPairStages]
+  static constexpr int kBarKVEmpty = 18 + kPairStages;
+  static constexpr int kNumBars = 18 + 2 * kPairStages;
   static constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 4;
   static constexpr int kBytes = kOffAbort + 4 + 1024;               // + slack for 1024-B alignment
@@ -107,7 +115,8 @@ struct AttnPairSmem {
 
 enum AttnPairWaitCode {
   kPWaitQFull = 301, kPWaitQEmpty = 302, kPWaitKVFull = 303, kPWaitKVEmpty = 304,
-  kPWaitSFull = 305, kPWaitPFull = 306, kPWaitOFull = 307, kPWaitOEmpty = 308, kPWaitEpi = 309
+  kPWaitSFull = 305, kPWaitPFull = 306, kPWaitOFull = 307, kPWaitOEmpty = 308, kPWaitEpi = 309,
+  kPWaitOutFree = 310, kPWaitOutFull = 311
 };
 
 // Work item -> (batch, head, pair).  Non-causal items of one head are adjacent
@@ -152,7 +161,8 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kPairThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                      const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, const AttnPairArgs pargs) {
+                     const __grid_constant__ CUtensorMap map_v,
+                     const __grid_constant__ CUtensorMap map_o, const AttnPairArgs pargs) {
   using S = AttnPairSmem<D>;
   const AttnFwdArgs& args = pargs.base;
   constexpr int kIsBf16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
@@ -179,6 +189,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(bar(S::kBarPFullHi + x), 128);
       mbar_init(bar(S::kBarOFull + x), 1);
       mbar_init(bar(S::kBarOEmpty + x), 128);
+      mbar_init(bar(S::kBarOutFree + x), 1);
+      mbar_init(bar(S::kBarOutFull + x), 128);
     }
     for (int s = 0; s < kPairStages; ++s) {
       mbar_init(bar(S::kBarKVFull + s), 1);
@@ -208,6 +220,36 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       uint32_t stage = 0, phase = 0;      // ring position; phase of the stage's barriers
       uint32_t q_uses[2] = {0, 0};        // loads issued so far into Q buffer x
       bool ok = true;
+      // One K (kv = 0) or V (kv = 1) tile of 128 keys starting at key0: loaded
+      // into shared memory at dst (signalling `full`), or, with dst == 0, only
+      // brought into L2.
+      auto kv_tile = [&](int kv, int key0, int b, int h, uint32_t dst, uint32_t full) {
+        const bool natural = kv == 0 ? !args.k_mn_major : (args.v_mn_major != 0);
+        const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
+        if (pargs.page_size > 0) {
+          // paged cache (always the row-per-key layout): outer coordinate = page
+          if (dst == 0) return;
+          const int pg = key0 / pargs.page_size;
+          const int page = pargs.block_table[(long long)b * pargs.max_pages + pg];
+#pragma unroll
+          for (int blk = 0; blk < kBlocks; ++blk)
+            tma_load_4d(dst + blk * S::kBlockBytes, map, full, blk * 64, key0 - pg * pargs.page_size, h, page);
+        } else if (natural) {
+          // rows = keys, 64 head-dim elements per swizzle block
+#pragma unroll
+          for (int blk = 0; blk < kBlocks; ++blk) {
+            if (dst != 0) tma_load_4d(dst + blk * S::kBlockBytes, map, full, blk * 64, key0, h, b);
+            else tma_prefetch_l2_4d(map, blk * 64, key0, h, b);
+          }
+        } else {
+          // rows = head dim, 64 keys per swizzle block
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            if (dst != 0) tma_load_4d(dst + blk * (D * 128), map, full, key0 + blk * 64, 0, h, b);
+            else tma_prefetch_l2_4d(map, key0 + blk * 64, 0, h, b);
+          }
+        }
+      };
       for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
         int b, h, pair, split, j0, j0_unused;
         pair_item(pargs, item, b, h, pair, split);
@@ -227,34 +269,31 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                         bar(S::kBarQFull + x), blk * 64, q0 + x * kAttnTile, h, b);
           ++q_uses[x];
         }
+        // The next item of this CTA usually belongs to another head: bring its Q
+        // tiles and its first K and V tiles into L2 now, so that the loads at the
+        // item boundary (which cannot be issued earlier: the Q buffers and the
+        // ring are in use) do not wait for HBM.
+        if (pargs.kv_splits == 0 && item + (int)gridDim.x < pargs.n_items) {
+          int b2, h2, pair2, split2;
+          pair_item(pargs, item + gridDim.x, b2, h2, pair2, split2);
+          const int q2 = pair2 * 2 * kAttnTile;
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            if (q2 + x * kAttnTile >= args.len_q) continue;
+#pragma unroll
+            for (int blk = 0; blk < kBlocks; ++blk)
+              tma_prefetch_l2_4d(&map_q, blk * 64, q2 + x * kAttnTile, h2, b2);
+          }
+          kv_tile(0, 0, b2, h2, 0, 0);
+          kv_tile(1, 0, b2, h2, 0, 0);
+        }
         for (int j = 0; ok && j < n; ++j) {
           for (int kv = 0; kv < 2; ++kv) {
             ok = mbar_wait(bar(S::kBarKVEmpty + stage), phase ^ 1, abort_flag, kPWaitKVEmpty);
             if (!ok) break;
-            const uint32_t dst = smem_base + S::kOffKV + stage * S::kTileBytes;
             const uint32_t full = bar(S::kBarKVFull + stage);
             mbar_arrive_expect_tx(full, S::kTileBytes);
-            const bool natural = kv == 0 ? !args.k_mn_major : (args.v_mn_major != 0);
-            const CUtensorMap* map = kv == 0 ? &map_k : &map_v;
-            if (pargs.page_size > 0) {
-              // paged cache (always the row-per-key layout): outer coordinate = page
-              const int key0 = (j0 + j) * kAttnTile;
-              const int pg = key0 / pargs.page_size;
-              const int page = pargs.block_table[(long long)b * pargs.max_pages + pg];
-#pragma unroll
-              for (int blk = 0; blk < kBlocks; ++blk)
-                tma_load_4d(dst + blk * S::kBlockBytes, map, full, blk * 64, key0 - pg * pargs.page_size, h, page);
-            } else if (natural) {
-              // rows = keys, 64 head-dim elements per swizzle block
-#pragma unroll
-              for (int blk = 0; blk < kBlocks; ++blk)
-                tma_load_4d(dst + blk * S::kBlockBytes, map, full, blk * 64, (j0 + j) * kAttnTile, h, b);
-            } else {
-              // rows = head dim, 64 keys per swizzle block
-#pragma unroll
-              for (int blk = 0; blk < 2; ++blk)
-                tma_load_4d(dst + blk * (D * 128), map, full, (j0 + j) * kAttnTile + blk * 64, 0, h, b);
-            }
+            kv_tile(kv, (j0 + j) * kAttnTile, b, h, smem_base + S::kOffKV + stage * S::kTileBytes, full);
             if (++stage == kPairStages) {
               stage = 0;
               phase ^= 1;
@@ -340,6 +379,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         const int nx[2] = {kv_tiles_for(pargs, q0, split, j0_unused),
                            kv_tiles_for(pargs, q0 + kAttnTile, split, j0_unused)};
         const int n = max(nx[0], nx[1]);
+        PAIR_TRACE(8, tn, 16, 0);
         for (int x = 0; x < 2 && ok; ++x) {
           if (nx[x] == 0) continue;
           ok = mbar_wait_warp(bar(S::kBarQFull + x), q_cnt[x] & 1, abort_flag, kPWaitQFull);
@@ -347,9 +387,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         if (!ok) break;
         uint32_t k_smem = 0, k_stage = 0, v_smem = 0, v_stage = 0;
+        PAIR_TRACE(8, tn, 17, 0);
         ok = next_stage(k_smem, k_stage);
         if (!ok) break;
         tc_fence_after();
+        PAIR_TRACE(8, tn, 18, 0);
         for (int x = 0; x < 2; ++x) {
           if (nx[x] == 0) continue;
           issue_s(x, k_smem);
@@ -411,6 +453,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t bar_p_hi = bar(S::kBarPFullHi + x);
     const uint32_t bar_o = bar(S::kBarOFull + x), bar_oe = bar(S::kBarOEmpty + x);
     uint32_t s_cnt = 0;      // S tiles consumed
+    uint32_t out_cnt = 0;    // items whose output went through the staging buffer
     uint32_t o_base = 0;     // PV completions of earlier items
     bool ok = true;
 #ifdef TF_PAIR_TRACE
@@ -438,8 +481,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         tc_fence_after();
         SM_TRACE(0, j);
 
-        // Load S in four 32-column chunks; the row maximum of a chunk is taken
-        // while the next chunk is still in flight.
+        // Load the whole S row (four 32-column chunks) into registers.
         const int kv0 = (j0 + j) * kAttnTile;
         const bool need_mask =
             (kv0 + kAttnTile > args.len_kv) || (args.causal && (kv0 + kAttnTile - 1 > q0));
@@ -449,9 +491,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + col_s + c * 32, sr[c]);
         tmem_wait_ld();
         SM_TRACE(4, j);
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if (need_mask) {
+          for (int c = 0; c < 4; ++c) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int col = kv0 + c * 32 + i;
@@ -459,14 +501,27 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
               if (masked) sr[c][i] = 0xff800000u;  // -inf
             }
           }
-          float m0 = max3(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
-          float m1 = max3(__uint_as_float(sr[c][3]), __uint_as_float(sr[c][4]), __uint_as_float(sr[c][5]));
+        }
+        // Row maximum: eight independent chains (two per chunk) in one straight
+        // line of code, so that the 3-input max instructions pipeline.
+        {
+          float ma[4], mb[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            ma[c] = max3(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
+            mb[c] = max3(__uint_as_float(sr[c][3]), __uint_as_float(sr[c][4]), __uint_as_float(sr[c][5]));
+          }
 #pragma unroll
           for (int i = 6; i + 3 < 32; i += 4) {
-            m0 = max3(m0, __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
-            m1 = max3(m1, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              ma[c] = max3(ma[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+              mb[c] = max3(mb[c], __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+            }
           }
-          mx[c] = max3(m0, m1, fmaxf(__uint_as_float(sr[c][30]), __uint_as_float(sr[c][31])));
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            mx[c] = max3(ma[c], mb[c], fmaxf(__uint_as_float(sr[c][30]), __uint_as_float(sr[c][31])));
         }
         const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         SM_TRACE(1, j);
@@ -500,9 +555,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
 
-        // P = 2^(s*scale - m): kPairEmuPer8 of every 8 exponentials run on the FMA
-        // pipe, the rest on the MUFU.  P is published in two halves so that the
-        // first four P.V MMAs start while the second half is still being computed.
+        // P = 2^(s*scale - m) on the MUFU (an FMA-pipe polynomial for part of the
+        // scores measured slower in this kernel), written as 16-bit over the start
+        // of S.  P is published in two halves.
         const float m_scaled = m_used * args.scale_log2;
         const uint64_t scale2 = f2_pack(args.scale_log2, args.scale_log2);
         const uint64_t negm2 = f2_pack(-m_scaled, -m_scaled);
@@ -515,14 +570,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
             float x0, x1;
             f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2),
                       x0, x1);
-            // element pairs (i, i+1) with (i & 7) < kPairEmuPer8 take the polynomial
-            float p0, p1;
-            if ((i & 7) < kPairEmuPer8) {
-              poly_exp2_x2(x0, x1, p0, p1);
-            } else {
-              p0 = fast_exp2(x0);
-              p1 = fast_exp2(x1);
-            }
+            const float p0 = fast_exp2(x0);
+            const float p1 = fast_exp2(x1);
             ls2[(i >> 1) & 3] = f2_add(ls2[(i >> 1) & 3], f2_pack(p0, p1));
             pk[i >> 1] = pack2<T>(p0, p1);
           }
@@ -550,6 +599,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       if (!ok) break;
       o_base += n_kv;
       tc_fence_after();
+      SM_TRACE(5, n_kv);
       const float inv_l = 1.0f / l_run;
       const bool row_valid = q_idx < args.len_q;
       if (pargs.kv_splits > 0) {
@@ -580,6 +630,55 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         continue;
       }
+      if (pargs.tma_store) {
+        // O leaves through shared memory: each thread writes its row of the
+        // 16-bit tile in the 128-byte-swizzle layout of the tensor map (16-byte
+        // unit u of row r sits at unit u ^ (r & 7) of its 128-byte line, which
+        // also keeps the writes of a warp free of bank conflicts), then one
+        // thread issues a TMA store per 64-column block.  Rows past len_q are
+        // clipped by the store.
+        const uint32_t stage_out = smem_base + S::kOffOut + x * S::kTileBytes;
+        if (row == 0) {
+          bulk_wait_group_read0();                   // the previous item's store has read the buffer
+          mbar_arrive(bar(S::kBarOutFree + x));
+        }
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(S::kBarOutFree + x), out_cnt & 1, abort_flag, kPWaitOutFree));
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t orow[32];
+          tmem_ld32(t_lane + col_o + c * 32, orow);
+          tmem_wait_ld();
+          if (c == D / 32 - 1) {
+            // O_x has been read out: the next item's first P V may overwrite it
+            tc_fence_before();
+            mbar_arrive(bar_oe);
+          }
+          const uint32_t line = stage_out + (c >> 1) * S::kBlockBytes + row * 128;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint32_t w0 = pack2<T>(__uint_as_float(orow[v * 8 + 0]) * inv_l, __uint_as_float(orow[v * 8 + 1]) * inv_l);
+            const uint32_t w1 = pack2<T>(__uint_as_float(orow[v * 8 + 2]) * inv_l, __uint_as_float(orow[v * 8 + 3]) * inv_l);
+            const uint32_t w2 = pack2<T>(__uint_as_float(orow[v * 8 + 4]) * inv_l, __uint_as_float(orow[v * 8 + 5]) * inv_l);
+            const uint32_t w3 = pack2<T>(__uint_as_float(orow[v * 8 + 6]) * inv_l, __uint_as_float(orow[v * 8 + 7]) * inv_l);
+            const uint32_t unit = (uint32_t)((c & 1) * 4 + v) ^ (uint32_t)(row & 7);
+            st_shared_v4(line + (unit << 4), w0, w1, w2, w3);
+          }
+        }
+        fence_proxy_async_smem();                    // my writes are visible to the TMA engine
+        mbar_arrive(bar(S::kBarOutFull + x));
+        if (warp == 4 * x) {
+          ok = mbar_wait_warp(bar(S::kBarOutFull + x), out_cnt & 1, abort_flag, kPWaitOutFull);
+          if (!ok) break;
+        }
+        ++out_cnt;
+        if (row == 0) {
+#pragma unroll
+          for (int blk = 0; blk < kBlocks; ++blk)
+            tma_store_4d(&map_o, stage_out + blk * S::kBlockBytes, blk * 64, q0, h, b);
+          bulk_commit_group();
+        }
+      } else {
       T* o_row = reinterpret_cast<T*>(args.o) + (long long)b * args.o_stride_b +
                  (long long)h * args.o_stride_h + (long long)q_idx * args.o_stride_l;
 #pragma unroll
@@ -608,14 +707,18 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
       }
+      }
       if (row_valid && args.lse != nullptr) {
         args.lse[(long long)b * args.lse_stride_b + (long long)h * args.lse_stride_h + q_idx] =
             0.6931471805599453f * (m_used * args.scale_log2 + log2f(l_run));
       }
+      SM_TRACE(6, n_kv);
     }
   }
 
   // ---------------------------------------------------------------- teardown --
+  // (threads that issued TMA stores wait for them; a no-op for the others)
+  bulk_wait_group0();
   tc_fence_before();
   __syncthreads();
   if (warp == 8) {

@@ -151,6 +151,39 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
+// Brings the box at these coordinates into L2 only (no shared-memory
+// destination, no barrier); same alignment rule for c0 as a load.
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(map),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
+// 4-D tiled tensor store shared -> global (rows and columns outside the
+// tensor are clipped); completion is tracked by the issuing thread's bulk
+// async-groups.  Coordinates must not be negative.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1,
+                                             int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+               "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// All bulk groups of this thread have finished READING shared memory.
+__device__ __forceinline__ void bulk_wait_group_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// All bulk groups of this thread are complete (writes performed).
+__device__ __forceinline__ void bulk_wait_group0() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // ----------------------------------------------------------------- tcgen05 --
 template <int kCols>
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem) {
@@ -383,30 +416,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
-}
-
-// 2^x on the FMA pipe (no MUFU) for a packed pair: round-to-nearest split
-// x = n + f with |f| <= 0.5 (adding 1.5 * 2^23 leaves n in the low mantissa
-// bits), a degree-3 minimax polynomial for 2^f (relative error 7.5e-5), and n
-// added into the exponent field.  Inputs below -125 (masked scores) return
-// ~2^-125, which rounds to zero in 16-bit P and is negligible in the fp32 row
-// sum.  The additions and the polynomial run as f32x2 instructions.
-__device__ __forceinline__ void poly_exp2_x2(float x0, float x1, float& r0, float& r1) {
-  const uint64_t x2 = f2_pack(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
-  const uint64_t magic = f2_pack(12582912.0f, 12582912.0f);
-  const uint64_t neg_magic = f2_pack(-12582912.0f, -12582912.0f);
-  const uint64_t t2 = f2_add(x2, magic);
-  const uint64_t n2 = f2_add(t2, neg_magic);
-  // f = x - n  (as x + (-1) * n)
-  const uint64_t f2 = f2_fma(n2, f2_pack(-1.0f, -1.0f), x2);
-  uint64_t p2 = f2_fma(f2, f2_pack(0.0551716648f, 0.0551716648f), f2_pack(0.2426111251f, 0.2426111251f));
-  p2 = f2_fma(p2, f2, f2_pack(0.6932609677f, 0.6932609677f));
-  p2 = f2_fma(p2, f2, f2_pack(0.9999280572f, 0.9999280572f));
-  float p0, p1, t0, t1;
-  f2_unpack(p2, p0, p1);
-  f2_unpack(t2, t0, t1);
-  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
 template <typename T>
