@@ -756,6 +756,9 @@ int tf_abi_version(void) { return 3; }
 __attribute__((visibility("default"))) int tf_debug_pair_trace(unsigned long long* out) {
   return (int)cudaMemcpyFromSymbol(out, tfb::g_pair_trace, sizeof(unsigned long long) * 9 * 1024);
 }
+__attribute__((visibility("default"))) int tf_debug_pair_cta_time(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, tfb::g_pair_cta_time, sizeof(unsigned long long) * 256 * 4);
+}
 #endif
 
 }  // extern "C"

@@ -52,6 +52,7 @@ constexpr int kPairStages = 3;        // K/V ring (a deeper ring measured slower
 // Optional phase trace of CTA 0 (debug builds only, -DTF_PAIR_TRACE): one
 // thread per role appends (event, tile, clock) records to a device array.
 #ifdef TF_PAIR_TRACE
+__device__ unsigned long long g_pair_cta_time[256][4];   // per CTA: globaltimer start/end, clock64 start/end
 __device__ unsigned long long g_pair_trace[9][1024];
 __device__ __forceinline__ void pair_trace(int role, int& n, int event, int tile) {
   if (blockIdx.x == 0 && n < 1024)
@@ -179,6 +180,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
+#ifdef TF_PAIR_TRACE
+  if (threadIdx.x == 0 && blockIdx.x < 256) {
+    g_pair_cta_time[blockIdx.x][0] = global_timer_ns();
+    g_pair_cta_time[blockIdx.x][2] = clock64();
+  }
+#endif
 
   if (threadIdx.x == 0) {
     for (int x = 0; x < 2; ++x) {
@@ -644,23 +651,23 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         ok = __all_sync(0xffffffffu, mbar_wait(bar(S::kBarOutFree + x), out_cnt & 1, abort_flag, kPWaitOutFree));
         if (!ok) break;
+        // (all of O_x is read with one wait: the S registers are free by now)
+        uint32_t orow[D / 32][32];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld32(t_lane + col_o + c * 32, orow[c]);
+        tmem_wait_ld();
+        // O_x has been read out: the next item's first P V may overwrite it
+        tc_fence_before();
+        mbar_arrive(bar_oe);
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          uint32_t orow[32];
-          tmem_ld32(t_lane + col_o + c * 32, orow);
-          tmem_wait_ld();
-          if (c == D / 32 - 1) {
-            // O_x has been read out: the next item's first P V may overwrite it
-            tc_fence_before();
-            mbar_arrive(bar_oe);
-          }
           const uint32_t line = stage_out + (c >> 1) * S::kBlockBytes + row * 128;
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            const uint32_t w0 = pack2<T>(__uint_as_float(orow[v * 8 + 0]) * inv_l, __uint_as_float(orow[v * 8 + 1]) * inv_l);
-            const uint32_t w1 = pack2<T>(__uint_as_float(orow[v * 8 + 2]) * inv_l, __uint_as_float(orow[v * 8 + 3]) * inv_l);
-            const uint32_t w2 = pack2<T>(__uint_as_float(orow[v * 8 + 4]) * inv_l, __uint_as_float(orow[v * 8 + 5]) * inv_l);
-            const uint32_t w3 = pack2<T>(__uint_as_float(orow[v * 8 + 6]) * inv_l, __uint_as_float(orow[v * 8 + 7]) * inv_l);
+            const uint32_t w0 = pack2<T>(__uint_as_float(orow[c][v * 8 + 0]) * inv_l, __uint_as_float(orow[c][v * 8 + 1]) * inv_l);
+            const uint32_t w1 = pack2<T>(__uint_as_float(orow[c][v * 8 + 2]) * inv_l, __uint_as_float(orow[c][v * 8 + 3]) * inv_l);
+            const uint32_t w2 = pack2<T>(__uint_as_float(orow[c][v * 8 + 4]) * inv_l, __uint_as_float(orow[c][v * 8 + 5]) * inv_l);
+            const uint32_t w3 = pack2<T>(__uint_as_float(orow[c][v * 8 + 6]) * inv_l, __uint_as_float(orow[c][v * 8 + 7]) * inv_l);
             const uint32_t unit = (uint32_t)((c & 1) * 4 + v) ^ (uint32_t)(row & 7);
             st_shared_v4(line + (unit << 4), w0, w1, w2, w3);
           }
@@ -725,6 +732,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     __syncwarp();
     tmem_dealloc<kTmemCols>(tmem_base);
   }
+#ifdef TF_PAIR_TRACE
+  if (threadIdx.x == 0 && blockIdx.x < 256) {
+    g_pair_cta_time[blockIdx.x][1] = global_timer_ns();
+    g_pair_cta_time[blockIdx.x][3] = clock64();
+  }
+#endif
 }
 
 }  // namespace tfb
