@@ -141,6 +141,34 @@ def test_large_scores_exercise_rescale(tile_q):
     _check(o, lse, ref, lse_ref, torch.float16)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("offset", [10, 80, 127], ids=["first_half", "second_half", "last_key"])
+@pytest.mark.parametrize("tile_q", TILE_Q)
+def test_score_jump_inside_a_later_tile(tile_q, offset, dtype):
+    """A few keys deep inside the third KV tile score 2^20 and more above everything
+    before them (for half of the query rows; far below for the other half).  The
+    two-tile kernel computes later tiles under the maximum carried over and only
+    looks for a new one when the sum of a half tile is out of range: the jump has
+    to be caught before P is published, in the first and in the second half."""
+    from cabi_helpers import attn_fwd, device_status
+
+    b, h, lq, lk, d = 1, 2, 384, 640, 128
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(b, h, lq, d, generator=g) * 0.1
+    sign = torch.where(torch.arange(lq) % 2 == 0, 1.0, -1.0).view(1, 1, lq, 1)
+    q = q + sign * 0.5                      # rows alternate between +0.5 and -0.5 on every dim
+    k = torch.randn(b, h, lk, d, generator=g) * 0.1
+    for pos, val in ((2 * 128 + offset, 0.5), (4 * 128 + offset, 1.0)):
+        k[:, :, pos] += val                 # q.k jumps by about +-32 and +-64 at these keys
+    v = torch.randn(b, h, lk, d, generator=g)
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    scale = 1.0
+    o, lse = attn_fwd(q.cuda(), k.cuda(), v.cuda(), scale, False, tile_q=tile_q)
+    ref, lse_ref = orc.attention_fp32(q, k, v, scale, False)
+    _check(o, lse, ref, lse_ref, dtype)
+    assert device_status() == 0
+
+
 @pytest.mark.parametrize("tile_q", TILE_Q)
 def test_strided_views_need_no_copy(tile_q):
     """Q/K/V/O as slices of packed [B, L, 3, H, D] / [B, L, H, D] buffers."""

@@ -43,11 +43,11 @@ constexpr int kPairRegsIssue = 88;
 // raise that does not fit into what the other warpgroups gave up blocks forever.
 static_assert(2 * kPairRegsSoftmax + kPairRegsIssue <= 3 * 168, "register split exceeds the CTA's allocation");
 constexpr int kPairStages = 3;        // K/V ring (a deeper ring measured slower)
-// Publish P in two halves: the first four P.V MMAs start while the second
-// half of the exponentials is still being computed.
-#ifndef TF_PAIR_SPLIT_P
-#define TF_PAIR_SPLIT_P 1
+#ifndef TF_PAIR_ALWAYS_MAX
+#define TF_PAIR_ALWAYS_MAX 0          // 1: take the row maximum of every tile (comparison builds)
 #endif
+// Largest sum of 64 values of P published without a look at the row maximum.
+constexpr float kPairSumLimit = 4096.0f;
 
 // Optional phase trace of CTA 0 (debug builds only, -DTF_PAIR_TRACE): one
 // thread per role appends (event, tile, clock) records to a device array.
@@ -106,9 +106,10 @@ struct AttnPairSmem {
   static constexpr int kBarPFullHi = 12;   // [2]  second half of P (keys 64..127)
   static constexpr int kBarOutFree = 14;   // [2]  output staging of tile x may be overwritten
   static constexpr int kBarOutFull = 16;   // [2]  all 128 rows of tile x are in the staging buffer
-  static constexpr int kBarKVFull = 18;    // [kPairStages]
-  static constexpr int kBarKVEmpty = 18 + kPairStages;
-  static constexpr int kNumBars = 18 + 2 * kPairStages;
+  static constexpr int kBarOLoFull = 18;   // [2]  P.V MMAs of the first half of a tile are complete
+  static constexpr int kBarKVFull = 20;    // [kPairStages]
+  static constexpr int kBarKVEmpty = 20 + kPairStages;
+  static constexpr int kNumBars = 20 + 2 * kPairStages;
   static constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 4;
   static constexpr int kBytes = kOffAbort + 4 + 1024;               // + slack for 1024-B alignment
@@ -195,6 +196,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(bar(S::kBarPFull + x), 128);
       mbar_init(bar(S::kBarPFullHi + x), 128);
       mbar_init(bar(S::kBarOFull + x), 1);
+      mbar_init(bar(S::kBarOLoFull + x), 1);
       mbar_init(bar(S::kBarOEmpty + x), 128);
       mbar_init(bar(S::kBarOutFree + x), 1);
       mbar_init(bar(S::kBarOutFull + x), 128);
@@ -365,7 +367,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                        b0 + (k >> 2) * v_step_hi + (k & 3) * v_step_lo, kDescHiSw128, idesc_o,
                        accumulate || (k > 0));
         }
-        if (half == 1) umma_commit(bar(S::kBarOFull + x));
+        umma_commit(bar((half == 0 ? S::kBarOLoFull : S::kBarOFull) + x));
       };
       // Waits for the next ring stage and returns its shared-memory address.
       auto next_stage = [&](uint32_t& smem_addr, uint32_t& stage_idx) -> bool {
@@ -459,6 +461,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t bar_s = bar(S::kBarSFull + x), bar_p = bar(S::kBarPFull + x);
     const uint32_t bar_p_hi = bar(S::kBarPFullHi + x);
     const uint32_t bar_o = bar(S::kBarOFull + x), bar_oe = bar(S::kBarOEmpty + x);
+    const uint32_t bar_o_lo = bar(S::kBarOLoFull + x);
     uint32_t s_cnt = 0;      // S tiles consumed
     uint32_t out_cnt = 0;    // items whose output went through the staging buffer
     uint32_t o_base = 0;     // PV completions of earlier items
@@ -493,7 +496,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         const bool need_mask =
             (kv0 + kAttnTile > args.len_kv) || (args.causal && (kv0 + kAttnTile - 1 > q0));
         uint32_t sr[4][32];
-        float mx[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + col_s + c * 32, sr[c]);
         tmem_wait_ld();
@@ -509,12 +511,13 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
             }
           }
         }
-        // Row maximum: eight independent chains (two per chunk) in one straight
-        // line of code, so that the 3-input max instructions pipeline.
-        {
+        // Row maximum over chunks [c0, c1): two independent chains per chunk in
+        // one straight line of code, so that the 3-input max instructions pipeline.
+        auto row_max = [&](int c0, int c1) -> float {
           float ma[4], mb[4];
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
+            if (c < c0 || c >= c1) continue;
             ma[c] = max3(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
             mb[c] = max3(__uint_as_float(sr[c][3]), __uint_as_float(sr[c][4]), __uint_as_float(sr[c][5]));
           }
@@ -522,82 +525,127 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           for (int i = 6; i + 3 < 32; i += 4) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
+              if (c < c0 || c >= c1) continue;
               ma[c] = max3(ma[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
               mb[c] = max3(mb[c], __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
             }
           }
+          float m = -INFINITY;
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            mx[c] = max3(ma[c], mb[c], fmaxf(__uint_as_float(sr[c][30]), __uint_as_float(sr[c][31])));
-        }
-        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        SM_TRACE(1, j);
-
-        const bool grow = (m_tile - m_used) * args.scale_log2 > kRescaleThreshold;
-        if (__any_sync(0xffffffffu, grow)) {
-          const float m_new = fmaxf(m_used, m_tile);
+          for (int c = 0; c < 4; ++c) {
+            if (c < c0 || c >= c1) continue;
+            m = fmaxf(m, max3(ma[c], mb[c], fmaxf(__uint_as_float(sr[c][30]), __uint_as_float(sr[c][31]))));
+          }
+          return m;
+        };
+        // Raises the maximum in use to at least m_seen and rescales what has been
+        // accumulated under the old one: the running sum, `extra` (a partial sum
+        // of this tile) and, once the P.V MMAs counted by `o_parity` on `o_bar`
+        // are complete, O in TMEM.
+        auto raise_max = [&](float m_seen, float& extra, bool rescale_o, uint32_t o_bar, uint32_t o_parity,
+                             int code) -> bool {
+          const float m_new = fmaxf(m_used, m_seen);
           const float alpha = fast_exp2((m_used - m_new) * args.scale_log2);
           m_used = m_new;
           l_run *= alpha;
-          if (j > 0) {
-            ok = __all_sync(0xffffffffu,
-                            mbar_wait(bar_o, (o_base + j - 1) & 1, abort_flag, kPWaitOFull));
-            if (!ok) break;
-            tc_fence_after();
+          extra *= alpha;
+          if (!rescale_o) return true;
+          if (!__all_sync(0xffffffffu, mbar_wait(o_bar, o_parity, abort_flag, code))) return false;
+          tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < D / 16; ++c) {
-              uint32_t orow[16];
-              tmem_ld16(t_lane + col_o + c * 16, orow);
-              tmem_wait_ld();
-              const uint64_t alpha2 = f2_pack(alpha, alpha);
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t orow[16];
+            tmem_ld16(t_lane + col_o + c * 16, orow);
+            tmem_wait_ld();
+            const uint64_t alpha2 = f2_pack(alpha, alpha);
 #pragma unroll
-              for (int i = 0; i < 16; i += 2) {
-                float lo, hi;
-                f2_unpack(f2_mul(f2_pack(__uint_as_float(orow[i]), __uint_as_float(orow[i + 1])), alpha2), lo, hi);
-                orow[i] = __float_as_uint(lo);
-                orow[i + 1] = __float_as_uint(hi);
-              }
-              tmem_st16(t_lane + col_o + c * 16, orow);
+            for (int i = 0; i < 16; i += 2) {
+              float lo, hi;
+              f2_unpack(f2_mul(f2_pack(__uint_as_float(orow[i]), __uint_as_float(orow[i + 1])), alpha2), lo, hi);
+              orow[i] = __float_as_uint(lo);
+              orow[i + 1] = __float_as_uint(hi);
             }
+            tmem_st16(t_lane + col_o + c * 16, orow);
           }
-        }
-
-        // P = 2^(s*scale - m) on the MUFU (an FMA-pipe polynomial for part of the
-        // scores measured slower in this kernel), written as 16-bit over the start
-        // of S.  P is published in two halves.
-        const float m_scaled = m_used * args.scale_log2;
+          return true;
+        };
+        // P = 2^(s*scale - m) for 64 keys (chunks 2*half, 2*half + 1) on the MUFU
+        // (an FMA-pipe polynomial for part of the scores measured slower in this
+        // kernel), written as 16-bit over the start of S; returns their sum.
         const uint64_t scale2 = f2_pack(args.scale_log2, args.scale_log2);
-        const uint64_t negm2 = f2_pack(-m_scaled, -m_scaled);
-        uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};      // four packed (even, odd) partial row sums
+        auto p_half = [&](int half) -> float {
+          const float m_scaled = m_used * args.scale_log2;
+          const uint64_t negm2 = f2_pack(-m_scaled, -m_scaled);
+          uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};    // four packed (even, odd) partial sums
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = 2 * half + cc;
+            uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0, x1;
-            f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2),
-                      x0, x1);
-            const float p0 = fast_exp2(x0);
-            const float p1 = fast_exp2(x1);
-            ls2[(i >> 1) & 3] = f2_add(ls2[(i >> 1) & 3], f2_pack(p0, p1));
-            pk[i >> 1] = pack2<T>(p0, p1);
+            for (int i = 0; i < 32; i += 2) {
+              float x0, x1;
+              f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2),
+                        x0, x1);
+              const float p0 = fast_exp2(x0);
+              const float p1 = fast_exp2(x1);
+              ls2[(i >> 1) & 3] = f2_add(ls2[(i >> 1) & 3], f2_pack(p0, p1));
+              pk[i >> 1] = pack2<T>(p0, p1);
+            }
+            tmem_st16(t_lane + col_p + c * 16, pk);
           }
-          tmem_st16(t_lane + col_p + c * 16, pk);
-          if ((TF_PAIR_SPLIT_P && c == 1) || c == 3) {
-            tmem_wait_st();
-            tc_fence_before();
-            if (c == 1 || !TF_PAIR_SPLIT_P) mbar_arrive(bar_p);
-            if (c == 3) mbar_arrive(bar_p_hi);
-            SM_TRACE(2 + (c >> 1), j);
-          }
-        }
-        float ls[4];
-        {
           float lo, hi;
           f2_unpack(f2_add(f2_add(ls2[0], ls2[1]), f2_add(ls2[2], ls2[3])), lo, hi);
-          ls[0] = lo; ls[1] = hi; ls[2] = 0.f; ls[3] = 0.f;
+          return lo + hi;
+        };
+
+        // The first tile of an item takes its row maximum before anything else.
+        // Later tiles skip that pass: they compute P under the maximum in use and
+        // look at the sum of each half before publishing it.  Every P is >= 0, so
+        // a sum within kPairSumLimit bounds each of them (far below the 16-bit
+        // overflow), and O and the running sum stay exact after the final 1/l
+        // whatever maximum was in use.  A larger sum (or a NaN) means the
+        // maximum in use is stale by more than the limit allows: only then is the
+        // half's true maximum taken, the accumulated state rescaled and the half
+        // computed again.  Nothing is published before its sum has passed.
+        float no_extra = 0.f;
+        if (j == 0) {
+          ok = raise_max(row_max(0, 4), no_extra, false, 0, 0, 0);
+          SM_TRACE(1, j);
+        } else if (TF_PAIR_ALWAYS_MAX) {
+          // (comparison build: the row maximum of every tile, rescale when it grew by 2^8)
+          const float m_tile = row_max(0, 4);
+          if (__any_sync(0xffffffffu, (m_tile - m_used) * args.scale_log2 > kRescaleThreshold)) {
+            ok = raise_max(m_tile, no_extra, true, bar_o, (o_base + j - 1) & 1, kPWaitOFull);
+            if (!ok) break;
+          }
+          SM_TRACE(1, j);
         }
-        l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        float lo_sum = p_half(0);
+        if (j > 0 && __any_sync(0xffffffffu, !(lo_sum <= kPairSumLimit))) {
+          ok = raise_max(row_max(0, 4), no_extra, true, bar_o, (o_base + j - 1) & 1, kPWaitOFull);
+          if (!ok) break;
+          tmem_wait_st();            // the discarded half must not land after the new one
+          lo_sum = p_half(0);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p);
+        SM_TRACE(2, j);
+        float hi_sum = p_half(1);
+        if (j > 0 && __any_sync(0xffffffffu, !(hi_sum <= kPairSumLimit))) {
+          // P.V of the first half (this tile) is in flight or done: wait for it,
+          // then O holds everything accumulated so far and nothing else touches it
+          // until the second half is published.
+          ok = raise_max(row_max(2, 4), lo_sum, true, bar_o_lo, (o_base + j) & 1, kPWaitOFull);
+          if (!ok) break;
+          tmem_wait_st();
+          hi_sum = p_half(1);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p_hi);
+        SM_TRACE(3, j);
+        l_run += lo_sum + hi_sum;
       }
       if (!ok) break;
 
