@@ -121,27 +121,59 @@ enum AttnPairWaitCode {
   kPWaitOutFree = 310, kPWaitOutFull = 311
 };
 
-// Work item -> (batch, head, pair).  Non-causal items of one head are adjacent
-// (their K/V stay in L2); causal items are ordered heaviest pair first so that
-// the round-robin deal over CTAs is balanced.
-__device__ __forceinline__ void pair_item(const AttnPairArgs& a, int item, int& b, int& h, int& pair,
-                                          int& split) {
-  split = 0;
-  if (a.kv_splits > 0) {
-    split = item % a.kv_splits;
-    item /= a.kv_splits;
+// Work item -> (batch, head, pair, split).  Non-causal items of one head are
+// adjacent (their K/V stay in L2); causal items are ordered heaviest pair
+// first so that the round-robin deal over CTAs is balanced:
+//   non-causal:  item = ((b * heads + h) * n_pairs + pair) * splits + split
+//   causal:      item = ((n_pairs - 1 - pair) * batch * heads + b * heads + h) * splits + split
+// A CTA walks items blockIdx.x, blockIdx.x + gridDim.x, ...; the cursor keeps
+// the item as a mixed-radix number and adds the step digit by digit, so that
+// no role pays for integer divisions at an item boundary.
+struct PairCursor {
+  int d[4];   // digits, least significant first: split | pair or h | h or b | b or (n_pairs - 1 - pair)
+  int s[4];   // the step (gridDim.x) in the same radices
+  int r[3];   // radices of digits 0..2
+};
+
+__device__ __forceinline__ void cursor_init(const AttnPairArgs& a, int item0, int step, PairCursor& c) {
+  c.r[0] = a.kv_splits > 0 ? a.kv_splits : 1;
+  c.r[1] = a.base.causal ? a.heads : a.n_pairs;
+  c.r[2] = a.base.causal ? a.batch : a.heads;
+  int v = item0, w = step;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    c.d[i] = v % c.r[i];
+    v /= c.r[i];
+    c.s[i] = w % c.r[i];
+    w /= c.r[i];
   }
-  int bh;
+  c.d[3] = v;
+  c.s[3] = w;
+}
+
+__device__ __forceinline__ void cursor_next(PairCursor& c) {
+  int carry = 0;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    int v = c.d[i] + c.s[i] + carry;
+    carry = v >= c.r[i] ? 1 : 0;
+    c.d[i] = v - (carry ? c.r[i] : 0);
+  }
+  c.d[3] += c.s[3] + carry;
+}
+
+__device__ __forceinline__ void cursor_get(const AttnPairArgs& a, const PairCursor& c, int& b, int& h, int& pair,
+                                           int& split) {
+  split = c.d[0];
   if (a.base.causal) {
-    const int n_bh = a.batch * a.heads;
-    pair = a.n_pairs - 1 - item / n_bh;
-    bh = item % n_bh;
+    h = c.d[1];
+    b = c.d[2];
+    pair = a.n_pairs - 1 - c.d[3];
   } else {
-    bh = item / a.n_pairs;
-    pair = item - bh * a.n_pairs;
+    pair = c.d[1];
+    h = c.d[2];
+    b = c.d[3];
   }
-  b = bh / a.heads;
-  h = bh - b * a.heads;
 }
 
 // Number of KV tiles visited by Q tile x (rows q0 .. q0+127) of a pair; the
@@ -259,32 +291,44 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
       };
-      for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
+      PairCursor cur;
+      cursor_init(pargs, blockIdx.x, gridDim.x, cur);
+      for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x, cursor_next(cur)) {
         int b, h, pair, split, j0, j0_unused;
-        pair_item(pargs, item, b, h, pair, split);
+        cursor_get(pargs, cur, b, h, pair, split);
         const int q0 = pair * 2 * kAttnTile;
         const int n0 = kv_tiles_for(pargs, q0, split, j0);          // tile 0 always exists; it sets j0
         const int n1 = kv_tiles_for(pargs, q0 + kAttnTile, split, j0_unused);
         const int n = max(n0, n1);
-        for (int x = 0; x < 2 && ok; ++x) {
-          if ((x == 0 ? n0 : n1) == 0) continue;
-          if (q_uses[x] > 0)
-            ok = mbar_wait(bar(S::kBarQEmpty + x), (q_uses[x] - 1) & 1, abort_flag, kPWaitQEmpty);
-          if (!ok) break;
+        // Q tile x of this item into its buffer, once the last S MMA of the
+        // previous item has read the buffer.
+        auto load_q = [&](int x) -> bool {
+          if ((x == 0 ? n0 : n1) == 0) return true;
+          if (q_uses[x] > 0 &&
+              !mbar_wait(bar(S::kBarQEmpty + x), (q_uses[x] - 1) & 1, abort_flag, kPWaitQEmpty))
+            return false;
           mbar_arrive_expect_tx(bar(S::kBarQFull + x), S::kTileBytes);
 #pragma unroll
           for (int blk = 0; blk < kBlocks; ++blk)
             tma_load_4d(smem_base + S::kOffQ + x * S::kTileBytes + blk * S::kBlockBytes, &map_q,
                         bar(S::kBarQFull + x), blk * 64, q0 + x * kAttnTile, h, b);
           ++q_uses[x];
-        }
+          return true;
+        };
+        // Order: Q0, the first K tile, Q1, then the rest of the ring.  The MMA
+        // issuer starts this item's first S tile of Q tile 0 while Q tile 1 of
+        // the previous item is still in its last KV tile, and the buffer of Q1
+        // is released later than that of Q0.
+        ok = load_q(0);
         // The next item of this CTA usually belongs to another head: bring its Q
         // tiles and its first K and V tiles into L2 now, so that the loads at the
         // item boundary (which cannot be issued earlier: the Q buffers and the
         // ring are in use) do not wait for HBM.
         if (pargs.kv_splits == 0 && item + (int)gridDim.x < pargs.n_items) {
           int b2, h2, pair2, split2;
-          pair_item(pargs, item + gridDim.x, b2, h2, pair2, split2);
+          PairCursor nxt = cur;
+          cursor_next(nxt);
+          cursor_get(pargs, nxt, b2, h2, pair2, split2);
           const int q2 = pair2 * 2 * kAttnTile;
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
@@ -296,19 +340,20 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           kv_tile(0, 0, b2, h2, 0, 0);
           kv_tile(1, 0, b2, h2, 0, 0);
         }
-        for (int j = 0; ok && j < n; ++j) {
-          for (int kv = 0; kv < 2; ++kv) {
-            ok = mbar_wait(bar(S::kBarKVEmpty + stage), phase ^ 1, abort_flag, kPWaitKVEmpty);
-            if (!ok) break;
-            const uint32_t full = bar(S::kBarKVFull + stage);
-            mbar_arrive_expect_tx(full, S::kTileBytes);
-            kv_tile(kv, (j0 + j) * kAttnTile, b, h, smem_base + S::kOffKV + stage * S::kTileBytes, full);
-            if (++stage == kPairStages) {
-              stage = 0;
-              phase ^= 1;
-            }
+        for (int t = 0; ok && t < 2 * n; ++t) {
+          const int j = t >> 1, kv = t & 1;
+          ok = mbar_wait(bar(S::kBarKVEmpty + stage), phase ^ 1, abort_flag, kPWaitKVEmpty);
+          if (!ok) break;
+          const uint32_t full = bar(S::kBarKVFull + stage);
+          mbar_arrive_expect_tx(full, S::kTileBytes);
+          kv_tile(kv, (j0 + j) * kAttnTile, b, h, smem_base + S::kOffKV + stage * S::kTileBytes, full);
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1;
           }
+          if (t == 0) ok = load_q(1);
         }
+        if (ok && n == 0) ok = load_q(1);
       }
       if (!ok) {
         // let copies still in flight land before the CTA gives up its shared memory
@@ -329,6 +374,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       uint32_t q_cnt[2] = {0, 0};          // Q loads consumed per buffer
       uint32_t p_cnt[2] = {0, 0};          // P tiles consumed per Q tile
       uint32_t items_done[2] = {0, 0};     // epilogues awaited per Q tile
+      bool first_s_issued = false;         // the current item's first S tiles were issued during the previous item
       bool ok = true;
 #ifdef TF_PAIR_TRACE
       int tn = 0;
@@ -381,32 +427,49 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         return true;
       };
 
-      for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
+      PairCursor cur;
+      cursor_init(pargs, blockIdx.x, gridDim.x, cur);
+      for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x, cursor_next(cur)) {
         int b, h, pair, split, j0_unused;
-        pair_item(pargs, item, b, h, pair, split);
+        cursor_get(pargs, cur, b, h, pair, split);
         const int q0 = pair * 2 * kAttnTile;
         const int nx[2] = {kv_tiles_for(pargs, q0, split, j0_unused),
                            kv_tiles_for(pargs, q0 + kAttnTile, split, j0_unused)};
         const int n = max(nx[0], nx[1]);
+        // The first S tiles of the CTA's next item are issued during the last
+        // KV tile of this one (below), so that the tensor pipe and the softmax
+        // warps do not drain at the item boundary.
+        int nx2[2] = {0, 0};
+        if (item + (int)gridDim.x < pargs.n_items) {
+          int b2, h2, pair2, split2;
+          PairCursor nxt = cur;
+          cursor_next(nxt);
+          cursor_get(pargs, nxt, b2, h2, pair2, split2);
+          nx2[0] = kv_tiles_for(pargs, pair2 * 2 * kAttnTile, split2, j0_unused);
+          nx2[1] = kv_tiles_for(pargs, pair2 * 2 * kAttnTile + kAttnTile, split2, j0_unused);
+        }
         PAIR_TRACE(8, tn, 16, 0);
-        for (int x = 0; x < 2 && ok; ++x) {
-          if (nx[x] == 0) continue;
-          ok = mbar_wait_warp(bar(S::kBarQFull + x), q_cnt[x] & 1, abort_flag, kPWaitQFull);
-          ++q_cnt[x];
-        }
-        if (!ok) break;
         uint32_t k_smem = 0, k_stage = 0, v_smem = 0, v_stage = 0;
-        PAIR_TRACE(8, tn, 17, 0);
-        ok = next_stage(k_smem, k_stage);
-        if (!ok) break;
-        tc_fence_after();
-        PAIR_TRACE(8, tn, 18, 0);
-        for (int x = 0; x < 2; ++x) {
-          if (nx[x] == 0) continue;
-          issue_s(x, k_smem);
-          if (leader && (nx[x] == 1)) umma_commit(bar(S::kBarQEmpty + x));
+        if (!first_s_issued) {
+          // first item of this CTA: both first S tiles back to back
+          for (int x = 0; x < 2 && ok; ++x) {
+            if (nx[x] == 0) continue;
+            ok = mbar_wait_warp(bar(S::kBarQFull + x), q_cnt[x] & 1, abort_flag, kPWaitQFull);
+            ++q_cnt[x];
+          }
+          if (!ok) break;
+          PAIR_TRACE(8, tn, 17, 0);
+          ok = next_stage(k_smem, k_stage);
+          if (!ok) break;
+          tc_fence_after();
+          PAIR_TRACE(8, tn, 18, 0);
+          for (int x = 0; x < 2; ++x) {
+            if (nx[x] == 0) continue;
+            issue_s(x, k_smem);
+            if (leader && (nx[x] == 1)) umma_commit(bar(S::kBarQEmpty + x));
+          }
+          if (leader) umma_commit(bar(S::kBarKVEmpty + k_stage));
         }
-        if (leader) umma_commit(bar(S::kBarKVEmpty + k_stage));
 
         for (int j = 0; ok && j < n; ++j) {
           ok = next_stage(v_smem, v_stage);
@@ -441,12 +504,27 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
               issue_s(x, k_smem);
               PAIR_TRACE(8, tn, 14 + x, j);
               if (leader && (j + 2 == nx[x])) umma_commit(bar(S::kBarQEmpty + x));
+            } else if (j + 1 == n && nx2[x] > 0) {
+              // first S tile of the next item (its K tile is the next ring stage)
+              ok = mbar_wait_warp(bar(S::kBarQFull + x), q_cnt[x] & 1, abort_flag, kPWaitQFull);
+              if (!ok) break;
+              ++q_cnt[x];
+              if (!have_k) {
+                ok = next_stage(k_smem, k_stage);
+                if (!ok) break;
+                have_k = true;
+              }
+              tc_fence_after();
+              issue_s(x, k_smem);
+              PAIR_TRACE(8, tn, 14 + x, j);
+              if (leader && (nx2[x] == 1)) umma_commit(bar(S::kBarQEmpty + x));
             }
             if (leader && (x == 1 && have_k)) umma_commit(bar(S::kBarKVEmpty + k_stage));
           }
         }
         for (int x = 0; x < 2; ++x)
           if (nx[x] > 0) ++items_done[x];
+        first_s_issued = n > 0 && nx2[0] > 0;
       }
     }
    }   // warps 10 and 11 only donate registers
@@ -474,9 +552,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
 #define SM_TRACE(event, tile)
 #endif
 
-    for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x) {
+    PairCursor cur;
+    cursor_init(pargs, blockIdx.x, gridDim.x, cur);
+    for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x, cursor_next(cur)) {
       int b, h, pair, split, j0;
-      pair_item(pargs, item, b, h, pair, split);
+      cursor_get(pargs, cur, b, h, pair, split);
       const int q0 = pair * 2 * kAttnTile + x * kAttnTile;
       const int n_kv = kv_tiles_for(pargs, q0, split, j0);
       if (n_kv == 0) continue;
