@@ -42,7 +42,14 @@ constexpr int kPairRegsIssue = 88;
 // launched with 168 registers per thread (65536 / 384, rounded down to 8), and a
 // raise that does not fit into what the other warpgroups gave up blocks forever.
 static_assert(2 * kPairRegsSoftmax + kPairRegsIssue <= 3 * 168, "register split exceeds the CTA's allocation");
-constexpr int kPairStages = 3;        // K/V ring (a deeper ring measured slower)
+constexpr int kPairStages = 3;        // K/V ring of a prefill launch (a deeper ring measured slower)
+// In split-KV mode (decoding: K/V stream from HBM, nothing is staged for a TMA
+// store) the two output staging tiles, which follow the ring in shared memory,
+// serve as two more ring stages.
+constexpr int kPairMaxStages = kPairStages + 2;
+#ifndef TF_PAIR_STREAM
+#define TF_PAIR_STREAM 1              // 0: do not issue the next item's first S tiles early (comparison builds)
+#endif
 #ifndef TF_PAIR_ALWAYS_MAX
 #define TF_PAIR_ALWAYS_MAX 0          // 1: take the row maximum of every tile (comparison builds)
 #endif
@@ -107,9 +114,9 @@ struct AttnPairSmem {
   static constexpr int kBarOutFree = 14;   // [2]  output staging of tile x may be overwritten
   static constexpr int kBarOutFull = 16;   // [2]  all 128 rows of tile x are in the staging buffer
   static constexpr int kBarOLoFull = 18;   // [2]  P.V MMAs of the first half of a tile are complete
-  static constexpr int kBarKVFull = 20;    // [kPairStages]
-  static constexpr int kBarKVEmpty = 20 + kPairStages;
-  static constexpr int kNumBars = 20 + 2 * kPairStages;
+  static constexpr int kBarKVFull = 20;    // [kPairMaxStages]
+  static constexpr int kBarKVEmpty = 20 + kPairMaxStages;
+  static constexpr int kNumBars = 20 + 2 * kPairMaxStages;
   static constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 4;
   static constexpr int kBytes = kOffAbort + 4 + 1024;               // + slack for 1024-B alignment
@@ -211,6 +218,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kOffTmemSlot);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
 
+  const uint32_t n_stages = pargs.kv_splits > 0 ? kPairMaxStages : kPairStages;
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
 #ifdef TF_PAIR_TRACE
@@ -233,7 +241,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(bar(S::kBarOutFree + x), 1);
       mbar_init(bar(S::kBarOutFull + x), 128);
     }
-    for (int s = 0; s < kPairStages; ++s) {
+    for (int s = 0; s < kPairMaxStages; ++s) {
       mbar_init(bar(S::kBarKVFull + s), 1);
       mbar_init(bar(S::kBarKVEmpty + s), 1);
     }
@@ -347,7 +355,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           const uint32_t full = bar(S::kBarKVFull + stage);
           mbar_arrive_expect_tx(full, S::kTileBytes);
           kv_tile(kv, (j0 + j) * kAttnTile, b, h, smem_base + S::kOffKV + stage * S::kTileBytes, full);
-          if (++stage == kPairStages) {
+          if (++stage == n_stages) {
             stage = 0;
             phase ^= 1;
           }
@@ -420,7 +428,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         if (!mbar_wait_warp(bar(S::kBarKVFull + stage), phase, abort_flag, kPWaitKVFull)) return false;
         smem_addr = smem_base + S::kOffKV + stage * S::kTileBytes;
         stage_idx = stage;
-        if (++stage == kPairStages) {
+        if (++stage == n_stages) {
           stage = 0;
           phase ^= 1;
         }
@@ -438,9 +446,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         const int n = max(nx[0], nx[1]);
         // The first S tiles of the CTA's next item are issued during the last
         // KV tile of this one (below), so that the tensor pipe and the softmax
-        // warps do not drain at the item boundary.
+        // warps do not drain at the item boundary.  Only when both Q tiles end
+        // on the same KV tile: with a causal mask Q tile 0 ends one tile early,
+        // and waiting for the next item's operands at that point would hold up
+        // the last P.V of Q tile 1 (measured slower).
         int nx2[2] = {0, 0};
-        if (item + (int)gridDim.x < pargs.n_items) {
+        if (TF_PAIR_STREAM && nx[0] == nx[1] && item + (int)gridDim.x < pargs.n_items) {
           int b2, h2, pair2, split2;
           PairCursor nxt = cur;
           cursor_next(nxt);
