@@ -62,6 +62,7 @@ WORKLOADS["decode_gqa"] = dict(WORKLOADS["decode_c3"], B=64, Hkv=8)
 # exceed the 126 MB L2, but only a few hundred MB are held on the device.
 WORKLOADS["prefill_profile"] = dict(WORKLOADS["prefill_c2"], B=4)
 WORKLOADS["decode_profile"] = dict(WORKLOADS["decode_c3"], B=4)
+WORKLOADS["decode_gqa_profile"] = dict(WORKLOADS["decode_gqa"], B=16)
 # One rank's share of decode_c4 when the KV length is sharded over 8 GPUs.
 WORKLOADS["decode_c4_shard8"] = dict(WORKLOADS["decode_c4"], L=131072 // 8, scaling="weak")
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)   # earlier measurement on this pool
@@ -76,10 +77,17 @@ NCU_TRAFFIC_PER_HEAD = {
     # decode_split_kernel, B4 H32 Lk8192 D128 fp16: 536.9 MB read + 3.8 MB written over 128 heads
     ("decode", 8192, 128): (536.9e6 + 3.8e6) / 128,
 }
+# attn_fwd_pair_kernel in split-KV mode, B16 Hq32 Hkv8 Lk8192 D128 fp16: 537.2 MB read + 5.9 MB
+# written over 128 (batch, KV head) groups
+NCU_TRAFFIC_PER_KV_HEAD_GQA = {("decode", 8192, 128): (537.2e6 + 5.9e6) / 128}
 
 
 def ncu_traffic(w, heads_in_launch):
-    per_head = NCU_TRAFFIC_PER_HEAD.get((w["kind"], w["L"], w["D"]))
+    if "Hkv" in w:      # grouped-query decode: traffic scales with the KV heads
+        per_head = NCU_TRAFFIC_PER_KV_HEAD_GQA.get((w["kind"], w["L"], w["D"]))
+        heads_in_launch = heads_in_launch // w["H"] * w["Hkv"]
+    else:
+        per_head = NCU_TRAFFIC_PER_HEAD.get((w["kind"], w["L"], w["D"]))
     return None if per_head is None else per_head * heads_in_launch
 
 
@@ -463,6 +471,7 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
         d.k_stride_b, d.k_stride_h = k.stride(0), k.stride(1)
         d.v_stride_b, d.v_stride_h = v.stride(0), v.stride(1)
         d.o_stride_b, d.o_stride_h = o.stride(0), o.stride(1)
+        d.heads_kv = w.get("Hkv", w["H"])
         plan = _cabi.TfDecodePlan()
         _cabi.check(lib.tf_decode_plan(C.byref(d), C.byref(plan)))
         ws = torch.empty(plan.workspace_bytes // 4, dtype=torch.float32, device=device)
