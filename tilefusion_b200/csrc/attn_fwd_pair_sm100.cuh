@@ -47,6 +47,7 @@ constexpr int kPairStages = 3;        // K/V ring of a prefill launch (a deeper 
 // store) the two output staging tiles, which follow the ring in shared memory,
 // serve as two more ring stages.
 constexpr int kPairMaxStages = kPairStages + 2;
+constexpr int kItemSlots = 4;         // ring of work-item coordinates in shared memory
 #ifndef TF_PAIR_STREAM
 #define TF_PAIR_STREAM 1              // 0: do not issue the next item's first S tiles early (comparison builds)
 #endif
@@ -78,6 +79,8 @@ struct AttnPairArgs {
   int n_pairs;          // ceil(len_q / 256)
   int n_items;          // batch * heads * n_pairs * max(kv_splits, 1)
   int tma_store;        // 1: O leaves through shared memory and a TMA store (map_o is valid)
+  int* queue;           // item counter of this launch (zero when the kernel starts)
+  int causal_block;     // causal item order: (batch, head) slices per block (see pair_item_decode)
   // Split-KV mode (kv_splits > 0; used for grouped-query decoding, where the
   // "query rows" of a head are the query heads that share one KV head): an item
   // covers KV tiles [split * tiles_per_split, ...), and instead of the final
@@ -114,73 +117,68 @@ struct AttnPairSmem {
   static constexpr int kBarOutFree = 14;   // [2]  output staging of tile x may be overwritten
   static constexpr int kBarOutFull = 16;   // [2]  all 128 rows of tile x are in the staging buffer
   static constexpr int kBarOLoFull = 18;   // [2]  P.V MMAs of the first half of a tile are complete
-  static constexpr int kBarKVFull = 20;    // [kPairMaxStages]
-  static constexpr int kBarKVEmpty = 20 + kPairMaxStages;
-  static constexpr int kNumBars = 20 + 2 * kPairMaxStages;
+  static constexpr int kBarItemFull = 20;   // [kItemSlots]  coordinates of an item are in the item ring
+  static constexpr int kBarItemEmpty = 20 + kItemSlots;   // [kItemSlots]  every role has moved past the item
+  static constexpr int kBarKVFull = 20 + 2 * kItemSlots;  // [kPairMaxStages]
+  static constexpr int kBarKVEmpty = kBarKVFull + kPairMaxStages;
+  static constexpr int kNumBars = kBarKVEmpty + kPairMaxStages;
   static constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
   static constexpr int kOffAbort = kOffTmemSlot + 4;
-  static constexpr int kBytes = kOffAbort + 4 + 1024;               // + slack for 1024-B alignment
+  static constexpr int kOffItems = kOffAbort + 4 + 8;                // kItemSlots x PairItem (16-byte aligned)
+  static constexpr int kBytes = kOffItems + kItemSlots * 16 + 1024;  // + slack for 1024-B alignment
 };
 
 enum AttnPairWaitCode {
   kPWaitQFull = 301, kPWaitQEmpty = 302, kPWaitKVFull = 303, kPWaitKVEmpty = 304,
   kPWaitSFull = 305, kPWaitPFull = 306, kPWaitOFull = 307, kPWaitOEmpty = 308, kPWaitEpi = 309,
-  kPWaitOutFree = 310, kPWaitOutFull = 311
+  kPWaitOutFree = 310, kPWaitOutFull = 311, kPWaitItemFull = 312, kPWaitItemEmpty = 313
 };
 
-// Work item -> (batch, head, pair, split).  Non-causal items of one head are
-// adjacent (their K/V stay in L2); causal items are ordered heaviest pair
-// first so that the round-robin deal over CTAs is balanced:
-//   non-causal:  item = ((b * heads + h) * n_pairs + pair) * splits + split
-//   causal:      item = ((n_pairs - 1 - pair) * batch * heads + b * heads + h) * splits + split
-// A CTA walks items blockIdx.x, blockIdx.x + gridDim.x, ...; the cursor keeps
-// the item as a mixed-radix number and adds the step digit by digit, so that
-// no role pays for integer divisions at an item boundary.
-struct PairCursor {
-  int d[4];   // digits, least significant first: split | pair or h | h or b | b or (n_pairs - 1 - pair)
-  int s[4];   // the step (gridDim.x) in the same radices
-  int r[3];   // radices of digits 0..2
+// Work items are handed out at run time: the producer thread of a CTA draws
+// item numbers from a counter in global memory (one atomicAdd per item) and
+// publishes the decoded coordinates to the other roles of its CTA through a
+// small ring in shared memory.  A CTA that runs slower, or that drew heavier
+// items, simply draws fewer; and the CTAs running at any moment work on
+// neighbouring item numbers.  Non-causal (all items cost the same):
+//   number = ((b * heads + h) * n_pairs + pair) * splits + split
+// so the tile pairs of one head, which read the same K/V, run at the same time
+// and L2 serves all but the first read.  Causal (pair p costs 2p + 2 KV tiles):
+// the (batch, head) slices are taken in blocks of `causal_block`; within a
+// block all heaviest pairs come first, then the next lighter ones, and so on.
+// Heavy items are thus drawn before light ones (a heavy item drawn last would
+// run on alone after every other CTA has finished), while the K/V of a block
+// stay in L2 from its first level to its last.
+struct PairItem {
+  int b, h, pair, split;      // b < 0: no more items
 };
 
-__device__ __forceinline__ void cursor_init(const AttnPairArgs& a, int item0, int step, PairCursor& c) {
-  c.r[0] = a.kv_splits > 0 ? a.kv_splits : 1;
-  c.r[1] = a.base.causal ? a.heads : a.n_pairs;
-  c.r[2] = a.base.causal ? a.batch : a.heads;
-  int v = item0, w = step;
-#pragma unroll
-  for (int i = 0; i < 3; ++i) {
-    c.d[i] = v % c.r[i];
-    v /= c.r[i];
-    c.s[i] = w % c.r[i];
-    w /= c.r[i];
+__device__ __forceinline__ PairItem pair_item_decode(const AttnPairArgs& a, int number) {
+  PairItem it;
+  if (number >= a.n_items) {
+    it.b = -1;
+    it.h = it.pair = it.split = 0;
+    return it;
   }
-  c.d[3] = v;
-  c.s[3] = w;
-}
-
-__device__ __forceinline__ void cursor_next(PairCursor& c) {
-  int carry = 0;
-#pragma unroll
-  for (int i = 0; i < 3; ++i) {
-    int v = c.d[i] + c.s[i] + carry;
-    carry = v >= c.r[i] ? 1 : 0;
-    c.d[i] = v - (carry ? c.r[i] : 0);
-  }
-  c.d[3] += c.s[3] + carry;
-}
-
-__device__ __forceinline__ void cursor_get(const AttnPairArgs& a, const PairCursor& c, int& b, int& h, int& pair,
-                                           int& split) {
-  split = c.d[0];
+  const int splits = a.kv_splits > 0 ? a.kv_splits : 1;
+  it.split = number % splits;
+  const int rest = number / splits;
+  int bh;
   if (a.base.causal) {
-    h = c.d[1];
-    b = c.d[2];
-    pair = a.n_pairs - 1 - c.d[3];
+    const int n_bh = a.batch * a.heads;
+    const int per_block = a.causal_block * a.n_pairs;
+    const int block = rest / per_block;
+    const int r = rest - block * per_block;
+    const int in_block = min(a.causal_block, n_bh - block * a.causal_block);   // the last block may be short
+    const int level = r / in_block;
+    bh = block * a.causal_block + (r - level * in_block);
+    it.pair = a.n_pairs - 1 - level;
   } else {
-    pair = c.d[1];
-    h = c.d[2];
-    b = c.d[3];
+    bh = rest / a.n_pairs;
+    it.pair = rest - bh * a.n_pairs;
   }
+  it.b = bh / a.heads;
+  it.h = bh - it.b * a.heads;
+  return it;
 }
 
 // Number of KV tiles visited by Q tile x (rows q0 .. q0+127) of a pair; the
@@ -228,6 +226,19 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
   }
 #endif
 
+  // Item ring: the n-th item of this CTA sits in slot n % kItemSlots.
+  volatile PairItem* item_ring = reinterpret_cast<volatile PairItem*>(smem_gen + S::kOffItems);
+  // (consumer side) waits for the n-th item and reads it; false if the wait gave up
+  auto item_get = [&](uint32_t n, PairItem& it) -> bool {
+    const uint32_t slot = n % kItemSlots;
+    if (!mbar_wait(bar(S::kBarItemFull + slot), (n / kItemSlots) & 1, abort_flag, kPWaitItemFull)) return false;
+    it.b = item_ring[slot].b;
+    it.h = item_ring[slot].h;
+    it.pair = item_ring[slot].pair;
+    it.split = item_ring[slot].split;
+    return true;
+  };
+
   if (threadIdx.x == 0) {
     for (int x = 0; x < 2; ++x) {
       mbar_init(bar(S::kBarQFull + x), 1);
@@ -240,6 +251,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(bar(S::kBarOEmpty + x), 128);
       mbar_init(bar(S::kBarOutFree + x), 1);
       mbar_init(bar(S::kBarOutFull + x), 128);
+    }
+    for (int s = 0; s < kItemSlots; ++s) {
+      mbar_init(bar(S::kBarItemFull + s), 1);
+      mbar_init(bar(S::kBarItemEmpty + s), 1 + 256);      // the issuer's leader and every softmax thread
     }
     for (int s = 0; s < kPairMaxStages; ++s) {
       mbar_init(bar(S::kBarKVFull + s), 1);
@@ -299,11 +314,29 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
       };
-      PairCursor cur;
-      cursor_init(pargs, blockIdx.x, gridDim.x, cur);
-      for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x, cursor_next(cur)) {
-        int b, h, pair, split, j0, j0_unused;
-        cursor_get(pargs, cur, b, h, pair, split);
+      // Draws the n-th item of this CTA and publishes it (or the end marker).
+      auto item_put = [&](uint32_t n, PairItem& it) -> bool {
+        const uint32_t slot = n % kItemSlots;
+        if (n >= kItemSlots &&
+            !mbar_wait(bar(S::kBarItemEmpty + slot), ((n / kItemSlots) - 1) & 1, abort_flag, kPWaitItemEmpty))
+          return false;
+        it = pair_item_decode(pargs, atomicAdd(pargs.queue, 1));
+        item_ring[slot].b = it.b;
+        item_ring[slot].h = it.h;
+        item_ring[slot].pair = it.pair;
+        item_ring[slot].split = it.split;
+        mbar_arrive(bar(S::kBarItemFull + slot));          // (release: orders the stores above)
+        return true;
+      };
+      PairItem cur, nxt;
+      ok = item_put(0, cur);
+      for (uint32_t n_item = 0; ok && cur.b >= 0; ++n_item, cur = nxt) {
+        // the next item is drawn before this one's loads start: the MMA issuer
+        // looks one item ahead
+        ok = item_put(n_item + 1, nxt);
+        if (!ok) break;
+        const int b = cur.b, h = cur.h, pair = cur.pair, split = cur.split;
+        int j0, j0_unused;
         const int q0 = pair * 2 * kAttnTile;
         const int n0 = kv_tiles_for(pargs, q0, split, j0);          // tile 0 always exists; it sets j0
         const int n1 = kv_tiles_for(pargs, q0 + kAttnTile, split, j0_unused);
@@ -328,15 +361,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         // the previous item is still in its last KV tile, and the buffer of Q1
         // is released later than that of Q0.
         ok = load_q(0);
-        // The next item of this CTA usually belongs to another head: bring its Q
+        // When the next item of this CTA belongs to another head, bring its Q
         // tiles and its first K and V tiles into L2 now, so that the loads at the
         // item boundary (which cannot be issued earlier: the Q buffers and the
         // ring are in use) do not wait for HBM.
-        if (pargs.kv_splits == 0 && item + (int)gridDim.x < pargs.n_items) {
-          int b2, h2, pair2, split2;
-          PairCursor nxt = cur;
-          cursor_next(nxt);
-          cursor_get(pargs, nxt, b2, h2, pair2, split2);
+        if (pargs.kv_splits == 0 && nxt.b >= 0 && (nxt.b != b || nxt.h != h)) {
+          const int b2 = nxt.b, h2 = nxt.h, pair2 = nxt.pair;
           const int q2 = pair2 * 2 * kAttnTile;
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
@@ -435,11 +465,15 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         return true;
       };
 
-      PairCursor cur;
-      cursor_init(pargs, blockIdx.x, gridDim.x, cur);
-      for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x, cursor_next(cur)) {
-        int b, h, pair, split, j0_unused;
-        cursor_get(pargs, cur, b, h, pair, split);
+      PairItem cur, nxt;
+      ok = __all_sync(0xffffffffu, item_get(0, cur));
+      for (uint32_t n_item = 0; ok && cur.b >= 0; ++n_item, cur = nxt) {
+        // (the producer publishes item n + 1 before it loads item n)
+        ok = __all_sync(0xffffffffu, item_get(n_item + 1, nxt));
+        if (!ok) break;
+        if (leader && n_item > 0) mbar_arrive(bar(S::kBarItemEmpty + (n_item - 1) % kItemSlots));
+        const int pair = cur.pair, split = cur.split;
+        int j0_unused;
         const int q0 = pair * 2 * kAttnTile;
         const int nx[2] = {kv_tiles_for(pargs, q0, split, j0_unused),
                            kv_tiles_for(pargs, q0 + kAttnTile, split, j0_unused)};
@@ -451,11 +485,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         // and waiting for the next item's operands at that point would hold up
         // the last P.V of Q tile 1 (measured slower).
         int nx2[2] = {0, 0};
-        if (TF_PAIR_STREAM && nx[0] == nx[1] && item + (int)gridDim.x < pargs.n_items) {
-          int b2, h2, pair2, split2;
-          PairCursor nxt = cur;
-          cursor_next(nxt);
-          cursor_get(pargs, nxt, b2, h2, pair2, split2);
+        if (TF_PAIR_STREAM && nx[0] == nx[1] && nxt.b >= 0) {
+          const int pair2 = nxt.pair, split2 = nxt.split;
           nx2[0] = kv_tiles_for(pargs, pair2 * 2 * kAttnTile, split2, j0_unused);
           nx2[1] = kv_tiles_for(pargs, pair2 * 2 * kAttnTile + kAttnTile, split2, j0_unused);
         }
@@ -563,13 +594,16 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
 #define SM_TRACE(event, tile)
 #endif
 
-    PairCursor cur;
-    cursor_init(pargs, blockIdx.x, gridDim.x, cur);
-    for (int item = blockIdx.x; ok && item < pargs.n_items; item += gridDim.x, cursor_next(cur)) {
-      int b, h, pair, split, j0;
-      cursor_get(pargs, cur, b, h, pair, split);
-      const int q0 = pair * 2 * kAttnTile + x * kAttnTile;
-      const int n_kv = kv_tiles_for(pargs, q0, split, j0);
+    for (uint32_t n_item = 0; ok; ++n_item) {
+      PairItem cur;
+      ok = __all_sync(0xffffffffu, item_get(n_item, cur));
+      if (!ok) break;
+      // (this thread is done with the previous item: its slot may be reused)
+      if (n_item > 0) mbar_arrive(bar(S::kBarItemEmpty + (n_item - 1) % kItemSlots));
+      if (cur.b < 0) break;
+      int j0;
+      const int q0 = cur.pair * 2 * kAttnTile + x * kAttnTile;
+      const int n_kv = kv_tiles_for(pargs, q0, cur.split, j0);
       if (n_kv == 0) continue;
       const int q_idx = q0 + row;
       float m_used = -INFINITY;
@@ -746,6 +780,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       o_base += n_kv;
       tc_fence_after();
       SM_TRACE(5, n_kv);
+      // (batch, head and split are read again here rather than kept in registers
+      // through the KV loop; the slot is this thread's until it moves on)
+      const int b = item_ring[n_item % kItemSlots].b, h = item_ring[n_item % kItemSlots].h;
+      const int split = item_ring[n_item % kItemSlots].split;
       const float inv_l = 1.0f / l_run;
       const bool row_valid = q_idx < args.len_q;
       if (pargs.kv_splits > 0) {
