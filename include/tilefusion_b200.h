@@ -143,6 +143,11 @@ typedef struct TfAttnPlan {
  * kernel it JIT-compiles (include/kernels/flash_attention_device.cuh:130-312).
  * `lse` may be NULL; otherwise it receives log-sum-exp rows, fp32 [B,H,Lq],
  * natural log of sum(exp(scale * q.k)).  Asynchronous: no device sync.
+ * Besides the kernel the call enqueues one 4-byte memset (the work-item
+ * counter of the launch) on `stream`; both can be captured into a CUDA graph
+ * once a first call on the device has been made outside a capture.  Calls on
+ * different streams may overlap; at most 64 launches of the two-tile variant
+ * may be in flight at once on a device (they take turns on 64 counter words).
  */
 TF_EXPORT int tf_attn_fwd(const void* q, const void* k, const void* v, void* o,
                           float* lse, const TfAttnDesc* desc, void* stream);
