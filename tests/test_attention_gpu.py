@@ -261,6 +261,33 @@ def test_config5_size_bf16_subset_and_properties():
     assert (o1.float() - 1.0).abs().max().item() <= 1e-2          # bf16 output spacing near 1 is 2^-8
 
 
+def test_overlapping_launches_on_several_streams():
+    """Launches of the two-tile kernel that are in flight together (four streams,
+    six rounds) each draw their work items from their own counter word: every
+    output must equal the one its problem gives alone."""
+    from cabi_helpers import attn_fwd, device_status
+
+    problems = []
+    for i in range(4):
+        b, h, lq, lk, d = 2, 8, 768, 512 + 128 * i, 128
+        q, k, v = orc.seeded_inputs(20 + i, (b, h, lq, d), (b, h, lk, d), (b, h, lk, d), 0.5)
+        causal = bool(i % 2)
+        ref, lse_ref = orc.attention_fp32(q, k, v, 1.0 / math.sqrt(d), causal)
+        problems.append((q.cuda(), k.cuda(), v.cuda(), causal, ref, lse_ref))
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in problems]
+    outs = []
+    for _ in range(6):
+        for (q, k, v, causal, _, _), s in zip(problems, streams):
+            with torch.cuda.stream(s):
+                outs.append(attn_fwd(q, k, v, 1.0 / math.sqrt(128), causal, tile_q=256))
+    torch.cuda.synchronize()
+    for n, (o, lse) in enumerate(outs):
+        _, _, _, _, ref, lse_ref = problems[n % len(problems)]
+        _check(o, lse, ref, lse_ref, torch.float16)
+    assert device_status() == 0
+
+
 def test_unsupported_inputs_report_errors():
     from cabi_helpers import attn_fwd
     from tilefusion_b200._cabi import TileFusionError, TF_ERR_UNSUPPORTED
