@@ -147,7 +147,9 @@ typedef struct TfAttnPlan {
  * counter of the launch) on `stream`; both can be captured into a CUDA graph
  * once a first call on the device has been made outside a capture.  Calls on
  * different streams may overlap; at most 64 launches of the two-tile variant
- * may be in flight at once on a device (they take turns on 64 counter words).
+ * may be in flight at once on a device (they take turns on 64 counter words;
+ * launches recorded into CUDA graphs take theirs from a separate set of 64 and
+ * keep it for every replay).
  */
 TF_EXPORT int tf_attn_fwd(const void* q, const void* k, const void* v, void* o,
                           float* lse, const TfAttnDesc* desc, void* stream);

@@ -288,6 +288,38 @@ def test_overlapping_launches_on_several_streams():
     assert device_status() == 0
 
 
+def test_cuda_graph_capture_and_replay():
+    """The launch (a 4-byte memset of its work-item counter plus the kernel) is
+    captured into a CUDA graph after one call outside the capture; replays see
+    new input values in the same buffers."""
+    from cabi_helpers import attn_fwd, attn_desc, _stream
+    from tilefusion_b200 import _cabi
+    import ctypes as C
+
+    b, h, l, d = 2, 8, 512, 128
+    scale = 1.0 / math.sqrt(d)
+    q, k, v = (t.cuda() for t in orc.seeded_inputs(31, (b, h, l, d), (b, h, l, d), (b, h, l, d), 0.5))
+    attn_fwd(q, k, v, scale, False, tile_q=256)                  # first call on the device, not captured
+    o = torch.empty_like(q)
+    desc = attn_desc(q, k, v, o, scale, False, 256, 128)
+    lib = _cabi.lib()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            rc = lib.tf_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), None, C.byref(desc), _stream())
+    _cabi.check(rc)
+    for seed in (32, 33):
+        q2, k2, v2 = orc.seeded_inputs(seed, (b, h, l, d), (b, h, l, d), (b, h, l, d), 0.5)
+        q.copy_(q2), k.copy_(k2), v.copy_(v2)
+        o.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        ref, _ = orc.attention_fp32(q2, k2, v2, scale, False)
+        _check(o, None, ref, None, torch.float16)
+
+
 def test_unsupported_inputs_report_errors():
     from cabi_helpers import attn_fwd
     from tilefusion_b200._cabi import TileFusionError, TF_ERR_UNSUPPORTED

@@ -234,13 +234,15 @@ int launch_two_gemms(const AttnLaunch& L, const TfAttnDesc* d, cudaStream_t stre
 // words (round robin), zeroes it on its stream and hands it to the kernel, whose
 // CTAs draw their work items from it.  Launches that overlap in time (different
 // streams) therefore use different words, up to kPairQueues of them in flight.
+// A launch recorded into a CUDA graph keeps its word for every replay, so
+// captured launches take theirs from a second set that eager launches never use.
 constexpr int kPairQueues = 64;
-static __device__ int g_pair_queue[kPairQueues];
+static __device__ int g_pair_queue[2 * kPairQueues];
 
-int* pair_queue_word() {
+int* pair_queue_word(cudaStream_t stream) {
   static thread_local int cached_device = -1;
   static thread_local int* base = nullptr;
-  static std::atomic<unsigned> next{0};
+  static std::atomic<unsigned> next_eager{0}, next_captured{0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
   if (cached_device != dev) {
@@ -249,7 +251,11 @@ int* pair_queue_word() {
     base = static_cast<int*>(p);
     cached_device = dev;
   }
-  return base + next.fetch_add(1, std::memory_order_relaxed) % kPairQueues;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) return nullptr;
+  if (cap == cudaStreamCaptureStatusActive)
+    return base + kPairQueues + next_captured.fetch_add(1, std::memory_order_relaxed) % kPairQueues;
+  return base + next_eager.fetch_add(1, std::memory_order_relaxed) % kPairQueues;
 }
 
 // Two Q tiles per CTA, persistent grid of one CTA per SM.
@@ -289,7 +295,7 @@ int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan&
     const long long n_blocks = std::max(1ll, (n_bh + fit / 2) / fit);
     a.causal_block = (int)((n_bh + n_blocks - 1) / n_blocks);
   }
-  a.queue = pair_queue_word();
+  a.queue = pair_queue_word(stream);
   if (a.queue == nullptr) return fail(TF_ERR_CUDA, "cannot resolve the item counter of the two-tile kernel");
   TF_CUDA_TRY(cudaMemsetAsync(a.queue, 0, sizeof(int), stream));
   a.kv_splits = kv_splits;
