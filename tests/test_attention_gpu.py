@@ -261,6 +261,33 @@ def test_config5_size_bf16_subset_and_properties():
     assert (o1.float() - 1.0).abs().max().item() <= 1e-2          # bf16 output spacing near 1 is 2^-8
 
 
+def test_causal_heads_in_unequal_blocks():
+    """Causal work items are ordered in blocks of (batch, head) slices sized to
+    the L2 cache.  53 heads of 4096 keys (2 MiB of K+V each) make two blocks of
+    27 and 26 slices: every (head, tile pair) must still be computed exactly
+    once.  Reference: the oracle's expression evaluated in fp32 on the GPU."""
+    from cabi_helpers import attn_fwd, device_status
+
+    b, h, l, d = 1, 53, 4096, 128
+    g = torch.Generator(device="cuda").manual_seed(7)
+    q = (torch.randn(b, h, l, d, generator=g, device="cuda") * 0.5).half()
+    k = (torch.randn(b, h, l, d, generator=g, device="cuda") * 0.5).half()
+    v = (torch.randn(b, h, l, d, generator=g, device="cuda") * 0.5).half()
+    scale = 1.0 / math.sqrt(d)
+    o, lse = attn_fwd(q, k, v, scale, True)
+    assert device_status() == 0
+    assert torch.isfinite(o.float()).all() and torch.isfinite(lse).all()
+    worst_abs, num, den = 0.0, 0.0, 0.0
+    for hi in range(h):
+        ref, lse_ref = orc.attention_fp32(q[0, hi], k[0, hi], v[0, hi], scale, True)
+        diff = o[0, hi].float() - ref
+        worst_abs = max(worst_abs, diff.abs().max().item())
+        num += diff.double().pow(2).sum().item()
+        den += ref.double().pow(2).sum().item()
+        assert (lse[0, hi] - lse_ref).abs().max().item() <= LSE_ABS
+    assert worst_abs <= MAX_ABS and math.sqrt(num / den) <= REL_L2[torch.float16]
+
+
 def test_overlapping_launches_on_several_streams():
     """Launches of the two-tile kernel that are in flight together (four streams,
     six rounds) each draw their work items from their own counter word: every
