@@ -72,8 +72,8 @@ FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)   # earlier measuremen
 # problem of the captured case; traffic grows in proportion to batch x heads,
 # so a launch is scaled by the problems it processes.
 NCU_TRAFFIC_PER_HEAD = {
-    # attn_fwd_pair_kernel, B4 H32 L2048 D128 fp16: 201.8 MB read + 43.3 MB written over 128 heads
-    ("prefill", 2048, 128): (201.8e6 + 43.3e6) / 128,
+    # attn_fwd_pair_kernel, B4 H32 L2048 D128 fp16: 203.0 MB read + 46.9 MB written over 128 heads
+    ("prefill", 2048, 128): (203.0e6 + 46.9e6) / 128,
     # decode_split_kernel, B4 H32 Lk8192 D128 fp16: 536.9 MB read + 3.8 MB written over 128 heads
     ("decode", 8192, 128): (536.9e6 + 3.8e6) / 128,
 }
