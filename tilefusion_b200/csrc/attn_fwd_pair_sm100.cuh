@@ -1,5 +1,6 @@
 // Fused attention forward for sm_100a, two Q tiles per CTA (256 query rows),
-// persistent over (head, Q-tile-pair) work items.
+// persistent over (head, Q-tile-pair) work items that the CTAs draw from a
+// counter at run time (see pair_item_decode).
 //
 // Same arithmetic as attn_fwd_kernel (attn_fwd_sm100.cuh) and the same place
 // in TileFusion's path (include/kernels/flash_attention_device.cuh:130-312);
@@ -12,7 +13,7 @@
 //   warps 4-7  softmax + epilogue of Q tile 1
 //   warp  8    tcgen05.mma issuer (the warp walks the schedule, one elected
 //              lane issues), owns the TMEM allocation
-//   warp  9    TMA producer (one thread)
+//   warp  9    TMA producer and work-item scheduler (one thread)
 //   warps 10-11 idle; they complete the third warpgroup so that it can hand
 //              its registers to the softmax warpgroups (setmaxnreg)
 // TMEM (512 columns): S0 | S1 | O0 | O1, each 128 fp32 columns (O: D columns);
@@ -22,7 +23,9 @@
 // Q tiles share every K/V load, and one output staging tile per Q tile: the
 // epilogue writes the 16-bit O tile there (swizzled) and one thread sends it
 // to global memory with a TMA store.  While an item runs, the producer brings
-// the next item's Q tiles and first K/V tiles into L2.
+// the next item's Q tiles and first K/V tiles into L2 if it belongs to another
+// head, and the issuer starts the next item's first S tiles during the last
+// KV tile of the current one.
 //
 // The same kernel serves grouped-query decoding in split-KV mode (see
 // AttnPairArgs): the query heads of a group are the rows of Q tile 0, an item
