@@ -597,17 +597,152 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
 #define SM_TRACE(event, tile)
 #endif
 
+    // Second part of an item's epilogue, run for the item in ring slot `slot`:
+    // O / l out of TMEM to global memory, then the item's slot is given back.
+    float pend_inv_l = 0.f;
+    bool have_pending = false;
+    auto flush_pending = [&](uint32_t slot) -> bool {
+      if (!have_pending) return true;
+      have_pending = false;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_o, (o_base - 1) & 1, abort_flag, kPWaitEpi))) return false;
+      tc_fence_after();
+      SM_TRACE(5, 0);
+      // (batch, head and split are read again here rather than kept in registers
+      // through the KV loop; the slot is this thread's until it moves on)
+      const int b = item_ring[slot].b, h = item_ring[slot].h;
+      const int split = item_ring[slot].split;
+      const int q0 = item_ring[slot].pair * 2 * kAttnTile + x * kAttnTile;
+      const int q_idx = q0 + row;
+      const float inv_l = pend_inv_l;
+      const bool row_valid = q_idx < args.len_q;
+      if (pargs.kv_splits > 0) {
+        // split-KV mode: one fp32 partial row (normalised O, log2-sum-exp) per split
+        const long long prow =
+            (((long long)b * pargs.heads + h) * args.len_q + q_idx) * pargs.kv_splits + split;
+        float* p_row = pargs.part_o + prow * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t orow[32];
+          tmem_ld32(t_lane + col_o + c * 32, orow);
+          tmem_wait_ld();
+          if (c == D / 32 - 1) {
+            tc_fence_before();
+            mbar_arrive(bar_oe);
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<float4*>(p_row + c * 32 + v * 4) =
+                  make_float4(__uint_as_float(orow[v * 4 + 0]) * inv_l, __uint_as_float(orow[v * 4 + 1]) * inv_l,
+                              __uint_as_float(orow[v * 4 + 2]) * inv_l, __uint_as_float(orow[v * 4 + 3]) * inv_l);
+          }
+        }
+        mbar_arrive(bar(S::kBarItemEmpty + slot));
+        SM_TRACE(6, 0);
+        return true;
+      }
+      if (pargs.tma_store) {
+        // O leaves through shared memory: each thread writes its row of the
+        // 16-bit tile in the 128-byte-swizzle layout of the tensor map (16-byte
+        // unit u of row r sits at unit u ^ (r & 7) of its 128-byte line, which
+        // also keeps the writes of a warp free of bank conflicts), then one
+        // thread issues a TMA store per 64-column block.  Rows past len_q are
+        // clipped by the store.
+        const uint32_t stage_out = smem_base + S::kOffOut + x * S::kTileBytes;
+        if (row == 0) {
+          bulk_wait_group_read0();                   // the previous item's store has read the buffer
+          mbar_arrive(bar(S::kBarOutFree + x));
+        }
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(S::kBarOutFree + x), out_cnt & 1, abort_flag, kPWaitOutFree));
+        if (!ok) return false;
+        // (all of O_x is read with one wait: the S registers are free by now)
+        uint32_t orow[D / 32][32];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld32(t_lane + col_o + c * 32, orow[c]);
+        tmem_wait_ld();
+        // O_x has been read out: the next item's first P V may overwrite it
+        tc_fence_before();
+        mbar_arrive(bar_oe);
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          const uint32_t line = stage_out + (c >> 1) * S::kBlockBytes + row * 128;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint32_t w0 = pack2<T>(__uint_as_float(orow[c][v * 8 + 0]) * inv_l, __uint_as_float(orow[c][v * 8 + 1]) * inv_l);
+            const uint32_t w1 = pack2<T>(__uint_as_float(orow[c][v * 8 + 2]) * inv_l, __uint_as_float(orow[c][v * 8 + 3]) * inv_l);
+            const uint32_t w2 = pack2<T>(__uint_as_float(orow[c][v * 8 + 4]) * inv_l, __uint_as_float(orow[c][v * 8 + 5]) * inv_l);
+            const uint32_t w3 = pack2<T>(__uint_as_float(orow[c][v * 8 + 6]) * inv_l, __uint_as_float(orow[c][v * 8 + 7]) * inv_l);
+            const uint32_t unit = (uint32_t)((c & 1) * 4 + v) ^ (uint32_t)(row & 7);
+            st_shared_v4(line + (unit << 4), w0, w1, w2, w3);
+          }
+        }
+        fence_proxy_async_smem();                    // my writes are visible to the TMA engine
+        mbar_arrive(bar(S::kBarOutFull + x));
+        if (warp == 4 * x) {
+          ok = mbar_wait_warp(bar(S::kBarOutFull + x), out_cnt & 1, abort_flag, kPWaitOutFull);
+          if (!ok) return false;
+        }
+        ++out_cnt;
+        if (row == 0) {
+#pragma unroll
+          for (int blk = 0; blk < kBlocks; ++blk)
+            tma_store_4d(&map_o, stage_out + blk * S::kBlockBytes, blk * 64, q0, h, b);
+          bulk_commit_group();
+        }
+      } else {
+      T* o_row = reinterpret_cast<T*>(args.o) + (long long)b * args.o_stride_b +
+                 (long long)h * args.o_stride_h + (long long)q_idx * args.o_stride_l;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t orow[32];
+        tmem_ld32(t_lane + col_o + c * 32, orow);
+        tmem_wait_ld();
+        if (c == D / 32 - 1) {
+          // O_x has been read out: the next item's first P V may overwrite it
+          tc_fence_before();
+          mbar_arrive(bar_oe);
+        }
+        if (row_valid) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 out;
+            out.x = pack2<T>(__uint_as_float(orow[v * 8 + 0]) * inv_l,
+                             __uint_as_float(orow[v * 8 + 1]) * inv_l);
+            out.y = pack2<T>(__uint_as_float(orow[v * 8 + 2]) * inv_l,
+                             __uint_as_float(orow[v * 8 + 3]) * inv_l);
+            out.z = pack2<T>(__uint_as_float(orow[v * 8 + 4]) * inv_l,
+                             __uint_as_float(orow[v * 8 + 5]) * inv_l);
+            out.w = pack2<T>(__uint_as_float(orow[v * 8 + 6]) * inv_l,
+                             __uint_as_float(orow[v * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(o_row + c * 32 + v * 8) = out;
+          }
+        }
+      }
+      }
+      mbar_arrive(bar(S::kBarItemEmpty + slot));
+      SM_TRACE(6, 0);
+      return true;
+    };
+
     for (uint32_t n_item = 0; ok; ++n_item) {
       PairItem cur;
       ok = __all_sync(0xffffffffu, item_get(n_item, cur));
       if (!ok) break;
-      // (this thread is done with the previous item: its slot may be reused)
-      if (n_item > 0) mbar_arrive(bar(S::kBarItemEmpty + (n_item - 1) % kItemSlots));
-      if (cur.b < 0) break;
+      // The slot of the previous item is given back once this thread is done with
+      // it: here if nothing of it is pending, else at the end of flush_pending.
+      const uint32_t prev_slot = (n_item + kItemSlots - 1) % kItemSlots;
+      if (n_item > 0 && !have_pending) mbar_arrive(bar(S::kBarItemEmpty + prev_slot));
+      if (cur.b < 0) {
+        ok = flush_pending(prev_slot);
+        break;
+      }
       int j0;
       const int q0 = cur.pair * 2 * kAttnTile + x * kAttnTile;
       const int n_kv = kv_tiles_for(pargs, q0, cur.split, j0);
-      if (n_kv == 0) continue;
+      if (n_kv == 0) {
+        ok = flush_pending(prev_slot);
+        continue;
+      }
       const int q_idx = q0 + row;
       float m_used = -INFINITY;
       float l_run = 0.f;
@@ -774,131 +909,38 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         mbar_arrive(bar_p_hi);
         SM_TRACE(3, j);
         l_run += lo_sum + hi_sum;
+        if (j == 0) {
+          // the previous item's O can leave now: its last P.V has had a whole
+          // tile's time to finish, and this item's first P.V waits for it
+          ok = flush_pending(prev_slot);
+          if (!ok) break;
+        }
       }
       if (!ok) break;
 
-      // ---------------------------------------------------------- epilogue --
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_o, (o_base + n_kv - 1) & 1, abort_flag, kPWaitEpi));
-      if (!ok) break;
+      // ------------------------------------------------------ end of the item --
+      // The log-sum-exp outputs are final now.  Reading O out of TMEM has to wait
+      // for the last P.V MMAs; that part is deferred until this thread has
+      // published the first tile of its next item (see flush_pending), so that it
+      // does not sit idle meanwhile.
+      {
+        const int b = item_ring[n_item % kItemSlots].b, h = item_ring[n_item % kItemSlots].h;
+        const int split = item_ring[n_item % kItemSlots].split;
+        if (q_idx < args.len_q) {
+          if (pargs.kv_splits > 0) {
+            const long long prow =
+                (((long long)b * pargs.heads + h) * args.len_q + q_idx) * pargs.kv_splits + split;
+            pargs.part_ml[prow * 2 + 0] = m_used * args.scale_log2 + log2f(l_run);
+            pargs.part_ml[prow * 2 + 1] = 1.0f;
+          } else if (args.lse != nullptr) {
+            args.lse[(long long)b * args.lse_stride_b + (long long)h * args.lse_stride_h + q_idx] =
+                0.6931471805599453f * (m_used * args.scale_log2 + log2f(l_run));
+          }
+        }
+      }
+      pend_inv_l = 1.0f / l_run;
+      have_pending = true;
       o_base += n_kv;
-      tc_fence_after();
-      SM_TRACE(5, n_kv);
-      // (batch, head and split are read again here rather than kept in registers
-      // through the KV loop; the slot is this thread's until it moves on)
-      const int b = item_ring[n_item % kItemSlots].b, h = item_ring[n_item % kItemSlots].h;
-      const int split = item_ring[n_item % kItemSlots].split;
-      const float inv_l = 1.0f / l_run;
-      const bool row_valid = q_idx < args.len_q;
-      if (pargs.kv_splits > 0) {
-        // split-KV mode: one fp32 partial row (normalised O, log2-sum-exp) per split
-        const long long prow =
-            (((long long)b * pargs.heads + h) * args.len_q + q_idx) * pargs.kv_splits + split;
-        float* p_row = pargs.part_o + prow * D;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t orow[32];
-          tmem_ld32(t_lane + col_o + c * 32, orow);
-          tmem_wait_ld();
-          if (c == D / 32 - 1) {
-            tc_fence_before();
-            mbar_arrive(bar_oe);
-          }
-          if (row_valid) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v)
-              *reinterpret_cast<float4*>(p_row + c * 32 + v * 4) =
-                  make_float4(__uint_as_float(orow[v * 4 + 0]) * inv_l, __uint_as_float(orow[v * 4 + 1]) * inv_l,
-                              __uint_as_float(orow[v * 4 + 2]) * inv_l, __uint_as_float(orow[v * 4 + 3]) * inv_l);
-          }
-        }
-        if (row_valid) {
-          pargs.part_ml[prow * 2 + 0] = m_used * args.scale_log2 + log2f(l_run);
-          pargs.part_ml[prow * 2 + 1] = 1.0f;
-        }
-        continue;
-      }
-      if (pargs.tma_store) {
-        // O leaves through shared memory: each thread writes its row of the
-        // 16-bit tile in the 128-byte-swizzle layout of the tensor map (16-byte
-        // unit u of row r sits at unit u ^ (r & 7) of its 128-byte line, which
-        // also keeps the writes of a warp free of bank conflicts), then one
-        // thread issues a TMA store per 64-column block.  Rows past len_q are
-        // clipped by the store.
-        const uint32_t stage_out = smem_base + S::kOffOut + x * S::kTileBytes;
-        if (row == 0) {
-          bulk_wait_group_read0();                   // the previous item's store has read the buffer
-          mbar_arrive(bar(S::kBarOutFree + x));
-        }
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(S::kBarOutFree + x), out_cnt & 1, abort_flag, kPWaitOutFree));
-        if (!ok) break;
-        // (all of O_x is read with one wait: the S registers are free by now)
-        uint32_t orow[D / 32][32];
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) tmem_ld32(t_lane + col_o + c * 32, orow[c]);
-        tmem_wait_ld();
-        // O_x has been read out: the next item's first P V may overwrite it
-        tc_fence_before();
-        mbar_arrive(bar_oe);
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          const uint32_t line = stage_out + (c >> 1) * S::kBlockBytes + row * 128;
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const uint32_t w0 = pack2<T>(__uint_as_float(orow[c][v * 8 + 0]) * inv_l, __uint_as_float(orow[c][v * 8 + 1]) * inv_l);
-            const uint32_t w1 = pack2<T>(__uint_as_float(orow[c][v * 8 + 2]) * inv_l, __uint_as_float(orow[c][v * 8 + 3]) * inv_l);
-            const uint32_t w2 = pack2<T>(__uint_as_float(orow[c][v * 8 + 4]) * inv_l, __uint_as_float(orow[c][v * 8 + 5]) * inv_l);
-            const uint32_t w3 = pack2<T>(__uint_as_float(orow[c][v * 8 + 6]) * inv_l, __uint_as_float(orow[c][v * 8 + 7]) * inv_l);
-            const uint32_t unit = (uint32_t)((c & 1) * 4 + v) ^ (uint32_t)(row & 7);
-            st_shared_v4(line + (unit << 4), w0, w1, w2, w3);
-          }
-        }
-        fence_proxy_async_smem();                    // my writes are visible to the TMA engine
-        mbar_arrive(bar(S::kBarOutFull + x));
-        if (warp == 4 * x) {
-          ok = mbar_wait_warp(bar(S::kBarOutFull + x), out_cnt & 1, abort_flag, kPWaitOutFull);
-          if (!ok) break;
-        }
-        ++out_cnt;
-        if (row == 0) {
-#pragma unroll
-          for (int blk = 0; blk < kBlocks; ++blk)
-            tma_store_4d(&map_o, stage_out + blk * S::kBlockBytes, blk * 64, q0, h, b);
-          bulk_commit_group();
-        }
-      } else {
-      T* o_row = reinterpret_cast<T*>(args.o) + (long long)b * args.o_stride_b +
-                 (long long)h * args.o_stride_h + (long long)q_idx * args.o_stride_l;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t orow[32];
-        tmem_ld32(t_lane + col_o + c * 32, orow);
-        tmem_wait_ld();
-        if (c == D / 32 - 1) {
-          // O_x has been read out: the next item's first P V may overwrite it
-          tc_fence_before();
-          mbar_arrive(bar_oe);
-        }
-        if (row_valid) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 out;
-            out.x = pack2<T>(__uint_as_float(orow[v * 8 + 0]) * inv_l,
-                             __uint_as_float(orow[v * 8 + 1]) * inv_l);
-            out.y = pack2<T>(__uint_as_float(orow[v * 8 + 2]) * inv_l,
-                             __uint_as_float(orow[v * 8 + 3]) * inv_l);
-            out.z = pack2<T>(__uint_as_float(orow[v * 8 + 4]) * inv_l,
-                             __uint_as_float(orow[v * 8 + 5]) * inv_l);
-            out.w = pack2<T>(__uint_as_float(orow[v * 8 + 6]) * inv_l,
-                             __uint_as_float(orow[v * 8 + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(o_row + c * 32 + v * 8) = out;
-          }
-        }
-      }
-      }
-      if (row_valid && args.lse != nullptr) {
-        args.lse[(long long)b * args.lse_stride_b + (long long)h * args.lse_stride_h + q_idx] =
-            0.6931471805599453f * (m_used * args.scale_log2 + log2f(l_run));
-      }
       SM_TRACE(6, n_kv);
     }
   }
