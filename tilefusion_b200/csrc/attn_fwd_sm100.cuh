@@ -298,11 +298,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
           }
       }
 
-      float m_tile = -INFINITY;
+      // Row maximum: eight independent chains (two per chunk) of 3-input max
+      // instructions in one straight line of code, so that they pipeline.
+      float m_tile;
+      {
+        float ma[4], mb[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c) {
+          ma[c] = max3(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
+          mb[c] = max3(__uint_as_float(sr[c][3]), __uint_as_float(sr[c][4]), __uint_as_float(sr[c][5]));
+        }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sr[c][i]));
+        for (int i = 6; i + 3 < 32; i += 4) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            ma[c] = max3(ma[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+            mb[c] = max3(mb[c], __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          ma[c] = max3(ma[c], mb[c], fmaxf(__uint_as_float(sr[c][30]), __uint_as_float(sr[c][31])));
+        m_tile = fmaxf(fmaxf(ma[0], ma[1]), fmaxf(ma[2], ma[3]));
+      }
 
       // Lazy rescale: keep the old reference maximum unless the new one is
       // more than 2^kRescaleThreshold above it.
@@ -330,22 +348,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
 
+      // P = 2^(s*scale - m); scale-subtract and row sum as packed f32x2
+      // instructions (they overlap with the MUFU, scalar FMAs only partly), the
+      // sum in four independent accumulators.
       const float m_scaled = m_used * args.scale_log2;
-      float l_tile = 0.f;
+      const uint64_t scale2 = f2_pack(args.scale_log2, args.scale_log2);
+      const uint64_t negm2 = f2_pack(-m_scaled, -m_scaled);
+      uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), args.scale_log2, -m_scaled));
-          const float p1 =
-              fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), args.scale_log2, -m_scaled));
-          l_tile += p0 + p1;
+          float x0, x1;
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2),
+                    x0, x1);
+          const float p0 = fast_exp2(x0);
+          const float p1 = fast_exp2(x1);
+          ls2[(i >> 1) & 3] = f2_add(ls2[(i >> 1) & 3], f2_pack(p0, p1));
           pk[i >> 1] = pack2<T>(p0, p1);
         }
         tmem_st16(t_lane + kColP + c * 16, pk);
       }
-      l_run += l_tile;
+      {
+        float lo, hi;
+        f2_unpack(f2_add(f2_add(ls2[0], ls2[1]), f2_add(ls2[2], ls2[3])), lo, hi);
+        l_run += lo + hi;
+      }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p);
