@@ -73,6 +73,13 @@ def test_attn_plan_and_layout_detection(native_lib):
     assert plan.tile_q == 128
     assert native_lib.tf_attn_plan(C.byref(_attn_desc(batch=1, heads=8, len_q=512)), C.byref(plan)) == 0
     assert plan.tile_q == 128
+    # ... unless there are at least 3/4 of an SM count of pairs and the KV loop is long (2048 keys)
+    assert native_lib.tf_attn_plan(C.byref(_attn_desc(batch=1, heads=16)), C.byref(plan)) == 0      # 128 pairs
+    assert plan.tile_q == 256
+    assert native_lib.tf_attn_plan(C.byref(_attn_desc(batch=1, heads=16, len_kv=1024)), C.byref(plan)) == 0
+    assert plan.tile_q == 128
+    assert native_lib.tf_attn_plan(C.byref(_attn_desc(batch=1, heads=8)), C.byref(plan)) == 0       # 64 pairs
+    assert plan.tile_q == 128
     assert native_lib.tf_attn_plan(C.byref(_attn_desc()), C.byref(plan)) == 0
     assert (plan.k_mn_major, plan.v_mn_major) == (0, 1)     # K [Lk, D], V [Lk, Dv]
     assert 0 < plan.smem_bytes * plan.ctas_per_sm <= 227 * 1024
