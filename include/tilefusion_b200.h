@@ -146,10 +146,11 @@ typedef struct TfAttnPlan {
  * Besides the kernel the call enqueues one 4-byte memset (the work-item
  * counter of the launch) on `stream`; both can be captured into a CUDA graph
  * once a first call on the device has been made outside a capture.  Calls on
- * different streams may overlap; at most 64 launches of the two-tile variant
- * may be in flight at once on a device (they take turns on 64 counter words;
- * launches recorded into CUDA graphs take theirs from a separate set of 64 and
- * keep it for every replay).
+ * different streams may overlap: every stream keeps a counter word of its own
+ * (up to 256 streams per device), and every launch recorded into a CUDA graph
+ * gets a word that no other launch ever uses (up to 4096 recorded launches per
+ * device), so graphs may replay side by side.  Beyond those limits the call
+ * returns TF_ERR_UNSUPPORTED.
  */
 TF_EXPORT int tf_attn_fwd(const void* q, const void* k, const void* v, void* o,
                           float* lse, const TfAttnDesc* desc, void* stream);
@@ -304,6 +305,92 @@ TF_EXPORT int tf_decode_static(const void* q, const void* k, const void* v, void
 /* Size in bytes of the built-in scratch that tf_decode_static uses. */
 TF_EXPORT uint64_t tf_decode_static_capacity(void);
 
+/* ---- single-box multi-GPU layer (one process per GPU) ----------------------
+ * No counterpart in the reference: it has no NCCL / peer-access call site.
+ * Prefill shards by (batch x heads) with no exchange; long-context decode
+ * shards by KV length and exchanges one (O, m, l) row per (batch, head). */
+
+/* [begin, end) of the flattened (batch x heads) axis that `rank` of `world`
+ * processes (contiguous; the first n % world ranks take one more). */
+TF_EXPORT int tf_shard_head_slice(int64_t n_heads_total, int32_t rank, int32_t world,
+                                  int64_t* begin, int64_t* end);
+
+/* [begin, end) of the key axis held by `rank`, boundaries on multiples of
+ * `align` keys (128 keeps every TMA stage inside one shard). */
+TF_EXPORT int tf_shard_kv_slice(int64_t len_kv, int32_t rank, int32_t world, int32_t align,
+                                int64_t* begin, int64_t* end);
+
+/*
+ * Runs this rank's slice of a prefill problem described by `desc` (the FULL
+ * problem: q, k, v, o, lse are the bases of the [B, H, ...] tensors; only the
+ * slice is read or written, so a rank may map only that part).  At most three
+ * tf_attn_fwd launches, no communication.  The slice is returned in
+ * begin_out / end_out (either may be NULL).
+ */
+TF_EXPORT int tf_prefill_sharded(int32_t rank, int32_t world, const void* q, const void* k,
+                                 const void* v, void* o, float* lse, const TfAttnDesc* desc,
+                                 void* stream, int64_t* begin_out, int64_t* end_out);
+
+#define TF_NCCL_ID_BYTES 128
+enum { TF_TRANSPORT_AUTO = 0, TF_TRANSPORT_P2P = 1, TF_TRANSPORT_NCCL = 2 };
+
+/* One rank's state of a KV-sharded decoder (opaque). */
+typedef struct TfShardCtx TfShardCtx;
+
+/* Rank 0 makes the 128-byte NCCL id that every rank passes to tf_shard_create;
+ * the caller carries it to the other ranks by whatever means it has.  NCCL
+ * (libnccl.so.2) is loaded at run time, on first use. */
+TF_EXPORT int tf_shard_unique_id(void* id_out);
+
+/*
+ * Collective over all `world` ranks, each with its GPU current.  Creates the
+ * rank's context for decode problems of (batch, heads, head_dim, dtype): an
+ * NCCL communicator (world > 1), two alternating gather areas of
+ * world * batch*heads * (head_dim+2) fp32 plus one flag word per sender,
+ * arrival counters, and -- for the peer-memory transport -- a table of every
+ * rank's gather buffer mapped into this process through CUDA IPC.
+ * transport: TF_TRANSPORT_P2P (fails if a peer cannot be mapped),
+ * TF_TRANSPORT_NCCL, or TF_TRANSPORT_AUTO (p2p, else nccl on every rank alike;
+ * tf_shard_note then says why).  world == 1 needs no id.
+ */
+TF_EXPORT int tf_shard_create(int32_t rank, int32_t world, const void* nccl_id,
+                              int32_t transport, int32_t batch, int32_t heads,
+                              int32_t head_dim, int32_t dtype, TfShardCtx** out);
+
+/* TF_TRANSPORT_P2P or TF_TRANSPORT_NCCL: what the context uses. */
+TF_EXPORT int tf_shard_transport(const TfShardCtx* ctx);
+TF_EXPORT const char* tf_shard_note(const TfShardCtx* ctx);
+
+/*
+ * One decode step over a KV sequence sharded across the ranks: q [B,H,D]
+ * replicated, k_local / v_local this rank's keys (desc->len_kv of them, may be
+ * 0), o [B,H,D] and lse [B,H] (may be NULL) written on EVERY rank.  Stream-
+ * ordered, no host synchronisation, and every rank must call it once per step.
+ *   p2p : ONE kernel launch -- split-KV pass; the CTA finishing a row's last
+ *         split merges the row and stores it into every rank's gather area;
+ *         the rank's last row raises its flag on every peer; CTAs then wait
+ *         (bounded) for all flags and write the final O / LSE.  Plain peer
+ *         stores and system-scope release/acquire only: no TMA, no multicast
+ *         and no library kernel touch peer memory.  (Grouped-query problems
+ *         take three launches: split, merge + scatter, combine.)
+ *   nccl: the same kernel writes this rank's slot, ncclAllGather in place,
+ *         then the combine kernel.
+ * The split-KV workspace is allocated by the first call and grown only when a
+ * later call needs more; otherwise a step allocates nothing.  If a rank never
+ * arrives, the bounded wait gives up: o / lse of that step read NaN, and the
+ * NEXT call returns TF_ERR_DEVICE_TIMEOUT before launching anything
+ * (tf_device_status clears the condition).  The wait limit (default 2 s,
+ * tf_set_wait_limit_ms) is therefore also the largest skew between ranks that
+ * the p2p transport tolerates.
+ */
+TF_EXPORT int tf_decode_sharded(TfShardCtx* ctx, const void* q, const void* k_local,
+                                const void* v_local, void* o, float* lse,
+                                const TfDecodeDesc* desc, void* stream);
+
+/* Frees the context (synchronises its device).  Collective in the sense that
+ * no peer may still be running a step that stores into this rank's buffer. */
+TF_EXPORT int tf_shard_destroy(TfShardCtx* ctx);
+
 /* ---- diagnostics -------------------------------------------------------- */
 
 /* Text of the last error raised on the calling thread ("" if none). */
@@ -313,8 +400,25 @@ TF_EXPORT const char* tf_last_error(void);
  * Reads and clears the device-side status word of the current device
  * (synchronises the device).  0 = every bounded wait completed; otherwise the
  * code of the first wait that gave up, and TF_ERR_DEVICE_TIMEOUT is returned.
+ * A kernel whose wait gave up leaves its output unwritten (prefill, split
+ * pass) or NaN (the combine behind the gather flags).
  */
 TF_EXPORT int tf_device_status(int32_t* code_out);
+
+/*
+ * The same word without synchronising: the device mirrors it into mapped host
+ * memory the moment a wait gives up, so this only reads a host variable.  It
+ * reports launches that have already failed; it neither waits for running
+ * ones nor clears anything.
+ */
+TF_EXPORT int tf_device_status_peek(int32_t* code_out);
+
+/*
+ * Upper bound of every device-side wait (mbarrier waits of the kernels, the
+ * flag wait of the sharded decode), in milliseconds; default 2000.  Takes
+ * effect on each device with the next launch made through this library.
+ */
+TF_EXPORT int tf_set_wait_limit_ms(uint32_t milliseconds);
 
 /* Library ABI version (bumped when a struct above changes). */
 TF_EXPORT int tf_abi_version(void);

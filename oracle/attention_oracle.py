@@ -173,6 +173,37 @@ def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
     return ((af - bf).norm() / bf.norm().clamp_min(1e-30)).item()
 
 
+# Root-mean-square relative error of rounding to bf16 (8 significant bits),
+# for values spread log-uniformly over a binade: 2^-8 / sqrt(3) * sqrt(E[1/x^2]).
+BF16_ROUNDING_RMS = 1.7e-3
+
+
+def rounding_floor(ref: torch.Tensor, dtype: torch.dtype) -> float:
+    """Relative-L2 error of the *exact* result once rounded to ``dtype``: no
+    kernel that returns ``dtype`` can do better than this on ``ref``."""
+    return rel_l2(ref.float().to(dtype), ref)
+
+
+def rel_l2_bound(ref: torch.Tensor, dtype: torch.dtype, p_rounded: bool = True) -> float:
+    """Bound on relative-L2(O) for an output of ``dtype``.
+
+    fp16: the north-star figure, 1e-3.  bf16: that figure cannot be met -- the
+    rounding of the exact result already costs about 1.7e-3 -- so the bound is
+    computed from the reference itself: the rounding floor of ``ref``, combined
+    in quadrature with a second term of the same size when the kernel feeds the
+    probabilities P to the tensor cores as bf16 (``p_rounded``; each p carries an
+    independent relative error of BF16_ROUNDING_RMS, which reaches O undamped:
+    err(O) = sum p_k d_k (v_k - O) / l has the spread of O itself for zero-mean
+    V), times a 15 % margin, plus 1e-4 for the fp32 arithmetic.  For i.i.d.
+    inputs this comes to about 2.9e-3 with and 2.1e-3 without P rounding; the
+    kernels sit at 2.4e-3 and 1.7e-3."""
+    if dtype != torch.bfloat16:
+        return 1e-3
+    floor = rounding_floor(ref, dtype)
+    extra = BF16_ROUNDING_RMS if p_rounded else 0.0
+    return 1.15 * math.sqrt(floor * floor + extra * extra) + 1e-4
+
+
 def seeded_inputs(seed: int, shape_q, shape_k, shape_v, sigma: float, dtype=torch.float16):
     """i.i.d. N(0, sigma^2) Q, K, V from a CPU generator, drawn in that order in
     fp32 and rounded to ``dtype`` -- the seeded inputs of the benchmark configs."""

@@ -2,8 +2,10 @@
 
 Tolerances (fp16 in, fp32 accumulate, fp16 out): max-abs <= 2e-2 and
 relative-L2 <= 1e-3 on O, |LSE error| <= 1e-3.  For bf16 the output rounding
-alone (8 mantissa bits) gives a relative-L2 of about 1.7e-3, so the bf16 bound
-on relative-L2 is 4e-3; max-abs and LSE bounds are unchanged.
+alone (8 significant bits) gives a relative-L2 of about 1.7e-3, so the bf16
+bound is computed per case from the reference (oracle.rel_l2_bound: rounding
+floor of the exact result and of P in quadrature, +15 %; about 2.9e-3 on
+i.i.d. inputs); max-abs and LSE bounds are unchanged.
 """
 
 import math
@@ -16,14 +18,14 @@ from oracle import attention_oracle as orc
 pytestmark = pytest.mark.gpu
 
 MAX_ABS = 2e-2
-REL_L2 = {torch.float16: 1e-3, torch.bfloat16: 4e-3}
+REL_L2_FP16 = 1e-3
 LSE_ABS = 1e-3
 
 
 def _check(o, lse, ref_o, ref_lse, dtype):
     assert torch.isfinite(o.float()).all(), "kernel left NaN/Inf in O"
     assert orc.max_abs(o.cpu(), ref_o) <= MAX_ABS
-    assert orc.rel_l2(o.cpu(), ref_o) <= REL_L2[dtype]
+    assert orc.rel_l2(o.cpu(), ref_o) <= orc.rel_l2_bound(ref_o, dtype)
     if lse is not None:
         assert torch.isfinite(lse).all(), "kernel left NaN/Inf in LSE"
         assert orc.max_abs(lse.cpu(), ref_lse) <= LSE_ABS
@@ -211,7 +213,7 @@ def test_config2_size_properties_and_subset():
         num += diff.double().pow(2).sum().item()
         den += ref.double().pow(2).sum().item()
         assert (lse[bi] - lse_ref).abs().max().item() <= LSE_ABS
-    assert worst_abs <= MAX_ABS and math.sqrt(num / den) <= REL_L2[torch.float16]
+    assert worst_abs <= MAX_ABS and math.sqrt(num / den) <= REL_L2_FP16
     # (3) rows of softmax sum to one: V = 1 gives O = 1
     ones = torch.ones_like(v[:1])
     o1, _ = attn_fwd(q[:1], k[:1], ones, scale, False)
@@ -244,7 +246,7 @@ def test_config5_size_bf16_subset_and_properties():
     o, lse = attn_fwd(q, k, v, scale, False, poison=False)
     assert device_status() == 0
     sample = [(0, 0), (3, 17), (7, 63), (15, 31), (9, 5), (12, 40), (1, 62), (15, 63)]
-    num = den = 0.0
+    num = den = floor_num = 0.0
     for bi, hi in sample:
         ref, lse_ref = orc.attention_fp32(q[bi, hi], k[bi, hi], v[bi, hi], scale)
         diff = o[bi, hi].float() - ref
@@ -252,7 +254,11 @@ def test_config5_size_bf16_subset_and_properties():
         assert (lse[bi, hi] - lse_ref).abs().max().item() <= LSE_ABS
         num += diff.double().pow(2).sum().item()
         den += ref.double().pow(2).sum().item()
-    assert math.sqrt(num / den) <= REL_L2[torch.bfloat16]
+        floor_num += (ref.to(torch.bfloat16).float() - ref).double().pow(2).sum().item()
+    # the bound of oracle.rel_l2_bound over the sampled heads together: rounding floor
+    # of the exact result and of P in quadrature, +15 % (about 2.9e-3; the kernel: 2.4e-3)
+    floor = math.sqrt(floor_num / den)
+    assert math.sqrt(num / den) <= 1.15 * math.hypot(floor, orc.BF16_ROUNDING_RMS) + 1e-4
     bi, hi = sample[1]
     ref, lse_ref = orc.attention_fp32(q[bi, hi].cpu(), k[bi, hi].cpu(), v[bi, hi].cpu(), scale)
     _check(o[bi, hi], lse[bi, hi], ref, lse_ref, torch.bfloat16)
@@ -285,7 +291,7 @@ def test_causal_heads_in_unequal_blocks():
         num += diff.double().pow(2).sum().item()
         den += ref.double().pow(2).sum().item()
         assert (lse[0, hi] - lse_ref).abs().max().item() <= LSE_ABS
-    assert worst_abs <= MAX_ABS and math.sqrt(num / den) <= REL_L2[torch.float16]
+    assert worst_abs <= MAX_ABS and math.sqrt(num / den) <= REL_L2_FP16
 
 
 def test_overlapping_launches_on_several_streams():

@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol(native_lib):
     assert sorted(declared) == sorted(_cabi.EXPORTED)
     for name in declared:
         assert hasattr(native_lib, name), f"{name} is declared but not exported"
-    assert native_lib.tf_abi_version() == 3
+    assert native_lib.tf_abi_version() == 4
 
 
 def test_struct_layouts_match_header():
@@ -241,3 +241,90 @@ def test_operator_refuses_cpu_tensors():
     q = torch.zeros(64, 128, dtype=torch.float16)
     with pytest.raises((RuntimeError, NotImplementedError)):
         tilefusion.ops.flash_attention(q, q.t(), q, 64, 128, 128, 128, 0.1, False)
+
+
+# ---- multi-GPU layer: slice arithmetic and argument validation (no GPU, no NCCL) ----
+def test_shard_slices_through_the_cabi(native_lib):
+    b, e = C.c_int64(), C.c_int64()
+    for total, world in [(1024, 8), (1024, 3), (5, 8), (256, 1), (0, 4)]:
+        spans = []
+        for r in range(world):
+            assert native_lib.tf_shard_head_slice(total, r, world, C.byref(b), C.byref(e)) == 0
+            spans.append((b.value, e.value))
+        assert spans[0][0] == 0 and spans[-1][1] == total
+        assert all(x[1] == y[0] for x, y in zip(spans, spans[1:]))
+        sizes = [y - x for x, y in spans]
+        assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
+    for lk, world, align in [(131072, 8, 128), (5000, 4, 128), (100, 8, 128), (129, 2, 128), (1000, 3, 256)]:
+        spans = []
+        for r in range(world):
+            assert native_lib.tf_shard_kv_slice(lk, r, world, align, C.byref(b), C.byref(e)) == 0
+            spans.append((b.value, e.value))
+        assert spans[0][0] == 0 and spans[-1][1] == lk
+        assert all(x[1] == y[0] for x, y in zip(spans, spans[1:]))
+        assert all(x % align == 0 for x, y in spans if y > x)
+    assert native_lib.tf_shard_head_slice(8, 8, 8, C.byref(b), C.byref(e)) == _cabi.TF_ERR_BAD_ARG
+    assert "rank 8" in native_lib.tf_last_error().decode()
+    assert native_lib.tf_shard_head_slice(8, 0, 0, C.byref(b), C.byref(e)) == _cabi.TF_ERR_BAD_ARG
+    assert native_lib.tf_shard_kv_slice(8, 0, 1, 0, C.byref(b), C.byref(e)) == _cabi.TF_ERR_BAD_ARG
+    assert native_lib.tf_shard_head_slice(8, 0, 1, None, None) == _cabi.TF_ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("args,code,needle", [
+    ((2, 2, None, 0, 4, 32, 128, 0), _cabi.TF_ERR_BAD_ARG, "rank 2"),
+    ((0, 65, None, 0, 4, 32, 128, 0), _cabi.TF_ERR_BAD_ARG, "world size"),
+    ((0, 1, None, 7, 4, 32, 128, 0), _cabi.TF_ERR_BAD_ARG, "transport"),
+    ((0, 1, None, 0, 0, 32, 128, 0), _cabi.TF_ERR_BAD_ARG, "positive"),
+    ((0, 1, None, 0, 4, 32, 96, 0), _cabi.TF_ERR_UNSUPPORTED, "head_dim"),
+    ((0, 1, None, 0, 4, 32, 128, 9), _cabi.TF_ERR_UNSUPPORTED, "dtype"),
+    ((1, 2, None, 0, 4, 32, 128, 0), _cabi.TF_ERR_BAD_ARG, "nccl_id is null"),
+])
+def test_shard_create_validation_precedes_cuda(native_lib, args, code, needle):
+    ctx = C.c_void_p()
+    rc = native_lib.tf_shard_create(*args, C.byref(ctx))
+    assert rc == code and needle in native_lib.tf_last_error().decode()
+    assert not ctx.value
+    assert native_lib.tf_shard_create(0, 1, None, 0, 4, 32, 128, 0, None) == _cabi.TF_ERR_BAD_ARG
+
+
+def test_sharded_calls_reject_bad_arguments(native_lib):
+    d = _decode_desc(4, 32, 1024)
+    assert native_lib.tf_decode_sharded(None, None, None, None, None, None, C.byref(d), None) == _cabi.TF_ERR_BAD_ARG
+    assert "ctx is null" in native_lib.tf_last_error().decode()
+    assert native_lib.tf_shard_destroy(None) == 0
+    assert native_lib.tf_shard_transport(None) == _cabi.TF_ERR_BAD_ARG
+    assert native_lib.tf_shard_unique_id(None) == _cabi.TF_ERR_BAD_ARG
+    a = _attn_desc()
+    assert native_lib.tf_prefill_sharded(3, 2, None, None, None, None, None, C.byref(a), None, None, None) \
+        == _cabi.TF_ERR_BAD_ARG
+    assert native_lib.tf_prefill_sharded(0, 2, None, None, None, None, None, C.byref(a), None, None, None) \
+        == _cabi.TF_ERR_BAD_ARG
+    assert "non-null" in native_lib.tf_last_error().decode()
+    assert native_lib.tf_prefill_sharded(0, 2, None, None, None, None, None, None, None, None, None) \
+        == _cabi.TF_ERR_BAD_ARG
+
+
+def test_status_peek_and_wait_limit_without_a_device(native_lib):
+    code = C.c_int32(5)
+    assert native_lib.tf_device_status_peek(C.byref(code)) == 0 and code.value == 0
+    assert native_lib.tf_set_wait_limit_ms(0) == _cabi.TF_ERR_BAD_ARG
+    assert native_lib.tf_set_wait_limit_ms(2000) == 0
+
+
+def test_work_item_counter_words_per_stream_and_per_captured_launch(tmp_path):
+    """The word a launch of the two-tile kernel draws its work items from must
+    never be shared by launches that can overlap.  tests/queue_words_test.cc
+    drives tfb::QueueWords (csrc/registry.h) directly."""
+    import shutil
+    import subprocess
+
+    cxx = shutil.which("g++")
+    if cxx is None:
+        pytest.skip("needs g++")
+    exe = tmp_path / "queue_words_test"
+    subprocess.run([cxx, "-std=c++17", "-O1", f"-I{ROOT / 'include'}", f"-I{ROOT / 'tilefusion_b200' / 'csrc'}",
+                    str(ROOT / "tests" / "queue_words_test.cc"), str(ROOT / "tilefusion_b200" / "csrc" / "registry.cc"),
+                    "-pthread", "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "ok" in out.stdout

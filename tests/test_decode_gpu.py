@@ -1,8 +1,10 @@
 """Parity of the CUDA flash-decoding kernels with the oracle, through the C-ABI.
 
-Tolerances: max-abs <= 2e-2, relative-L2 <= 1e-3 (4e-3 for bf16 outputs, whose
-rounding alone is ~1.7e-3), |LSE error| <= 1e-3; fp32 partials are compared
-with relative-L2 <= 1e-5.
+Tolerances: max-abs <= 2e-2, relative-L2 <= 1e-3 for fp16; for bf16 outputs,
+whose rounding alone is ~1.7e-3, the bound is computed from the reference
+(oracle.rel_l2_bound: 1.15 x the rounding floor of the exact result, in
+quadrature with the rounding of P where the tensor-core path rounds it);
+|LSE error| <= 1e-3; fp32 partials are compared with relative-L2 <= 1e-5.
 """
 
 import math
@@ -15,7 +17,7 @@ from oracle import attention_oracle as orc
 pytestmark = pytest.mark.gpu
 
 MAX_ABS = 2e-2
-REL_L2 = {torch.float16: 1e-3, torch.bfloat16: 4e-3}
+REL_L2_FP16 = 1e-3
 LSE_ABS = 1e-3
 
 
@@ -23,10 +25,12 @@ def _inputs(seed, b, h, lk, d, dtype=torch.float16):
     return orc.seeded_inputs(seed, (b, h, 1, d), (b, h, lk, d), (b, h, lk, d), 1.0, dtype)
 
 
-def _check(o, lse, ref_o, ref_lse, dtype):
+def _check(o, lse, ref_o, ref_lse, dtype, p_rounded=False):
+    """p_rounded: the grouped-query path runs on the tensor cores and rounds P to
+    the 16-bit dtype; the one-head-per-KV-head kernel keeps P in fp32."""
     assert torch.isfinite(o.float()).all() and torch.isfinite(lse).all()
     assert orc.max_abs(o.cpu(), ref_o) <= MAX_ABS
-    assert orc.rel_l2(o.cpu(), ref_o) <= REL_L2[dtype]
+    assert orc.rel_l2(o.cpu(), ref_o) <= orc.rel_l2_bound(ref_o, dtype, p_rounded)
     assert orc.max_abs(lse.cpu(), ref_lse) <= LSE_ABS
 
 
@@ -126,7 +130,7 @@ def test_grouped_query_decode(case, dtype):
     o, lse = decode(q.cuda(), k.cuda(), v.cuda())
     g = hq // hkv
     ref, lse_ref = orc.decode_fp32(q, k.repeat_interleave(g, dim=1), v.repeat_interleave(g, dim=1))
-    _check(o, lse, ref, lse_ref, dtype)
+    _check(o, lse, ref, lse_ref, dtype, p_rounded=True)
     assert device_status() == 0
 
 
@@ -211,7 +215,7 @@ def test_config3_size_properties_and_subset():
         num += diff.double().pow(2).sum().item()
         den += ref.double().pow(2).sum().item()
         assert (lse[bi:bi + 1] - lse_ref).abs().max().item() <= LSE_ABS
-    assert worst <= MAX_ABS and math.sqrt(num / den) <= REL_L2[torch.float16]
+    assert worst <= MAX_ABS and math.sqrt(num / den) <= REL_L2_FP16
     o1, _ = decode(q[:2], k[:2], torch.ones_like(v[:2]))
     assert (o1.float() - 1.0).abs().max().item() <= 2e-3
 
@@ -246,7 +250,7 @@ def test_config4_size_subset_sharded_and_properties():
             num += diff.double().pow(2).sum().item()
             den += ref.double().pow(2).sum().item()
             assert (lse[bi:bi + 1, h0:h0 + 8] - lse_ref).abs().max().item() <= LSE_ABS
-    assert worst <= MAX_ABS and math.sqrt(num / den) <= REL_L2[torch.float16]
+    assert worst <= MAX_ABS and math.sqrt(num / den) <= REL_L2_FP16
     ref, lse_ref = orc.decode_fp32(q[2:3, 5:6].cpu(), k[2:3, 5:6].cpu(), v[2:3, 5:6].cpu())
     _check(o[2:3, 5:6], lse[2:3, 5:6], ref, lse_ref, torch.float16)
     # the sharded path on the same tensors (views of the shards, no copies)
@@ -273,31 +277,103 @@ def test_bad_arguments_report_errors():
 def test_missing_peer_is_reported_not_hung():
     """Failure detection: the combine of a KV-sharded decode waits for a flag per
     sending rank.  Here one sender never shows up (its flag stays 0); the bounded
-    wait must give up, the kernel must return, the device status word must name
-    the wait, and the context must stay usable."""
+    wait must give up, the kernel must return NaN rows rather than a plausible
+    result, the status word (and its host-visible mirror, without a
+    synchronisation) must name the wait, and the context must stay usable."""
     import ctypes as C
+    import time
 
     from cabi_helpers import decode, device_status
     from tilefusion_b200 import _cabi
 
     lib = _cabi.lib()
-    b, h, d, n_ranks = 1, 2, 128, 2
-    slots = torch.zeros(n_ranks, b * h * (d + 2), dtype=torch.float32, device="cuda")
-    flags = torch.zeros(n_ranks, dtype=torch.int32, device="cuda")
-    flags[0] = 1                                   # rank 0 "arrived", rank 1 never does
-    o = torch.zeros(b, h, 1, d, dtype=torch.float16, device="cuda")
-    lse = torch.zeros(b, h, 1, dtype=torch.float32, device="cuda")
-    rc = lib.tf_decode_gathered_wait(slots.data_ptr(), flags.data_ptr(), n_ranks, 1, b, h, d, _cabi.TF_F16,
-                                     o.data_ptr(), o.stride(0), o.stride(1), lse.data_ptr(),
-                                     torch.cuda.current_stream().cuda_stream)
-    assert rc == 0                                 # the launch itself succeeds
-    code = C.c_int32(0)
-    rc = lib.tf_device_status(C.byref(code))       # synchronises; the wait has run out by now
-    assert rc == _cabi.TF_ERR_DEVICE_TIMEOUT and code.value == 401
-    assert "wait gave up" in lib.tf_last_error().decode()
-    assert device_status() == 0                    # the word is cleared by the read
+    assert lib.tf_set_wait_limit_ms(0) == _cabi.TF_ERR_BAD_ARG
+    assert lib.tf_set_wait_limit_ms(300) == 0       # the limit is configurable; 0.3 s keeps the test short
+    try:
+        b, h, d, n_ranks = 1, 2, 128, 2
+        slots = torch.zeros(n_ranks, b * h * (d + 2), dtype=torch.float32, device="cuda")
+        flags = torch.zeros(n_ranks, dtype=torch.int32, device="cuda")
+        flags[0] = 1                                   # rank 0 "arrived", rank 1 never does
+        o = torch.zeros(b, h, 1, d, dtype=torch.float16, device="cuda")
+        lse = torch.zeros(b, h, 1, dtype=torch.float32, device="cuda")
+        t0 = time.perf_counter()
+        rc = lib.tf_decode_gathered_wait(slots.data_ptr(), flags.data_ptr(), n_ranks, 1, b, h, d, _cabi.TF_F16,
+                                         o.data_ptr(), o.stride(0), o.stride(1), lse.data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream)
+        assert rc == 0                                 # the launch itself succeeds
+        # the host sees the failure without synchronising: poll the mirror word
+        code = C.c_int32(0)
+        while lib.tf_device_status_peek(C.byref(code)) == 0 and time.perf_counter() - t0 < 10.0:
+            time.sleep(0.01)
+        assert code.value == 401 and time.perf_counter() - t0 < 5.0
+        assert "earlier launch gave up" in lib.tf_last_error().decode()
+        torch.cuda.synchronize()
+        assert torch.isnan(o.float()).all() and torch.isnan(lse).all()   # no plausible-looking garbage
+        rc = lib.tf_device_status(C.byref(code))       # synchronises, reports and clears
+        assert rc == _cabi.TF_ERR_DEVICE_TIMEOUT and code.value == 401
+        assert "wait gave up" in lib.tf_last_error().decode()
+        assert device_status() == 0                    # the word is cleared by the read
+        assert lib.tf_device_status_peek(C.byref(code)) == 0 and code.value == 0
+    finally:
+        assert lib.tf_set_wait_limit_ms(2000) == 0
     # the context is intact: an ordinary decode still runs and is correct
     q, k, v = _inputs(30, 1, 2, 512, 128)
     out, l2 = decode(q.cuda(), k.cuda(), v.cuda())
     ref, lse_ref = orc.decode_fp32(q, k, v)
     _check(out, l2, ref, lse_ref, torch.float16)
+
+
+@pytest.mark.parametrize("transport", ["p2p", "nccl"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_sharded_context_single_rank(transport, dtype):
+    """tf_shard_create / tf_decode_sharded with a world of one: the p2p transport
+    runs split, merge, exchange and final combine in ONE launch (the rank is its
+    own only peer), the nccl transport runs the fused merge into the local slot
+    and the gathered combine.  Several steps reuse the two gather areas, the
+    flags and the arrival counters; a second, longer problem grows the workspace."""
+    from cabi_helpers import device_status
+    from tilefusion_b200.shard import ShardedDecoder
+
+    b, h, d = 2, 8, 128
+    dec = ShardedDecoder(b, h, d, dtype, "cuda", transport=transport)
+    assert dec.transport == transport and dec.world == 1
+    try:
+        for step, lk in enumerate([3000, 3000, 700, 9000, 9000]):
+            q, k, v = _inputs(60 + step, b, h, lk, d, dtype)
+            out = torch.full((b, h, 1, d), float("nan"), dtype=dtype, device="cuda")
+            lse = torch.full((b, h, 1), float("nan"), dtype=torch.float32, device="cuda")
+            dec(q.cuda(), k.cuda(), v.cuda(), out=out, lse=lse)
+            ref, lse_ref = orc.decode_fp32(q, k, v)
+            _check(out, lse, ref, lse_ref, dtype)
+        assert device_status() == 0
+    finally:
+        dec.close()
+
+
+def test_sharded_context_grouped_query_and_head_dim_64():
+    """The grouped-query form takes the three-launch route through the same
+    context; head_dim 64 takes the fused one."""
+    from cabi_helpers import device_status
+    from tilefusion_b200.shard import ShardedDecoder
+
+    b, hq, hkv, lk, d = 2, 8, 2, 2048, 128
+    q, _, _ = _inputs(70, b, hq, 128, d)
+    _, k, v = _inputs(71, b, hkv, lk, d)
+    dec = ShardedDecoder(b, hq, d, torch.float16, "cuda", transport="p2p")
+    try:
+        for _ in range(3):
+            out, lse = dec(q.cuda(), k.cuda(), v.cuda())
+        ref, lse_ref = orc.decode_fp32(q, k.repeat_interleave(hq // hkv, 1), v.repeat_interleave(hq // hkv, 1))
+        _check(out, lse, ref, lse_ref, torch.float16)
+    finally:
+        dec.close()
+    q, k, v = _inputs(72, 3, 5, 1500, 64)
+    dec = ShardedDecoder(3, 5, 64, torch.float16, "cuda")
+    try:
+        for _ in range(2):
+            out, lse = dec(q.cuda(), k.cuda(), v.cuda())
+        ref, lse_ref = orc.decode_fp32(q, k, v)
+        _check(out, lse, ref, lse_ref, torch.float16)
+        assert device_status() == 0
+    finally:
+        dec.close()

@@ -54,9 +54,9 @@ def test_shapes_through_cabi(m, n, k, p, dtype):
     _cabi.check(rc)
     ref = orc.fused_two_gemms_fp32(a.cpu(), b.cpu(), c.cpu())
     assert torch.isfinite(d.float()).all()
-    # output rounding: 2^-11 (fp16) / 2^-8 (bf16) relative
-    tol = 1e-3 if dtype == torch.float16 else 4e-3
-    assert orc.rel_l2(d.cpu(), ref) <= tol
+    # fp16: 1e-3.  bf16: the oracle rounds the intermediate product exactly as the
+    # kernel does, so only the rounding of the output is left: 1.15 x its floor
+    assert orc.rel_l2(d.cpu(), ref) <= orc.rel_l2_bound(ref, dtype, p_rounded=False)
     assert device_status() == 0
 
 

@@ -30,7 +30,12 @@ EXPORTED = (
     "tf_last_error", "tf_device_status", "tf_abi_version",
     "tf_decode_static", "tf_decode_static_capacity",
     "tf_decode_partial_scatter", "tf_decode_gathered_wait", "tf_fused_two_gemms",
+    "tf_shard_head_slice", "tf_shard_kv_slice", "tf_prefill_sharded", "tf_shard_unique_id",
+    "tf_shard_create", "tf_shard_transport", "tf_shard_note", "tf_decode_sharded", "tf_shard_destroy",
+    "tf_device_status_peek", "tf_set_wait_limit_ms",
 )
+TF_NCCL_ID_BYTES = 128
+TF_TRANSPORT_AUTO, TF_TRANSPORT_P2P, TF_TRANSPORT_NCCL = 0, 1, 2
 
 
 class TfAttnDesc(C.Structure):
@@ -123,8 +128,21 @@ def lib() -> C.CDLL:
     handle.tf_decode_static_capacity.argtypes = []
     handle.tf_last_error.restype = C.c_char_p
     handle.tf_device_status.argtypes = [C.POINTER(C.c_int32)]
+    handle.tf_device_status_peek.argtypes = [C.POINTER(C.c_int32)]
+    handle.tf_set_wait_limit_ms.argtypes = [C.c_uint32]
+    handle.tf_shard_head_slice.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]
+    handle.tf_shard_kv_slice.argtypes = [i64, i32, i32, i32, C.POINTER(i64), C.POINTER(i64)]
+    handle.tf_prefill_sharded.argtypes = [i32, i32, vp, vp, vp, vp, fp, C.POINTER(TfAttnDesc), vp,
+                                          C.POINTER(i64), C.POINTER(i64)]
+    handle.tf_shard_unique_id.argtypes = [vp]
+    handle.tf_shard_create.argtypes = [i32, i32, vp, i32, i32, i32, i32, i32, C.POINTER(vp)]
+    handle.tf_shard_transport.argtypes = [vp]
+    handle.tf_shard_note.argtypes = [vp]
+    handle.tf_shard_note.restype = C.c_char_p
+    handle.tf_decode_sharded.argtypes = [vp, vp, vp, vp, vp, fp, C.POINTER(TfDecodeDesc), vp]
+    handle.tf_shard_destroy.argtypes = [vp]
     for name in EXPORTED:
-        if name not in ("tf_last_error", "tf_decode_static_capacity"):
+        if name not in ("tf_last_error", "tf_decode_static_capacity", "tf_shard_note"):
             getattr(handle, name).restype = C.c_int
     handle.tf_decode_static_capacity.restype = C.c_uint64
     _lib = handle

@@ -87,20 +87,18 @@ def _run(cmd: list[str]) -> None:
 def build_library(force: bool = False, verbose: bool = False) -> Path:
     """Compile the kernels + C-ABI into ``libtilefusion_b200.so``."""
     out = PKG_DIR / LIB_NAME
-    sources = [CSRC / "api.cu", CSRC / "registry.cc"]
+    sources = [CSRC / "api.cu", CSRC / "registry.cc", CSRC / "shard.cc"]
     deps = sources + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [
         INCLUDE / "tilefusion_b200.h"
     ]
-    # TF_NVCC_EXTRA: extra compiler flags (e.g. "-DTF_PAIR_SPLIT_P=0") for tuning runs.
-    extra = os.environ.get("TF_NVCC_EXTRA", "").split()
-    digest = _source_hash(deps, " ".join(NVCC_FLAGS + extra))
+    digest = _source_hash(deps, " ".join(NVCC_FLAGS))
     if not force and _up_to_date(out, digest):
         return out
     with _BuildLock():
         if not force and _up_to_date(out, digest):
             return out
         tmp = out.with_suffix(".so.tmp")
-        cmd = [_nvcc(), *NVCC_FLAGS, *extra, f"-I{INCLUDE}", f"-I{CSRC}", "-shared", "-o", str(tmp)]
+        cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "-shared", "-o", str(tmp), "-ldl"]
         if verbose:
             cmd += ["-Xptxas", "-v"]
         cmd += [str(s) for s in sources]

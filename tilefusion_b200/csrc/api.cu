@@ -19,6 +19,7 @@
 #include "attn_fwd_sm100.cuh"
 #include "attn_fwd_pair_sm100.cuh"
 #include "decode_sm100.cuh"
+#include "internal.h"
 #include "registry.h"
 #include "tilefusion_b200.h"
 
@@ -33,6 +34,8 @@ int fail(int code, const char* fmt, ...) {
   va_end(ap);
   return code;
 }
+
+constexpr int kMaxDevices = 64;
 
 #define TF_CUDA_TRY(expr)                                                          \
   do {                                                                             \
@@ -230,32 +233,43 @@ int launch_two_gemms(const AttnLaunch& L, const TfAttnDesc* d, cudaStream_t stre
   return TF_OK;
 }
 
-// Item counters of the two-tile kernel: every launch takes the next of these
-// words (round robin), zeroes it on its stream and hands it to the kernel, whose
-// CTAs draw their work items from it.  Launches that overlap in time (different
-// streams) therefore use different words, up to kPairQueues of them in flight.
-// A launch recorded into a CUDA graph keeps its word for every replay, so
-// captured launches take theirs from a second set that eager launches never use.
-constexpr int kPairQueues = 64;
-static __device__ int g_pair_queue[2 * kPairQueues];
+// Item counters of the two-tile kernel.  A launch zeroes one of these words on
+// its stream and hands it to the kernel, whose CTAs draw their work items from
+// it.  tfb::QueueWords (registry.h) decides which word: one per stream for
+// eager launches, a fresh one for every launch recorded into a CUDA graph.
+static __device__ int g_pair_queue[tfb::QueueWords::kWords];
 
-int* pair_queue_word(cudaStream_t stream) {
-  static thread_local int cached_device = -1;
-  static thread_local int* base = nullptr;
-  static std::atomic<unsigned> next_eager{0}, next_captured{0};
+struct PairQueues {
+  tfb::QueueWords words;
+  std::mutex mutex;
+  int* base = nullptr;      // device address of g_pair_queue on this device
+};
+PairQueues g_pair_queues[kMaxDevices];
+
+int pair_queue_word(cudaStream_t stream, int** out) {
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-  if (cached_device != dev) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_pair_queue) != cudaSuccess) return nullptr;
-    base = static_cast<int*>(p);
-    cached_device = dev;
+  TF_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(TF_ERR_UNSUPPORTED, "device index %d is out of range", dev);
+  PairQueues& q = g_pair_queues[dev];
+  {
+    std::lock_guard<std::mutex> lock(q.mutex);
+    if (q.base == nullptr) {
+      void* p = nullptr;
+      TF_CUDA_TRY(cudaGetSymbolAddress(&p, g_pair_queue));
+      q.base = static_cast<int*>(p);
+    }
   }
   cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) return nullptr;
-  if (cap == cudaStreamCaptureStatusActive)
-    return base + kPairQueues + next_captured.fetch_add(1, std::memory_order_relaxed) % kPairQueues;
-  return base + next_eager.fetch_add(1, std::memory_order_relaxed) % kPairQueues;
+  TF_CUDA_TRY(cudaStreamIsCapturing(stream, &cap));
+  const bool capturing = cap == cudaStreamCaptureStatusActive;
+  const int idx = capturing ? q.words.captured() : q.words.eager(reinterpret_cast<uintptr_t>(stream));
+  if (idx < 0)
+    return fail(TF_ERR_UNSUPPORTED,
+                capturing ? "more than %d launches of the two-tile kernel have been recorded into CUDA graphs on this device"
+                          : "more than %d streams have launched the two-tile kernel on this device",
+                capturing ? tfb::QueueWords::kCapturedWords : tfb::QueueWords::kEagerWords);
+  *out = q.base + idx;
+  return TF_OK;
 }
 
 // Two Q tiles per CTA, persistent grid of one CTA per SM.
@@ -295,8 +309,7 @@ int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan&
     const long long n_blocks = std::max(1ll, (n_bh + fit / 2) / fit);
     a.causal_block = (int)((n_bh + n_blocks - 1) / n_blocks);
   }
-  a.queue = pair_queue_word(stream);
-  if (a.queue == nullptr) return fail(TF_ERR_CUDA, "cannot resolve the item counter of the two-tile kernel");
+  if (int rc = pair_queue_word(stream, &a.queue)) return rc;
   TF_CUDA_TRY(cudaMemsetAsync(a.queue, 0, sizeof(int), stream));
   a.kv_splits = kv_splits;
   a.tiles_per_split = tiles_per_split;
@@ -359,10 +372,12 @@ bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0;
 
 template <typename T, int D>
 int launch_decode_split(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
-                        const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream) {
+                        const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream,
+                        const tfb::DecodeFuseArgs* fuse = nullptr) {
   constexpr int kStages = 3;
   using Smem = tfb::DecodeSmem<D, kStages>;
   tfb::DecodeSplitArgs a;
+  a.fuse = fuse != nullptr ? *fuse : tfb::DecodeFuseArgs{};
   a.q = q;
   a.k = k;
   a.v = v;
@@ -473,14 +488,18 @@ int launch_gqa_split(const void* q, const void* k, const void* v, float* part_o,
              : launch_attn_pair<__nv_bfloat16, 64>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages);
 }
 
+bool is_grouped(const TfDecodeDesc* d) { return d->heads_kv > 0 && d->heads_kv != d->heads; }
+
+// `fuse` (one query head per KV head only): merge, exchange and final combine in the same launch.
 int dispatch_split(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
-                   const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream) {
-  if (d->heads_kv > 0 && d->heads_kv != d->heads) return launch_gqa_split(q, k, v, part_o, part_ml, d, plan, stream);
+                   const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream,
+                   const tfb::DecodeFuseArgs* fuse = nullptr) {
+  if (is_grouped(d)) return launch_gqa_split(q, k, v, part_o, part_ml, d, plan, stream);
   if (d->head_dim == 128)
-    return d->dtype == TF_F16 ? launch_decode_split<__half, 128>(q, k, v, part_o, part_ml, d, plan, stream)
-                              : launch_decode_split<__nv_bfloat16, 128>(q, k, v, part_o, part_ml, d, plan, stream);
-  return d->dtype == TF_F16 ? launch_decode_split<__half, 64>(q, k, v, part_o, part_ml, d, plan, stream)
-                            : launch_decode_split<__nv_bfloat16, 64>(q, k, v, part_o, part_ml, d, plan, stream);
+    return d->dtype == TF_F16 ? launch_decode_split<__half, 128>(q, k, v, part_o, part_ml, d, plan, stream, fuse)
+                              : launch_decode_split<__nv_bfloat16, 128>(q, k, v, part_o, part_ml, d, plan, stream, fuse);
+  return d->dtype == TF_F16 ? launch_decode_split<__half, 64>(q, k, v, part_o, part_ml, d, plan, stream, fuse)
+                            : launch_decode_split<__nv_bfloat16, 64>(q, k, v, part_o, part_ml, d, plan, stream, fuse);
 }
 
 int plan_and_check_decode(const void* q, const void* k, const void* v, const void* workspace,
@@ -494,7 +513,7 @@ int plan_and_check_decode(const void* q, const void* k, const void* v, const voi
   if (workspace_bytes < plan->workspace_bytes)
     return fail(TF_ERR_WORKSPACE, "workspace holds %llu bytes but %llu are needed",
                 (unsigned long long)workspace_bytes, (unsigned long long)plan->workspace_bytes);
-  return TF_OK;
+  return tfb::ensure_device_ready();
 }
 
 // ---- scratch for tf_decode_static -------------------------------------------
@@ -505,7 +524,6 @@ int plan_and_check_decode(const void* q, const void* k, const void* v, const voi
 constexpr uint64_t kStaticScratchBytes = 4ull << 20;
 static __device__ __align__(256) float g_decode_scratch[kStaticScratchBytes / sizeof(float)];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_scratch_mutex;
 float* g_scratch_ptr[kMaxDevices] = {};
 
@@ -527,7 +545,128 @@ int static_scratch(float** out) {
   return TF_OK;
 }
 
+
+// ---- per-device state shared by the entry points ----------------------------
+struct DeviceState {
+  bool ready = false;
+  int* mirror_host = nullptr;                 // mapped host copy of the device status word
+  unsigned long long limit_applied_ns = 0;    // value of g_wait_limit_ns on the device
+};
+std::mutex g_device_mutex;
+DeviceState g_device[kMaxDevices];
+std::atomic<unsigned long long> g_wait_limit_ns_host{2000000000ull};
+
 }  // namespace
+
+namespace tfb {
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int ensure_device_ready() {
+  int dev = 0;
+  TF_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(TF_ERR_UNSUPPORTED, "device index %d is out of range", dev);
+  const unsigned long long limit = g_wait_limit_ns_host.load(std::memory_order_relaxed);
+  static thread_local int ready_device = -1;
+  static thread_local unsigned long long ready_limit = 0;
+  if (ready_device == dev && ready_limit == limit) return TF_OK;
+  std::lock_guard<std::mutex> lock(g_device_mutex);
+  DeviceState& st = g_device[dev];
+  if (!st.ready) {
+    // One mapped host word per device: a device-side wait that gives up stores its
+    // code there too, so the host can see a failed launch without synchronising.
+    void* host = nullptr;
+    TF_CUDA_TRY(cudaHostAlloc(&host, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
+    *static_cast<volatile int*>(host) = 0;
+    void* mapped = nullptr;
+    TF_CUDA_TRY(cudaHostGetDevicePointer(&mapped, host, 0));
+    TF_CUDA_TRY(cudaMemcpyToSymbol(tfb::g_status_mirror, &mapped, sizeof(mapped)));
+    st.mirror_host = static_cast<int*>(host);
+    st.limit_applied_ns = 2000000000ull;
+    st.ready = true;
+  }
+  if (st.limit_applied_ns != limit) {
+    TF_CUDA_TRY(cudaMemcpyToSymbol(tfb::g_wait_limit_ns, &limit, sizeof(limit)));
+    st.limit_applied_ns = limit;
+  }
+  ready_device = dev;
+  ready_limit = limit;
+  return TF_OK;
+}
+
+int launch_sharded_decode(const void* q, const void* k, const void* v, void* o, float* lse,
+                          const TfDecodeDesc* d, const ShardStep& st, cudaStream_t stream) {
+  TfDecodePlan plan;
+  if (int rc = plan_and_check_decode(q, k, v, st.workspace, st.workspace_bytes, d, &plan)) return rc;
+  const bool p2p = st.peer_table != nullptr;
+  if (p2p && o == nullptr) return fail(TF_ERR_BAD_ARG, "o is null");
+  if (int rc = ensure_device_ready()) return rc;
+  const int rows = d->batch * d->heads;
+  const int D = d->head_dim;
+  const long long slot_floats = (long long)rows * (D + 2);
+  const long long my_slot = st.area_offset + (long long)st.rank * slot_floats;
+  float* part_o = static_cast<float*>(st.workspace);
+  float* part_ml = part_o + (int64_t)rows * plan.num_splits * D;
+  const unsigned* local_flags = reinterpret_cast<const unsigned*>(st.local_base + st.flag_offset);
+  if (!is_grouped(d)) {
+    // one launch: split, merge, exchange, final combine
+    DecodeFuseArgs f{};
+    f.row_arrivals = st.row_arrivals;
+    f.rows_done = st.rows_done;
+    f.rows = rows;
+    f.peer_bases = st.peer_table;
+    f.out_slot = st.local_base + my_slot;
+    f.n_peers = st.n_ranks;
+    f.my_rank = st.rank;
+    f.slot_offset = my_slot;
+    f.flag_offset = st.flag_offset;
+    f.step = st.step;
+    f.final_phase = p2p ? 1 : 0;
+    f.local_area = st.local_base + st.area_offset;
+    f.local_flags = local_flags;
+    f.o = o;
+    f.o_stride_b = d->o_stride_b;
+    f.o_stride_h = d->o_stride_h;
+    f.lse = lse;
+    return dispatch_split(q, k, v, part_o, part_ml, d, plan, stream, &f);
+  }
+  // grouped-query heads run on the two-tile kernel, which has no fused tail:
+  // split pass, merge (+ scatter to the peers), then the combine behind the flags
+  if (int rc = dispatch_split(q, k, v, part_o, part_ml, d, plan, stream)) return rc;
+  DecodeCombineArgs a{};
+  a.part_o = part_o;
+  a.part_ml = part_ml;
+  a.n_parts = plan.num_splits;
+  a.part_stride_o = D;
+  a.row_stride_o = (int64_t)plan.num_splits * D;
+  a.part_stride_ml = 2;
+  a.row_stride_ml = (int64_t)plan.num_splits * 2;
+  a.heads = d->heads;
+  if (p2p) {
+    a.peer_bases = st.peer_table;
+    a.n_peers = st.n_ranks;
+    a.my_rank = st.rank;
+    a.rows_total = rows;
+    a.scatter_offset = my_slot;
+    a.flag_offset = st.flag_offset;
+    a.step = st.step;
+  } else {
+    a.out_part_o = st.local_base + my_slot;
+    a.out_part_ml = a.out_part_o + (long long)rows * D;
+  }
+  if (int rc = dispatch_combine(a, rows, D, d->dtype, stream)) return rc;
+  if (!p2p) return TF_OK;
+  return tf_decode_gathered_wait(st.local_base + st.area_offset, local_flags, st.n_ranks, st.step, d->batch,
+                                 d->heads, D, d->dtype, o, d->o_stride_b, d->o_stride_h, lse, stream);
+}
+
+}  // namespace tfb
 
 extern "C" {
 
@@ -548,6 +687,7 @@ int tf_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   if (q == nullptr || k == nullptr || v == nullptr || o == nullptr)
     return fail(TF_ERR_BAD_ARG, "q, k, v and o must be non-null");
   if (!aligned16(o)) return fail(TF_ERR_UNSUPPORTED, "o must be 16-byte aligned");
+  if (int rc = tfb::ensure_device_ready()) return rc;
   TfAttnPlan plan;
   tfb::plan_attn(*desc, sm_count(), &plan);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -570,6 +710,7 @@ int tf_fused_two_gemms(const void* a, const void* b, const void* c, void* d, int
     return fail(TF_ERR_UNSUPPORTED, "fused_two_gemms needs k == p in {64, 128} (got k=%d, p=%d)", k, p);
   if (lda < k || ldb < k || ldc < n || ldd < p) return fail(TF_ERR_BAD_ARG, "a leading dimension is smaller than its row");
   if (!aligned16(d) || ldd % 8 != 0) return fail(TF_ERR_UNSUPPORTED, "d must be 16-byte aligned with ldd a multiple of 8");
+  if (int rc = tfb::ensure_device_ready()) return rc;
   TfAttnDesc desc{};
   desc.dtype = dtype;
   desc.batch = desc.heads = 1;
@@ -689,6 +830,7 @@ int tf_decode_gathered_wait(const float* slots, const uint32_t* flags, int32_t n
   if (n_ranks < 1 || n_ranks > 64 || batch < 1 || heads < 1)
     return fail(TF_ERR_BAD_ARG, "n_ranks (<= 64), batch and heads must be positive");
   if (dtype != TF_F16 && dtype != TF_BF16) return fail(TF_ERR_UNSUPPORTED, "dtype code %d is not fp16 or bf16", dtype);
+  if (int rc = tfb::ensure_device_ready()) return rc;
   const int64_t rows = (int64_t)batch * heads;
   const int64_t slot_floats = rows * (head_dim + 2);
   tfb::DecodeCombineArgs a{};
@@ -792,21 +934,35 @@ int tf_device_status(int32_t* code_out) {
     const int zero = 0;
     TF_CUDA_TRY(cudaMemcpyToSymbol(tfb::g_status_word, &zero, sizeof(int)));
   }
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices) {
+    std::lock_guard<std::mutex> lock(g_device_mutex);
+    if (g_device[dev].mirror_host != nullptr) *static_cast<volatile int*>(g_device[dev].mirror_host) = 0;
+  }
   if (code_out != nullptr) *code_out = code;
   if (code != 0) return fail(TF_ERR_DEVICE_TIMEOUT, "a device-side wait gave up (site code %d)", code);
   return TF_OK;
 }
 
-int tf_abi_version(void) { return 3; }
+int tf_device_status_peek(int32_t* code_out) {
+  int code = 0, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices) {
+    std::lock_guard<std::mutex> lock(g_device_mutex);
+    if (g_device[dev].mirror_host != nullptr) code = *static_cast<volatile int*>(g_device[dev].mirror_host);
+  }
+  if (code_out != nullptr) *code_out = code;
+  if (code != 0)
+    return fail(TF_ERR_DEVICE_TIMEOUT, "a device-side wait of an earlier launch gave up (site code %d); its output is not valid",
+                code);
+  return TF_OK;
+}
 
-#ifdef TF_PAIR_TRACE
-// Debug builds only: copies the phase trace of CTA 0 (3 roles x 1024 records).
-__attribute__((visibility("default"))) int tf_debug_pair_trace(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, tfb::g_pair_trace, sizeof(unsigned long long) * 9 * 1024);
+int tf_set_wait_limit_ms(uint32_t milliseconds) {
+  if (milliseconds == 0) return fail(TF_ERR_BAD_ARG, "the wait limit must be positive");
+  g_wait_limit_ns_host.store((unsigned long long)milliseconds * 1000000ull, std::memory_order_relaxed);
+  return TF_OK;
 }
-__attribute__((visibility("default"))) int tf_debug_pair_cta_time(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, tfb::g_pair_cta_time, sizeof(unsigned long long) * 256 * 4);
-}
-#endif
+
+int tf_abi_version(void) { return 4; }
 
 }  // extern "C"

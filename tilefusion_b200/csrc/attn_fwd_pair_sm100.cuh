@@ -51,29 +51,8 @@ constexpr int kPairStages = 3;        // K/V ring of a prefill launch (a deeper 
 // serve as two more ring stages.
 constexpr int kPairMaxStages = kPairStages + 2;
 constexpr int kItemSlots = 4;         // ring of work-item coordinates in shared memory
-#ifndef TF_PAIR_STREAM
-#define TF_PAIR_STREAM 1              // 0: do not issue the next item's first S tiles early (comparison builds)
-#endif
-#ifndef TF_PAIR_ALWAYS_MAX
-#define TF_PAIR_ALWAYS_MAX 0          // 1: take the row maximum of every tile (comparison builds)
-#endif
 // Largest sum of 64 values of P published without a look at the row maximum.
 constexpr float kPairSumLimit = 4096.0f;
-
-// Optional phase trace of CTA 0 (debug builds only, -DTF_PAIR_TRACE): one
-// thread per role appends (event, tile, clock) records to a device array.
-#ifdef TF_PAIR_TRACE
-__device__ unsigned long long g_pair_cta_time[256][4];   // per CTA: globaltimer start/end, clock64 start/end
-__device__ unsigned long long g_pair_trace[9][1024];
-__device__ __forceinline__ void pair_trace(int role, int& n, int event, int tile) {
-  if (blockIdx.x == 0 && n < 1024)
-    g_pair_trace[role][n++] = ((unsigned long long)event << 56) | ((unsigned long long)(tile & 0xFFFF) << 40) |
-                              (clock64() & 0xFFFFFFFFFFull);
-}
-#define PAIR_TRACE(role, n, event, tile) pair_trace(role, n, event, tile)
-#else
-#define PAIR_TRACE(role, n, event, tile)
-#endif
 
 struct AttnPairArgs {
   AttnFwdArgs base;
@@ -222,12 +201,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
   const uint32_t n_stages = pargs.kv_splits > 0 ? kPairMaxStages : kPairStages;
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
-#ifdef TF_PAIR_TRACE
-  if (threadIdx.x == 0 && blockIdx.x < 256) {
-    g_pair_cta_time[blockIdx.x][0] = global_timer_ns();
-    g_pair_cta_time[blockIdx.x][2] = clock64();
-  }
-#endif
 
   // Item ring: the n-th item of this CTA sits in slot n % kItemSlots.
   volatile PairItem* item_ring = reinterpret_cast<volatile PairItem*>(smem_gen + S::kOffItems);
@@ -417,9 +390,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       uint32_t items_done[2] = {0, 0};     // epilogues awaited per Q tile
       bool first_s_issued = false;         // the current item's first S tiles were issued during the previous item
       bool ok = true;
-#ifdef TF_PAIR_TRACE
-      int tn = 0;
-#endif
 
       // Operand B addressing, in 16-byte units: MMA step k (16 elements along the
       // contraction) starts at (k >> 2) * step_hi + (k & 3) * step_lo.
@@ -488,12 +458,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         // and waiting for the next item's operands at that point would hold up
         // the last P.V of Q tile 1 (measured slower).
         int nx2[2] = {0, 0};
-        if (TF_PAIR_STREAM && nx[0] == nx[1] && nxt.b >= 0) {
+        if (nx[0] == nx[1] && nxt.b >= 0) {
           const int pair2 = nxt.pair, split2 = nxt.split;
           nx2[0] = kv_tiles_for(pargs, pair2 * 2 * kAttnTile, split2, j0_unused);
           nx2[1] = kv_tiles_for(pargs, pair2 * 2 * kAttnTile + kAttnTile, split2, j0_unused);
         }
-        PAIR_TRACE(8, tn, 16, 0);
         uint32_t k_smem = 0, k_stage = 0, v_smem = 0, v_stage = 0;
         if (!first_s_issued) {
           // first item of this CTA: both first S tiles back to back
@@ -503,11 +472,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
             ++q_cnt[x];
           }
           if (!ok) break;
-          PAIR_TRACE(8, tn, 17, 0);
           ok = next_stage(k_smem, k_stage);
           if (!ok) break;
           tc_fence_after();
-          PAIR_TRACE(8, tn, 18, 0);
           for (int x = 0; x < 2; ++x) {
             if (nx[x] == 0) continue;
             issue_s(x, k_smem);
@@ -530,13 +497,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                 if (!ok) break;
               }
               tc_fence_after();
-              PAIR_TRACE(8, tn, 10 + x, j);
               issue_pv_half(x, 0, v_smem, j > 0);
               ok = mbar_wait_warp(bar(S::kBarPFullHi + x), p_cnt[x] & 1, abort_flag, kPWaitPFull);
               if (!ok) break;
               ++p_cnt[x];
               tc_fence_after();
-              PAIR_TRACE(8, tn, 12 + x, j);
               issue_pv_half(x, 1, v_smem, true);
             }
             if (leader && (x == 1)) umma_commit(bar(S::kBarKVEmpty + v_stage));
@@ -547,7 +512,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                 have_k = true;
               }
               issue_s(x, k_smem);
-              PAIR_TRACE(8, tn, 14 + x, j);
               if (leader && (j + 2 == nx[x])) umma_commit(bar(S::kBarQEmpty + x));
             } else if (j + 1 == n && nx2[x] > 0) {
               // first S tile of the next item (its K tile is the next ring stage)
@@ -561,7 +525,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
               }
               tc_fence_after();
               issue_s(x, k_smem);
-              PAIR_TRACE(8, tn, 14 + x, j);
               if (leader && (nx2[x] == 1)) umma_commit(bar(S::kBarQEmpty + x));
             }
             if (leader && (x == 1 && have_k)) umma_commit(bar(S::kBarKVEmpty + k_stage));
@@ -589,13 +552,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     uint32_t out_cnt = 0;    // items whose output went through the staging buffer
     uint32_t o_base = 0;     // PV completions of earlier items
     bool ok = true;
-#ifdef TF_PAIR_TRACE
-    int tn = 0;
-    const bool tracer = (lane == 0);
-#define SM_TRACE(event, tile) if (tracer) PAIR_TRACE(warp, tn, event, tile)
-#else
-#define SM_TRACE(event, tile)
-#endif
 
     // Second part of an item's epilogue, run for the item in ring slot `slot`:
     // O / l out of TMEM to global memory, then the item's slot is given back.
@@ -606,7 +562,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       have_pending = false;
       if (!__all_sync(0xffffffffu, mbar_wait(bar_o, (o_base - 1) & 1, abort_flag, kPWaitEpi))) return false;
       tc_fence_after();
-      SM_TRACE(5, 0);
       // (batch, head and split are read again here rather than kept in registers
       // through the KV loop; the slot is this thread's until it moves on)
       const int b = item_ring[slot].b, h = item_ring[slot].h;
@@ -638,7 +593,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
         mbar_arrive(bar(S::kBarItemEmpty + slot));
-        SM_TRACE(6, 0);
         return true;
       }
       if (pargs.tma_store) {
@@ -720,7 +674,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       }
       mbar_arrive(bar(S::kBarItemEmpty + slot));
-      SM_TRACE(6, 0);
       return true;
     };
 
@@ -752,7 +705,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         if (!ok) break;
         ++s_cnt;
         tc_fence_after();
-        SM_TRACE(0, j);
 
         // Load the whole S row (four 32-column chunks) into registers.
         const int kv0 = (j0 + j) * kAttnTile;
@@ -762,7 +714,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + col_s + c * 32, sr[c]);
         tmem_wait_ld();
-        SM_TRACE(4, j);
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -873,15 +824,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         float no_extra = 0.f;
         if (j == 0) {
           ok = raise_max(row_max(0, 4), no_extra, false, 0, 0, 0);
-          SM_TRACE(1, j);
-        } else if (TF_PAIR_ALWAYS_MAX) {
-          // (comparison build: the row maximum of every tile, rescale when it grew by 2^8)
-          const float m_tile = row_max(0, 4);
-          if (__any_sync(0xffffffffu, (m_tile - m_used) * args.scale_log2 > kRescaleThreshold)) {
-            ok = raise_max(m_tile, no_extra, true, bar_o, (o_base + j - 1) & 1, kPWaitOFull);
-            if (!ok) break;
-          }
-          SM_TRACE(1, j);
         }
         float lo_sum = p_half(0);
         if (j > 0 && __any_sync(0xffffffffu, !(lo_sum <= kPairSumLimit))) {
@@ -893,7 +835,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p);
-        SM_TRACE(2, j);
         float hi_sum = p_half(1);
         if (j > 0 && __any_sync(0xffffffffu, !(hi_sum <= kPairSumLimit))) {
           // P.V of the first half (this tile) is in flight or done: wait for it,
@@ -907,7 +848,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p_hi);
-        SM_TRACE(3, j);
         l_run += lo_sum + hi_sum;
         if (j == 0) {
           // the previous item's O can leave now: its last P.V has had a whole
@@ -941,7 +881,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       pend_inv_l = 1.0f / l_run;
       have_pending = true;
       o_base += n_kv;
-      SM_TRACE(6, n_kv);
     }
   }
 
@@ -954,12 +893,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     __syncwarp();
     tmem_dealloc<kTmemCols>(tmem_base);
   }
-#ifdef TF_PAIR_TRACE
-  if (threadIdx.x == 0 && blockIdx.x < 256) {
-    g_pair_cta_time[blockIdx.x][1] = global_timer_ns();
-    g_pair_cta_time[blockIdx.x][3] = clock64();
-  }
-#endif
 }
 
 }  // namespace tfb

@@ -241,7 +241,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         // retires its shared memory.
         const unsigned long long t0 = global_timer_ns();
         while ((k_seen < k_issued || v_seen < v_issued) &&
-               global_timer_ns() - t0 < kWaitLimitNs) {
+               global_timer_ns() - t0 < wait_limit_ns()) {
           if (k_seen < k_issued && mbar_try_wait(bar_k, k_seen & 1)) ++k_seen;
           if (v_seen < v_issued && mbar_try_wait(bar_v, v_seen & 1)) ++v_seen;
         }

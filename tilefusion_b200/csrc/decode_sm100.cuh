@@ -24,6 +24,15 @@
 // final O (16-bit) and LSE (natural log), or one merged partial row (used when
 // the KV sequence is sharded across GPUs and the merge continues after an
 // all-gather).
+//
+// KV sharded across GPUs: with DecodeFuseArgs set, decode_split_kernel carries
+// the exchange itself.  The CTA that finishes the last split of a (b, h) merges
+// that row's partials and stores the merged (O, m, l) row straight into the
+// gather area of every rank through peer-mapped pointers; the CTA that
+// completes the rank's last row raises this rank's flag on every peer; and
+// CTAs then wait (bounded) for all ranks' flags and write the final O / LSE
+// for their rows -- split, all-gather and combine in one launch.  Only plain
+// peer stores and system-scope release/acquire touch peer memory.
 #pragma once
 
 #include <type_traits>
@@ -36,6 +45,31 @@ constexpr int kDecKeysPerStage = 128;
 constexpr int kDecConsumerThreads = 256;
 constexpr int kDecThreads = kDecConsumerThreads + 32;
 constexpr int kDecMaxChunk = 1024;        // keys; bounds the score buffers
+
+// Fused merge / exchange / final combine of a KV-sharded decode step (all
+// fields zero: the split pass only writes its partial rows).
+struct DecodeFuseArgs {
+  unsigned* row_arrivals;     // [rows], zero between steps: splits of a (b,h) finished so far
+  unsigned* rows_done;        // one word, zero between steps: merged rows of this rank
+  int rows;                   // batch * heads
+  // Destination of the merged rows: every peer's gather area (peer_bases[p] +
+  // slot_offset floats; rows*D of O, then rows*2 of (m, l)), or out_slot alone.
+  float* const* peer_bases;   // device array [n_peers], or null
+  float* out_slot;
+  int n_peers;
+  int my_rank;
+  long long slot_offset;
+  long long flag_offset;      // floats from a peer base to its flag words (one per sender)
+  unsigned step;              // value the flags receive; grows by one per step
+  // Final phase (p2p only): wait for all senders' flags, then combine the
+  // n_peers gathered rows of each (b,h) into O / LSE.
+  int final_phase;
+  const float* local_area;    // this rank's current gather area: [n_peers][rows*(D+2)]
+  const unsigned* local_flags;
+  void* o;
+  long long o_stride_b, o_stride_h;
+  float* lse;                 // [rows] or null
+};
 
 struct DecodeSplitArgs {
   const void* q;
@@ -58,6 +92,7 @@ struct DecodeSplitArgs {
   int page_size;
   int max_pages;
   long long k_stride_page, v_stride_page;
+  DecodeFuseArgs fuse;
 };
 
 template <int D, int kStages>
@@ -69,11 +104,41 @@ struct DecodeSmem {
   static constexpr int kGroups = kDecConsumerThreads / (D / 8);
   static constexpr int kOffWarp = kOffRed + kGroups * D * 4;            // 16 fp32 scratch
   static constexpr int kOffBar = kOffWarp + 64;                         // 2*kStages mbarriers
-  static constexpr int kOffAbort = kOffBar + 2 * kStages * 8;
+  static constexpr int kOffAbort = kOffBar + 2 * kStages * 8;            // abort flag, then two flag words of the fused tail
   static constexpr int kBytes = kOffAbort + 16 + 128;                   // + alignment slack
 };
 
 enum DecodeWaitCode { kWaitDecEmpty = 201, kWaitDecFullK = 202, kWaitDecFullV = 203 };
+enum CombineWaitCode { kWaitGatherFlag = 401 };
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait until the flag word has reached `step` (flags only grow).  False
+// when the wait gave up; the status word then holds kWaitGatherFlag.
+__device__ __forceinline__ bool wait_gather_flag(const unsigned* flag, unsigned step) {
+  const unsigned long long t0 = global_timer_ns();
+  while ((int)(ld_acquire_sys(flag) - step) < 0) {
+    if (global_timer_ns() - t0 > wait_limit_ns()) {
+      report_wait_timeout((int)kWaitGatherFlag);
+      return false;
+    }
+  }
+  return true;
+}
+
+template <typename T>
+__device__ __forceinline__ T to_out(float v);
+template <>
+__device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerThreads) : "memory");
@@ -95,6 +160,8 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
   float* red = reinterpret_cast<float*>(smem_gen + S::kOffRed);
   float* warp_scratch = reinterpret_cast<float*>(smem_gen + S::kOffWarp);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
+  volatile int* s_last = abort_flag + 1;       // this CTA finished the last split of the current row
+  volatile int* s_gave_up = abort_flag + 2;    // the wait for the peers' flags ran out
   const uint32_t bar_full = smem_base + S::kOffBar;
   const uint32_t bar_empty = smem_base + S::kOffBar + kStages * 8;
 
@@ -108,6 +175,8 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
       mbar_init(bar_empty + s * 8, kDecConsumerThreads / 32);
     }
     *abort_flag = 0;
+    *s_last = 0;
+    *s_gave_up = 0;
     mbar_fence_init();
   }
   __syncthreads();
@@ -368,6 +437,90 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
         args.part_ml[(long long)item * 2 + 0] = m_run;
         args.part_ml[(long long)item * 2 + 1] = l;
       }
+
+      if (args.fuse.row_arrivals != nullptr) {
+        // ---- fused merge: whoever finishes a row's last split merges the row ----
+        const DecodeFuseArgs& f = args.fuse;
+        __threadfence();                 // this item's partial row is visible device-wide ...
+        consumer_sync();
+        if (tid == 0)                    // ... before its arrival is counted
+          *s_last = (atomicAdd(f.row_arrivals + bh, 1u) == (unsigned)args.num_splits - 1u) ? 1 : 0;
+        consumer_sync();
+        if (*s_last) {
+          __threadfence();
+          if (tid < D) {
+            // (partial rows written by other SMs: read past L1)
+            const float* ml = args.part_ml + (long long)bh * args.num_splits * 2;
+            const float* po = args.part_o + (long long)bh * args.num_splits * D;
+            float m = -INFINITY;
+            for (int p = 0; p < args.num_splits; ++p) m = fmaxf(m, __ldcg(ml + 2 * p));
+            float acc_o = 0.f, l = 0.f;
+            for (int p = 0; p < args.num_splits; ++p) {
+              const float mp = __ldcg(ml + 2 * p), lp = __ldcg(ml + 2 * p + 1);
+              const float w = (mp == -INFINITY) ? 0.f : fast_exp2(mp - m);
+              l = fmaf(lp, w, l);
+              acc_o = fmaf(__ldcg(po + (long long)p * D + tid), w, acc_o);
+            }
+            const int n_dst = f.peer_bases != nullptr ? f.n_peers : 1;
+            for (int p = 0; p < n_dst; ++p) {
+              float* base = f.peer_bases != nullptr ? f.peer_bases[p] + f.slot_offset : f.out_slot;
+              base[(long long)bh * D + tid] = acc_o;
+              if (tid == 0) {
+                float* mlp = base + (long long)f.rows * D + (long long)bh * 2;
+                mlp[0] = m;
+                mlp[1] = l;
+              }
+            }
+          }
+          if (tid == 0) f.row_arrivals[bh] = 0;      // re-armed for the next step
+          __threadfence_system();                    // my peer stores are performed before the row is counted
+          consumer_sync();
+          if (tid == 0) {
+            if (atomicAdd(f.rows_done, 1u) == (unsigned)f.rows - 1u) {
+              // the rank's last row: re-arm the counter and raise this rank's flag everywhere
+              *f.rows_done = 0;
+              __threadfence_system();
+              if (f.peer_bases != nullptr)
+                for (int p = 0; p < f.n_peers; ++p)
+                  st_release_sys(reinterpret_cast<unsigned*>(f.peer_bases[p] + f.flag_offset) + f.my_rank, f.step);
+            }
+          }
+        }
+      }
+    }
+
+    if (ok && args.fuse.final_phase) {
+      // ---- final combine of the gathered rows, once every sender's flag is up ----
+      const DecodeFuseArgs& f = args.fuse;
+      bool waited = false;
+      for (int row = blockIdx.x; row < f.rows; row += gridDim.x) {
+        if (!waited) {
+          if (tid < f.n_peers && !wait_gather_flag(f.local_flags + tid, f.step)) *s_gave_up = 1;
+          consumer_sync();
+          waited = true;
+        }
+        if (tid < D) {
+          const long long slot_floats = (long long)f.rows * (D + 2);
+          const float* ml = f.local_area + (long long)f.rows * D + (long long)row * 2;
+          const float* po = f.local_area + (long long)row * D + tid;
+          float m = -INFINITY;
+          for (int p = 0; p < f.n_peers; ++p) m = fmaxf(m, __ldcg(ml + p * slot_floats));
+          float acc_o = 0.f, l = 0.f;
+          for (int p = 0; p < f.n_peers; ++p) {
+            const float mp = __ldcg(ml + p * slot_floats), lp = __ldcg(ml + p * slot_floats + 1);
+            const float w = (mp == -INFINITY) ? 0.f : fast_exp2(mp - m);
+            l = fmaf(lp, w, l);
+            acc_o = fmaf(__ldcg(po + p * slot_floats), w, acc_o);
+          }
+          // a wait that gave up must not pass for a result: the rows read NaN
+          const bool bad = *s_gave_up != 0;
+          const int b = row / args.heads, h = row - b * args.heads;
+          T* op = reinterpret_cast<T*>(f.o) + b * f.o_stride_b + h * f.o_stride_h;
+          op[tid] = to_out<T>(bad ? __int_as_float(0x7fc00000) : acc_o / l);
+          if (tid == 0 && f.lse != nullptr)
+            f.lse[row] = bad ? __int_as_float(0x7fc00000) : 0.6931471805599453f * (m + log2f(l));
+        }
+      }
     }
   }
 }
@@ -408,17 +561,6 @@ struct DecodeCombineArgs {
 // may be in flight per device).
 __device__ unsigned int g_scatter_done = 0;
 
-enum CombineWaitCode { kWaitGatherFlag = 401 };
-
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
 constexpr int kCombineGroups = 4;
 
 // grid = rows, block = (D, kCombineGroups).  Thread (d, j) walks parts j,
@@ -436,20 +578,17 @@ __global__ void __launch_bounds__(D * kCombineGroups) decode_combine_kernel(cons
   const float* ml = a.part_ml + (long long)row * a.row_stride_ml;
   const float* po = a.part_o + (long long)row * a.row_stride_o;
 
+  __shared__ int s_gave_up;
   if (a.wait_flags != nullptr) {
     // Bounded wait for the peers' stores (flags are written with release
     // semantics after a system-scope fence on the sending GPU).
-    if (tid < a.wait_n) {
-      const unsigned long long t0 = global_timer_ns();
-      while ((int)(ld_acquire_sys(a.wait_flags + tid) - a.wait_step) < 0) {
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
-          atomicCAS(&g_status_word, 0, (int)kWaitGatherFlag);
-          break;
-        }
-      }
-    }
+    if (tid == 0) s_gave_up = 0;
+    __syncthreads();
+    if (tid < a.wait_n && !wait_gather_flag(a.wait_flags + tid, a.wait_step)) s_gave_up = 1;
     __syncthreads();
   }
+  // a wait that gave up must not pass for a result: the row reads NaN
+  const bool bad = a.wait_flags != nullptr && s_gave_up != 0;
 
   // pass 1: global maximum
   float m = -INFINITY;
@@ -500,13 +639,9 @@ __global__ void __launch_bounds__(D * kCombineGroups) decode_combine_kernel(cons
     } else {
       const int b = row / a.heads, h = row - b * a.heads;
       T* op = reinterpret_cast<T*>(a.o) + b * a.o_stride_b + h * a.o_stride_h;
-      const float val = o / lt;
-      if constexpr (std::is_same<T, __half>::value) {
-        op[d] = __float2half_rn(val);
-      } else {
-        op[d] = __float2bfloat16_rn(val);
-      }
-      if (d == 0 && a.lse != nullptr) a.lse[row] = 0.6931471805599453f * (m + log2f(lt));
+      const float nan = __int_as_float(0x7fc00000);
+      op[d] = to_out<T>(bad ? nan : o / lt);
+      if (d == 0 && a.lse != nullptr) a.lse[row] = bad ? nan : 0.6931471805599453f * (m + log2f(lt));
     }
   }
   if (a.peer_bases != nullptr) {

@@ -130,4 +130,25 @@ void plan_decode(const TfDecodeDesc& d, int sm_count, TfDecodePlan* plan) {
   plan->workspace_bytes = (uint64_t)bh * splits * (d.head_dim + 2) * sizeof(float);
 }
 
+int QueueWords::eager(uintptr_t stream) {
+  std::lock_guard<std::mutex> lock(mutex_);
+  for (int i = 0; i < n_streams_; ++i)
+    if (streams_[i] == stream) return i;
+  if (n_streams_ == kEagerWords) return -1;
+  streams_[n_streams_] = stream;
+  return n_streams_++;
+}
+
+int QueueWords::captured() {
+  std::lock_guard<std::mutex> lock(mutex_);
+  if (n_captured_ == kCapturedWords) return -1;
+  return kEagerWords + n_captured_++;
+}
+
+void shard_range(int64_t total, int rank, int world, int64_t* begin, int64_t* end) {
+  const int64_t base = total / world, extra = total % world;
+  *begin = rank * base + std::min<int64_t>(rank, extra);
+  *end = *begin + base + (rank < extra ? 1 : 0);
+}
+
 }  // namespace tfb

@@ -19,9 +19,14 @@ namespace tfb {
 // exactly one translation unit (the library is built without relocatable
 // device code), which therefore owns the definition.
 __device__ int g_status_word = 0;
+// Optional mirror of the status word in mapped host memory (set once per device
+// by the host library; null until then).  A wait that gives up also stores its
+// code there, so the host can notice a failed launch without synchronising.
+__device__ int* g_status_mirror = nullptr;
 
-// Upper bound for one wait, in nanoseconds of %globaltimer.
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+// Upper bound for one wait, in nanoseconds of %globaltimer (tf_set_wait_limit_ms
+// changes it).  Read only on the slow path of a wait.
+__device__ unsigned long long g_wait_limit_ns = 2000000000ull;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -31,6 +36,21 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+
+// Records that the wait at site `code` gave up: first code wins in the device
+// status word, and the host-visible mirror (if set up) receives it as well.
+__device__ __noinline__ void report_wait_timeout(int code) {
+  atomicCAS(&g_status_word, 0, code);
+  int* mirror = *reinterpret_cast<int* volatile*>(&g_status_mirror);
+  if (mirror != nullptr) {
+    *reinterpret_cast<volatile int*>(mirror) = code;
+    __threadfence_system();
+  }
+}
+
+__device__ __forceinline__ unsigned long long wait_limit_ns() {
+  return *reinterpret_cast<volatile unsigned long long*>(&g_wait_limit_ns);
 }
 
 // ---------------------------------------------------------------- mbarrier --
@@ -78,9 +98,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 0x3Fu) == 0) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > wait_limit_ns()) {
         *abort_flag = code;
-        atomicCAS(&g_status_word, 0, code);
+        report_wait_timeout(code);
         return false;
       }
     }

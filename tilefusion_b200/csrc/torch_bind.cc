@@ -52,6 +52,18 @@ int dtype_code(const at::Tensor& t) {
 
 void check_status(int rc) { TORCH_CHECK(rc == TF_OK, "tilefusion_b200: ", tf_last_error()); }
 
+// Raises if a device-side wait of an EARLIER launch on this device gave up (its
+// output was left unwritten or NaN).  Costs one read of a host variable; the
+// condition is cleared so that the error is raised once.
+void check_earlier_launches() {
+  int32_t code = 0;
+  if (tf_device_status_peek(&code) != TF_OK) {
+    tf_device_status(nullptr);
+    TORCH_CHECK(false, "tilefusion_b200: a device-side wait of an earlier launch gave up (site code ", code,
+                "); the output of that launch is not valid");
+  }
+}
+
 // Splits leading dims of a [..., rows, cols] tensor into (batch, heads) with
 // element strides; 2-D tensors are one (batch, head).
 struct Lead {
@@ -106,17 +118,15 @@ void attention_impl(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& 
   d.k_stride_d = K.stride(-1);
   d.v_stride_b = lv.stride_b;
   d.v_stride_h = lv.stride_h;
-  // The reference operand is V^T [..., Dv, Lk]; the natural [..., Lk, Dv] form
-  // is accepted when the shape is unambiguous.
-  if (V.size(-2) == d.head_dim_v && V.size(-1) == d.len_kv) {
-    d.v_stride_d = V.stride(-2);
-    d.v_stride_l = V.stride(-1);
-  } else {
-    TORCH_CHECK(V.size(-2) == d.len_kv && V.size(-1) == d.head_dim_v,
-                "V must be [..., Dv, Lk] (or [..., Lk, Dv]) with Lk = K.size(-2), Dv = O.size(-1)");
-    d.v_stride_l = V.stride(-2);
-    d.v_stride_d = V.stride(-1);
-  }
+  // The operand is V^T [..., Dv, Lk], as in the reference.  A caller holding V
+  // as [..., Lk, Dv] passes V.transpose(-1, -2): a view, nothing is copied (the
+  // kernels read either memory layout).  The shape alone cannot tell the two
+  // apart when Lk == Dv, so no other form is accepted.
+  TORCH_CHECK(V.size(-2) == d.head_dim_v && V.size(-1) == d.len_kv,
+              "V must be V^T, [..., Dv, Lk], with Lk = K.size(-2) and Dv = O.size(-1); pass "
+              "value.transpose(-1, -2) (a view) for a value stored [..., Lk, Dv]");
+  d.v_stride_d = V.stride(-2);
+  d.v_stride_l = V.stride(-1);
   d.o_stride_b = lo.stride_b;
   d.o_stride_h = lo.stride_h;
   d.o_stride_l = O.stride(-2);
@@ -132,6 +142,7 @@ void attention_impl(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& 
     lse_ptr = LSE->data_ptr<float>();
   }
   const c10::cuda::CUDAGuard guard(Q.device());
+  check_earlier_launches();
   check_status(tf_attn_fwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), lse_ptr, &d,
                            at::cuda::getCurrentCUDAStream().stream()));
 }
@@ -201,6 +212,7 @@ void flash_decoding(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& 
   d.o_stride_b = O.stride(0);
   d.o_stride_h = O.stride(1);
   const c10::cuda::CUDAGuard guard(Q.device());
+  check_earlier_launches();
   at::Tensor ws = decode_workspace(d, Q);
   check_status(tf_decode(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), LSE.data_ptr<float>(),
                          ws.data_ptr(), (uint64_t)ws.numel() * 4, &d,
