@@ -21,11 +21,29 @@ over one batch of synthetic input:
                         combine (strong scaling).
 
 `value` is measured with inputs resident in HBM, CUDA events on the launching
-stream, max over ranks.  `e2e` is the same metric through the public Python
-operator with inputs copied from pinned host memory and the result copied back
-inside the timed region.  `roofline` describes the dominant kernel against the
-measured peaks in MEASURED_PEAKS.json; `cpu_baseline` times the oracle (the
-reference's torch expression, fp32) on the host cores on a bounded sample.
+stream, max over ranks: W warm-up steps, then timed regions of exactly K steps
+each, bracketed by a barrier and a device synchronisation on both sides.  The
+region is repeated (a short idle gap in between, so that every region starts
+from the same burst state a kernel timed alone sees) until about a quarter of
+a second has been spent under load; `value` and `ms_per_step` are the median
+region, `region_ms_per_step` lists them all, and `clocks` holds the NVML
+samples that fell inside the regions.  `e2e` is the same metric through the
+public Python operator with inputs copied from pinned host memory and the
+result copied back inside the timed region.  `roofline` describes the dominant
+kernel against the measured peaks in MEASURED_PEAKS.json; `cpu_baseline` times
+the oracle (the reference's torch expression, fp32) on the host cores on a
+bounded sample.
+
+Besides the headline workload the default line carries, at every N:
+  decode      decode_c3, one batch per rank
+  decode_c4   long-context decode with the KV length sharded over the N ranks
+              (N = 1: the whole sequence on one GPU), both transports, with a
+              parity object: every rank evaluates the fp32 expression on its own
+              KV shard for two (batch, head) rows, the partial rows are gathered
+              and merged by the oracle's combine, and the kernel's O / LSE are
+              held against that
+  prefill_c5  bf16 B16 H64 L8192, batch x heads split over the N ranks
+  causal      prefill_c2 with the causal mask (FLOPs of unmasked pairs only)
 
 `--impl reference` times that CPU expression alone, as the reference arm.
 """
@@ -67,28 +85,43 @@ WORKLOADS["decode_gqa_profile"] = dict(WORKLOADS["decode_gqa"], B=16)
 WORKLOADS["decode_c4_shard8"] = dict(WORKLOADS["decode_c4"], L=131072 // 8, scaling="weak")
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)   # earlier measurement on this pool
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant
-# kernel from the ncu captures summarised under profiles/, per (batch, head)
-# problem of the captured case; traffic grows in proportion to batch x heads,
-# so a launch is scaled by the problems it processes.
-NCU_TRAFFIC_PER_HEAD = {
-    # attn_fwd_pair_kernel, B4 H32 L2048 D128 fp16: 203.0 MB read + 46.9 MB written over 128 heads
-    ("prefill", 2048, 128): (203.0e6 + 46.9e6) / 128,
-    # decode_split_kernel, B4 H32 Lk8192 D128 fp16: 536.9 MB read + 3.8 MB written over 128 heads
-    ("decode", 8192, 128): (536.9e6 + 3.8e6) / 128,
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel
+# comes from the ncu captures summarised under profiles/: NCU_TRAFFIC.json (beside
+# profiles/) holds, per kernel and captured case, the bytes of one launch, the (batch, head)
+# problems that launch processed, and a hash of the kernel's source files at the
+# time of the capture.  Traffic grows in proportion to the problems processed, so a
+# launch is scaled by that; when the kernel source has changed since the capture the
+# figure is withheld (null) rather than carried over.
+KERNEL_SOURCES = {
+    "attn_fwd_pair_kernel": ("attn_fwd_pair_sm100.cuh", "sm100_ptx.cuh"),
+    "decode_split_kernel": ("decode_sm100.cuh", "sm100_ptx.cuh"),
 }
-# attn_fwd_pair_kernel in split-KV mode, B16 Hq32 Hkv8 Lk8192 D128 fp16: 537.2 MB read + 5.9 MB
-# written over 128 (batch, KV head) groups
-NCU_TRAFFIC_PER_KV_HEAD_GQA = {("decode", 8192, 128): (537.2e6 + 5.9e6) / 128}
 
 
-def ncu_traffic(w, heads_in_launch):
-    if "Hkv" in w:      # grouped-query decode: traffic scales with the KV heads
-        per_head = NCU_TRAFFIC_PER_KV_HEAD_GQA.get((w["kind"], w["L"], w["D"]))
-        heads_in_launch = heads_in_launch // w["H"] * w["Hkv"]
-    else:
-        per_head = NCU_TRAFFIC_PER_HEAD.get((w["kind"], w["L"], w["D"]))
-    return None if per_head is None else per_head * heads_in_launch
+def kernel_source_hash(kernel):
+    import hashlib
+
+    h = hashlib.sha256()
+    for name in KERNEL_SOURCES[kernel]:
+        h.update((ROOT / "tilefusion_b200" / "csrc" / name).read_bytes())
+    return h.hexdigest()[:16]
+
+
+def ncu_traffic(w, units_in_launch):
+    """(bytes per launch or None, note).  `units_in_launch`: (batch, head) problems
+    for one-head-per-KV-head workloads, (batch, KV head) groups for grouped-query."""
+    table = ROOT / "NCU_TRAFFIC.json"
+    if not table.exists():
+        return None, "no capture recorded"
+    kernel = "attn_fwd_pair_kernel" if (w["kind"] == "prefill" or "Hkv" in w) else "decode_split_kernel"
+    case = f"{w['kind']}{'_gqa' if 'Hkv' in w else ''}_L{w['L']}_D{w['D']}"
+    entry = json.loads(table.read_text()).get(kernel, {}).get(case)
+    if entry is None:
+        return None, f"no capture of {kernel} for {case}"
+    if entry["source_hash"] != kernel_source_hash(kernel):
+        return None, f"{kernel} changed since its capture ({entry['capture']}); not carried over"
+    per_unit = (entry["dram_bytes_read"] + entry["dram_bytes_write"]) / entry["units"]
+    return per_unit * units_in_launch, f"{entry['capture']}, scaled by problems per launch"
 
 
 def peaks():
@@ -123,7 +156,7 @@ class ClockSampler:
     }
 
     def __init__(self, device_index: int):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.reasons, self.max_mhz, self.timed = [], set(), None, []
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -140,18 +173,25 @@ class ClockSampler:
 
     def _sample(self):
         try:
-            self.samples.append(self._nv.nvmlDeviceGetClockInfo(self._h, self._nv.NVML_CLOCK_SM))
+            mhz = self._nv.nvmlDeviceGetClockInfo(self._h, self._nv.NVML_CLOCK_SM)
             mask = self._nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
-            for bit, name in self.REASONS.items():
-                if mask & bit:
-                    self.reasons.add(name)
+            self.timed.append((time.perf_counter(), mhz, mask))
         except Exception:
             pass
 
     def _run(self):
         while not self._stop.is_set():
             self._sample()
-            time.sleep(0.005)
+            time.sleep(0.001)
+
+    def keep_within(self, windows):
+        """Keeps the samples taken inside the (start, end) host-time windows."""
+        for t, mhz, mask in self.timed:
+            if any(a <= t <= b for a, b in windows):
+                self.samples.append(mhz)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
 
     def __enter__(self):
         if self._nv is not None:
@@ -169,7 +209,8 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
         s = sorted(self.samples)
         return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(s)}
+                "samples": len(s), "sm_mhz_min": s[0], "sm_mhz_all": self.samples,
+                "sampled": "NVML, 1 ms period, samples inside the timed regions only"}
 
 
 # ------------------------------------------------------------------- inputs --
@@ -288,132 +329,204 @@ def workload_config(w, name, n_gpus, causal=False):
             "heads": w["H"], "len_q": w["L"] if w["kind"] == "prefill" else 1, "len_kv": w["L"],
             "head_dim": w["D"], "causal": bool(causal), "softmax_scale": "1/sqrt(D)",
             "sharding": ("batch x heads, no collective" if w["kind"] == "prefill" or w["scaling"] == "weak"
-                         else "KV length + NCCL all-gather of (m,l,O) rows"),
-            "l2": "inputs larger than L2 (126 MB); no flush between steps"}
+                         else "KV length; (O, m, l) rows exchanged by peer stores inside the decode kernel, "
+                              "or by one NCCL all-gather"),
+            "l2": "inputs larger than L2 (126 MB); no flush between steps",
+            "timing": "median of repeated regions of exactly `steps` steps, idle gap between regions"}
 
 
 # ------------------------------------------------------------- GPU timing ----
-def time_steps(fn, steps, warmup, device, world, sampler_holder=None):
-    """W warm-up steps, then K steps bracketed by barrier+synchronize; CUDA events on
-    the current stream; returns max-over-ranks seconds."""
+TARGET_LOADED_S = 0.25     # time under load over which clock samples are collected
+MAX_REPEATS = 25
+IDLE_GAP_S = 0.02
+
+
+def time_steps(fn, steps, warmup, device, world, max_repeats=MAX_REPEATS):
+    """W warm-up steps, then regions of exactly `steps` steps, each bracketed by
+    barrier + synchronize on both sides and timed with CUDA events on the current
+    stream, max over ranks.  Returns (median seconds per region, info)."""
     import torch.distributed as dist
+
+    def fence():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
 
     for _ in range(warmup):
         fn()
-    torch.cuda.synchronize(device)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize(device)
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(device.index if device.index is not None else 0)
+    regions, windows = [], []
     with sampler:
-        start.record()
-        for _ in range(steps):
-            fn()
-        end.record()
-        end.synchronize()
-    torch.cuda.synchronize(device)
-    if world > 1:
-        dist.barrier()
-    secs = start.elapsed_time(end) / 1e3
-    if world > 1:
-        t = torch.tensor([secs], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        secs = t.item()
-    if sampler_holder is not None:
-        sampler_holder.append(sampler.summary())
-    return secs
+        repeats = 1
+        r = 0
+        while r < repeats:
+            fence()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            start.record()
+            for _ in range(steps):
+                fn()
+            end.record()
+            end.synchronize()
+            t1 = time.perf_counter()
+            fence()
+            secs = start.elapsed_time(end) / 1e3
+            if world > 1:
+                t = torch.tensor([secs], dtype=torch.float64, device=device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                secs = t.item()
+            regions.append(secs)
+            windows.append((t0, t1))
+            if r == 0:      # every rank derives the same count from the max-over-ranks time
+                repeats = int(max(1, min(max_repeats, math.ceil(TARGET_LOADED_S / max(secs, 1e-6)))))
+            r += 1
+            if r < repeats:
+                time.sleep(IDLE_GAP_S)
+    sampler.keep_within(windows)
+    ordered = sorted(regions)
+    median = ordered[len(ordered) // 2]
+    info = {"clocks": sampler.summary(), "repeats": len(regions),
+            "region_ms_per_step": [round(x / steps * 1e3, 5) for x in regions]}
+    return median, info
 
 
-def run_prefill(args, w, name, device, rank, world):
-    import ctypes as C
-
+def attn_desc_for(q, k, v, o, dtype_name, scale, causal):
     from tilefusion_b200 import _cabi
-    import tilefusion_b200 as tilefusion
 
-    lib = _cabi.lib()
-    # local batch: weak scaling keeps B per rank; strong scaling splits batch x heads
-    causal = bool(getattr(args, "causal", False))
-    if w["scaling"] == "weak":
-        b_local, h_local = w["B"], w["H"]
-        total_units = prefill_flops(w["B"] * world, w["H"], w["L"], w["L"], w["D"], causal)
-    else:
-        from tilefusion_b200.shard import head_slice
-
-        h0, h1 = head_slice(w["B"] * w["H"], rank, world)
-        b_local, h_local = (h1 - h0), 1         # flattened heads as the batch axis
-        total_units = prefill_flops(w["B"], w["H"], w["L"], w["L"], w["D"], causal)
-    wl = dict(w, H=h_local, seed=w["seed"] + 1000 * rank)
-    q, k, v = make_inputs(wl, device, b=b_local)
-    o = torch.empty_like(q)
-    scale = 1.0 / math.sqrt(w["D"])
     d = _cabi.TfAttnDesc()
-    d.dtype = _cabi.TF_F16 if w["dtype"] == "fp16" else _cabi.TF_BF16
-    d.batch, d.heads, d.len_q, d.len_kv, d.head_dim, d.head_dim_v = b_local, h_local, w["L"], w["L"], w["D"], w["D"]
+    d.dtype = _cabi.TF_F16 if dtype_name == "fp16" else _cabi.TF_BF16
+    d.batch, d.heads, d.len_q, d.head_dim = q.shape
+    d.len_kv, d.head_dim_v = k.size(2), v.size(3)
     d.softmax_scale = scale
     d.causal = int(causal)
     d.q_stride_b, d.q_stride_h, d.q_stride_l = q.stride(0), q.stride(1), q.stride(2)
     d.k_stride_b, d.k_stride_h, d.k_stride_l, d.k_stride_d = k.stride()
     d.v_stride_b, d.v_stride_h, d.v_stride_l, d.v_stride_d = v.stride()
     d.o_stride_b, d.o_stride_h, d.o_stride_l = o.stride(0), o.stride(1), o.stride(2)
-    stream = torch.cuda.current_stream(device).cuda_stream
-    qp, kp, vp, op = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    return d
 
-    def step():
-        rc = lib.tf_attn_fwd(qp, kp, vp, op, None, C.byref(d), stream)
-        if rc != 0:
-            _cabi.check(rc)
 
-    clocks = []
-    secs = time_steps(step, args.steps, args.warmup, device, world, clocks)
-    value = total_units * args.steps / secs / 1e12
-    per_launch_s = secs / args.steps
-    local_flops = prefill_flops(b_local, h_local, w["L"], w["L"], w["D"], causal)
+def gpu_attention_fp32(q, k, v, scale, causal):
+    """softmax(q k^T * scale [+ mask]) v and LSE in fp32 with torch on the device,
+    for one (batch, head): q [Lq, D], k/v [Lk, D].  Used for parity only."""
+    s = (q.float() @ k.float().t()) * scale
+    if causal:
+        lq, lk = s.shape
+        s = s.masked_fill(torch.arange(lk, device=s.device)[None, :] > torch.arange(lq, device=s.device)[:, None],
+                          float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    return torch.exp(s - lse[:, None]) @ v.float(), lse
 
+
+def prefill_roofline(w, local_flops, per_launch_s, units, loaded_s, reasons):
     pk = peaks()
     # A kernel timed alone in a short region is held against the burst cuBLAS figure;
     # when the timed region is long enough to run into the power cap (seconds-long
     # loops, sw_power_cap active) the sustained figure is the like-for-like peak.
-    sustained = ("sw_power_cap" in clocks[0]["reasons"] or secs > 0.5) and pk.get("bf16_tflops_sustained", 0) > 0
+    sustained = ("sw_power_cap" in reasons or loaded_s > 0.5) and pk.get("bf16_tflops_sustained", 0) > 0
     peak_tf = pk["bf16_tflops_sustained"] if sustained else pk["bf16_tflops"]
-    roof = {"bound": "tensor", "achieved": local_flops / per_launch_s / 1e12, "peak": peak_tf,
-            "unit": "TFLOP/s", "frac": local_flops / per_launch_s / 1e12 / peak_tf,
-            "traffic": ncu_traffic(w, b_local * h_local), "kernel": "attn_fwd_pair_kernel",
-            "algorithmic_bytes": 4.0 * b_local * h_local * w["L"] * w["D"] * 2,
+    ach = local_flops / per_launch_s / 1e12
+    traffic, note = ncu_traffic(w, units)
+    return {"bound": "tensor", "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
+            "traffic": traffic, "traffic_source": note, "kernel": "attn_fwd_pair_kernel",
+            "algorithmic_bytes": 4.0 * units * w["L"] * w["D"] * 2,
             "peak_source": pk["source"] + (" (sustained cuBLAS bf16, power-capped loop)" if sustained
                                            else " (burst cuBLAS bf16)"),
-            "frac_of_burst": local_flops / per_launch_s / 1e12 / pk["bf16_tflops"],
-            "frac_of_nominal_2250": local_flops / per_launch_s / 1e12 / 2250.0}
-    if args.profile:
-        return dict(value=value, unit="TFLOP/s", secs=secs, clocks=clocks[0], roofline=roof,
-                    launches=args.steps)
+            "frac_of_burst": ach / pk["bf16_tflops"],
+            "frac_of_sustained": (ach / pk["bf16_tflops_sustained"]) if pk.get("bf16_tflops_sustained") else None,
+            "frac_of_nominal_2250": ach / 2250.0}
 
-    # parity spot check on one (b, h) against the oracle
+
+def run_prefill(args, w, name, device, rank, world, causal=False, steps=None, warmup=None, with_e2e=True):
+    import ctypes as C
+
+    from tilefusion_b200 import _cabi
+    import tilefusion_b200 as tilefusion
+
+    steps = args.steps if steps is None else steps
+    warmup = args.warmup if warmup is None else warmup
+    lib = _cabi.lib()
+    scale = 1.0 / math.sqrt(w["D"])
+    stream = torch.cuda.current_stream(device).cuda_stream
+    if w["scaling"] == "weak":
+        # every rank runs its own batch of the same shape
+        b_local, h_local = w["B"], w["H"]
+        total_units = prefill_flops(w["B"] * world, w["H"], w["L"], w["L"], w["D"], causal)
+        q, k, v = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), device)
+        o = torch.empty_like(q)
+        d = attn_desc_for(q, k, v, o, w["dtype"], scale, causal)
+        qp, kp, vp, op = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+
+        def step():
+            rc = lib.tf_attn_fwd(qp, kp, vp, op, None, C.byref(d), stream)
+            if rc != 0:
+                _cabi.check(rc)
+        local_heads = b_local * h_local
+    else:
+        # strong scaling: the flattened (batch x heads) axis is split by tf_prefill_sharded; a
+        # rank holds only its slice, laid out where the full [B, H, L, D] tensor would have it
+        from tilefusion_b200.shard import head_slice
+
+        h0, h1 = head_slice(w["B"] * w["H"], rank, world)
+        local_heads = h1 - h0
+        total_units = prefill_flops(w["B"], w["H"], w["L"], w["L"], w["D"], causal)
+        q, k, v = make_inputs(dict(w, H=1, seed=w["seed"] + 1000 * rank), device, b=local_heads)
+        o = torch.empty_like(q)
+        full = torch.empty(0, dtype=q.dtype, device="meta").new_empty((w["B"], w["H"], w["L"], w["D"]))
+        d = attn_desc_for(full, full, full, full, w["dtype"], scale, causal)
+        head_bytes = w["L"] * w["D"] * q.element_size()
+        bases = [t.data_ptr() - h0 * head_bytes for t in (q, k, v, o)]
+
+        def step():
+            rc = lib.tf_prefill_sharded(rank, world, bases[0], bases[1], bases[2], bases[3], None, C.byref(d),
+                                        stream, None, None)
+            if rc != 0:
+                _cabi.check(rc)
+
+    secs, info = time_steps(step, steps, warmup, device, world)
+    value = total_units * steps / secs / 1e12
+    per_launch_s = secs / steps
+    local_flops = prefill_flops(1, local_heads, w["L"], w["L"], w["D"], causal)
+    roof = prefill_roofline(w, local_flops, per_launch_s, local_heads, secs * info["repeats"],
+                            info["clocks"]["reasons"])
+    res = dict(value=value, unit="TFLOP/s", secs=secs, info=info, roofline=roof, launches=steps)
+    if args.profile:
+        return res
+
+    # parity of the timed output: one (batch, head) against the fp32 expression evaluated on the
+    # device, and (where a head is small enough for the host) against the oracle on the CPU
     from oracle import attention_oracle as orc
 
-    ref, _ = orc.attention_fp32(q[0, 0].cpu(), k[0, 0].cpu(), v[0, 0].cpu(), scale, causal)
-    parity = {"max_abs": orc.max_abs(o[0, 0].cpu(), ref), "rel_l2": orc.rel_l2(o[0, 0].cpu(), ref),
-              "checked": "one (batch, head) of the timed output vs the fp32 oracle"}
+    ref, _ = gpu_attention_fp32(q[0, 0], k[0, 0], v[0, 0], scale, causal)
+    dt = torch_dtype(w["dtype"])
+    parity = {"max_abs": (o[0, 0].float() - ref).abs().max().item(), "rel_l2": orc.rel_l2(o[0, 0].cpu(), ref.cpu()),
+              "rel_l2_bound": orc.rel_l2_bound(ref.cpu(), dt), "rel_l2_rounding_floor": orc.rounding_floor(ref.cpu(), dt),
+              "checked": "one (batch, head) of the timed output vs softmax(QK^T s)V in fp32 (torch, on the device)"}
+    if w["L"] <= 4096:
+        ref_cpu, _ = orc.attention_fp32(q[0, 0].cpu(), k[0, 0].cpu(), v[0, 0].cpu(), scale, causal)
+        parity["oracle_max_abs"] = orc.max_abs(o[0, 0].cpu(), ref_cpu)
+        parity["oracle_rel_l2"] = orc.rel_l2(o[0, 0].cpu(), ref_cpu)
+        parity["checked"] += " and vs the CPU oracle"
+    res["parity"] = parity
+    if not with_e2e:
+        return res
 
     # end to end through the public operator, host buffers in and out
-    e2e_steps = max(1, min(args.steps, 20))
+    e2e_steps = max(1, min(steps, 20))
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     ho = torch.empty(o.shape, dtype=o.dtype).pin_memory()
-
     pipe = tilefusion.HostPipeline(
         lambda dq, dk, dv: tilefusion.ops.flash_attention(dq, dk.transpose(-1, -2), dv, 0, 0, 0, 0, scale, causal),
         device)
 
-    def e2e_step():
+    def e2e_steps_timed(n):
         # pinned host Q, K, V in, O back into pinned host memory; copies of neighbouring
         # steps overlap with the kernel (tilefusion_b200.HostPipeline)
-        pipe.submit((hq, hk, hv), ho)
-
-    def e2e_steps_timed(n):
         torch.cuda.synchronize(device)
         t0 = time.perf_counter()
         for _ in range(n):
-            e2e_step()
+            pipe.submit((hq, hk, hv), ho)
         pipe.flush()
         return time.perf_counter() - t0
 
@@ -425,12 +538,100 @@ def run_prefill(args, w, name, device, rank, world):
         t = torch.tensor([e2e_secs], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_secs = t.item()
-    e2e = {"value": total_units * e2e_steps / e2e_secs / 1e12, "unit": "TFLOP/s",
-           "h2d_bytes_per_step": 3 * q.numel() * q.element_size(),
-           "d2h_bytes_per_step": o.numel() * o.element_size(), "steps": e2e_steps,
-           "timing": "host wall clock around submit..flush (three streams), max over ranks"}
-    return dict(value=value, unit="TFLOP/s", secs=secs, clocks=clocks[0], parity=parity, e2e=e2e,
-                roofline=roof, launches=args.steps)
+    res["e2e"] = {"value": total_units * e2e_steps / e2e_secs / 1e12, "unit": "TFLOP/s",
+                  "h2d_bytes_per_step": 3 * q.numel() * q.element_size(),
+                  "d2h_bytes_per_step": o.numel() * o.element_size(), "steps": e2e_steps,
+                  "timing": "host wall clock around submit..flush (three streams), max over ranks"}
+    return res
+
+
+def sharded_parity(q, k_local, v_local, o, lse, scale, device, world):
+    """Parity of a KV-sharded decode step without ever holding the whole sequence in
+    one place: every rank evaluates the fp32 expression on its own shard for two
+    (batch, head) rows with torch on the device, giving one (O, m, l) partial row
+    each; the rows of all ranks are gathered (NCCL) and merged by the oracle's
+    combine on the host; the kernel's O / LSE of those rows are compared with it."""
+    import torch.distributed as dist
+
+    from oracle import attention_oracle as orc
+
+    b_n, h_n = q.size(0), q.size(1)
+    picks = [(0, 0), (b_n - 1, h_n - 1)]
+    dim = q.size(3)
+    rows = torch.zeros(len(picks), dim + 2, dtype=torch.float32, device=device)
+    for i, (b, h) in enumerate(picks):
+        hk = h * k_local.size(1) // h_n
+        if k_local.size(2) == 0:
+            rows[i, dim] = float("-inf")
+            continue
+        sc = (k_local[b, hk].float() @ q[b, h, 0].float()) * (scale * orc.LOG2E)
+        m = sc.max()
+        p = torch.exp2(sc - m)
+        rows[i, :dim] = p @ v_local[b, hk].float()
+        rows[i, dim], rows[i, dim + 1] = m, p.sum()
+    if world > 1:
+        gathered = torch.empty(world, len(picks), dim + 2, dtype=torch.float32, device=device)
+        dist.all_gather_into_tensor(gathered, rows)
+    else:
+        gathered = rows[None]
+    g = gathered.cpu().permute(1, 0, 2)                       # [rows, ranks, D + 2]
+    ref_o, ref_lse, _ = orc.decode_combine(g[..., :dim], g[..., dim:])
+    got_o = torch.stack([o[b, h, 0] for b, h in picks]).float().cpu()
+    got_lse = torch.stack([lse[b, h, 0] for b, h in picks]).cpu()
+    return {"max_abs": (got_o - ref_o).abs().max().item(), "rel_l2": orc.rel_l2(got_o, ref_o),
+            "lse_abs": (got_lse - ref_lse).abs().max().item(),
+            "checked": "two (batch, head) rows: per-rank fp32 partials on each rank's own KV shard (torch, on the "
+                       "device), gathered and merged by the oracle's combine, vs the kernel's O / LSE on rank 0"}
+
+
+def decode_roofline(w, local_units, secs, steps, units_in_launch, sharded):
+    pk = peaks()
+    ach = local_units * steps / secs / 1e9
+    traffic, note = (None, "not captured for the sharded step") if sharded else ncu_traffic(w, units_in_launch)
+    return {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
+            "traffic": traffic, "traffic_source": note, "algorithmic_bytes": local_units,
+            "kernel": ("attn_fwd_pair_kernel in split-KV mode (+ combine)" if "Hkv" in w
+                       else "decode_split_kernel" + (" (split, merge, exchange and combine in one launch)" if sharded
+                                                     else " (+ combine)")),
+            "peak_source": pk["source"] + " (torch copy, read+write)", "frac_of_nominal_8000": ach / 8000.0}
+
+
+def run_decode_sharded(args, w, name, device, rank, world, steps, warmup):
+    """decode_c4: the KV length split over the ranks (world 1: one GPU holds it all),
+    through tf_decode_sharded, once per transport."""
+    from tilefusion_b200.shard import ShardedDecoder, kv_slice
+
+    scale = 1.0 / math.sqrt(w["D"])
+    k0, k1 = kv_slice(w["L"], rank, world)
+    q = make_inputs(dict(w, L=128), device)[0]                 # replicated Q (same seed on every rank)
+    _, k, v = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), device, l=k1 - k0)
+    out = torch.empty(w["B"], w["H"], 1, w["D"], dtype=q.dtype, device=device)
+    lse = torch.empty(w["B"], w["H"], 1, dtype=torch.float32, device=device)
+    total_units = decode_bytes(w["B"], w["H"], w["L"], w["D"])
+    local_units = decode_bytes(w["B"], w["H"], k1 - k0, w["D"])
+    wanted = [args.transport] if getattr(args, "transport", None) else ["p2p", "nccl"]
+    results = {}
+    for transport in wanted:
+        dec = ShardedDecoder(w["B"], w["H"], w["D"], q.dtype, device, transport=transport)
+
+        def step():
+            dec(q, k, v, scale, out=out, lse=lse)
+
+        secs, info = time_steps(step, steps, warmup, device, world)
+        r = dict(value=total_units * steps / secs / 1e9, unit="GB/s", secs=secs, info=info,
+                 roofline=decode_roofline(w, local_units, secs, steps, w["B"] * w["H"], True),
+                 transport=dec.transport, transport_note=dec.transport_note,
+                 launches=(1 if dec.transport == "p2p" else 3) * steps)
+        if not args.profile:
+            r["parity"] = sharded_parity(q, k, v, out, lse, scale, device, world)
+        torch.cuda.synchronize(device)
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()          # no rank frees its gather buffer while a peer may still store into it
+        dec.close()
+        results[transport] = r
+    return results
 
 
 def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
@@ -440,97 +641,83 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
 
     steps = args.steps if steps is None else steps
     warmup = args.warmup if warmup is None else warmup
+    if w["scaling"] == "strong":
+        results = run_decode_sharded(args, w, name, device, rank, world, steps, warmup)
+        first = next(iter(results.values()))
+        res = dict(first)
+        res["by_transport"] = results
+        return res
     lib = _cabi.lib()
     scale = 1.0 / math.sqrt(w["D"])
     stream = torch.cuda.current_stream(device).cuda_stream
-    sharded = w["scaling"] == "strong" and world > 1
-    if sharded:
-        from tilefusion_b200.shard import ShardedDecoder, kv_slice
+    q, k, v = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), device)
+    o = torch.empty_like(q)
+    lse = torch.empty(w["B"], w["H"], 1, dtype=torch.float32, device=device)
+    d = _cabi.TfDecodeDesc()
+    d.dtype = _cabi.TF_F16 if w["dtype"] == "fp16" else _cabi.TF_BF16
+    d.batch, d.heads, d.len_kv, d.head_dim = w["B"], w["H"], w["L"], w["D"]
+    d.kv_chunk, d.num_splits, d.softmax_scale = 512, 0, scale
+    d.q_stride_b, d.q_stride_h = q.stride(0), q.stride(1)
+    d.k_stride_b, d.k_stride_h = k.stride(0), k.stride(1)
+    d.v_stride_b, d.v_stride_h = v.stride(0), v.stride(1)
+    d.o_stride_b, d.o_stride_h = o.stride(0), o.stride(1)
+    hkv = w.get("Hkv", w["H"])
+    d.heads_kv = hkv
+    plan = _cabi.TfDecodePlan()
+    _cabi.check(lib.tf_decode_plan(C.byref(d), C.byref(plan)))
+    ws = torch.empty(plan.workspace_bytes // 4, dtype=torch.float32, device=device)
+    ptrs = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ws.data_ptr())
 
-        k0, k1 = kv_slice(w["L"], rank, world)
-        wq = dict(w)
-        q = make_inputs(dict(wq, L=128), device)[0]                # replicated Q (same seed on every rank)
-        _, k, v = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), device, l=k1 - k0)
-        dec = ShardedDecoder(w["B"], w["H"], w["D"], q.dtype, device, transport=getattr(args, "transport", None))
+    def step():
+        rc = lib.tf_decode(ptrs[0], ptrs[1], ptrs[2], ptrs[3], ptrs[4], ptrs[5], ws.numel() * 4,
+                           C.byref(d), stream)
+        if rc != 0:
+            _cabi.check(rc)
 
-        def step():
-            dec(q, k, v, scale)
+    total_units = decode_bytes(w["B"] * world, hkv, w["L"], w["D"])
+    local_units = decode_bytes(w["B"], hkv, w["L"], w["D"])
+    secs, info = time_steps(step, steps, warmup, device, world)
+    res = dict(value=total_units * steps / secs / 1e9, unit="GB/s", secs=secs, info=info,
+               roofline=decode_roofline(w, local_units, secs, steps, w["B"] * hkv, False), launches=2 * steps)
+    if args.profile:
+        return res
+    from oracle import attention_oracle as orc
 
-        total_units = decode_bytes(w["B"], w["H"], w["L"], w["D"])
-        local_units = decode_bytes(w["B"], w["H"], k1 - k0, w["D"])
-        launches_per_step = 3      # split, merge (+ peer scatter), combine; the nccl transport adds one collective
-    else:
-        q, k, v = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), device)
-        o = torch.empty_like(q)
-        lse = torch.empty(w["B"], w["H"], 1, dtype=torch.float32, device=device)
-        d = _cabi.TfDecodeDesc()
-        d.dtype = _cabi.TF_F16 if w["dtype"] == "fp16" else _cabi.TF_BF16
-        d.batch, d.heads, d.len_kv, d.head_dim = w["B"], w["H"], w["L"], w["D"]
-        d.kv_chunk, d.num_splits, d.softmax_scale = 512, 0, scale
-        d.q_stride_b, d.q_stride_h = q.stride(0), q.stride(1)
-        d.k_stride_b, d.k_stride_h = k.stride(0), k.stride(1)
-        d.v_stride_b, d.v_stride_h = v.stride(0), v.stride(1)
-        d.o_stride_b, d.o_stride_h = o.stride(0), o.stride(1)
-        d.heads_kv = w.get("Hkv", w["H"])
-        plan = _cabi.TfDecodePlan()
-        _cabi.check(lib.tf_decode_plan(C.byref(d), C.byref(plan)))
-        ws = torch.empty(plan.workspace_bytes // 4, dtype=torch.float32, device=device)
-        ptrs = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ws.data_ptr())
+    grp = w["H"] // hkv
+    ref, lse_ref = orc.decode_fp32(q[:1, :2].cpu(), k[:1, :1].cpu().expand(-1, 2, -1, -1) if grp > 1 else k[:1, :2].cpu(),
+                                   v[:1, :1].cpu().expand(-1, 2, -1, -1) if grp > 1 else v[:1, :2].cpu(), scale)
+    res["parity"] = {"max_abs": orc.max_abs(o[:1, :2].cpu(), ref), "rel_l2": orc.rel_l2(o[:1, :2].cpu(), ref),
+                     "lse_abs": orc.max_abs(lse[:1, :2].cpu(), lse_ref),
+                     "checked": "two (batch, head) rows of the timed output vs the fp32 oracle"}
+    # end to end: pinned host K/V/Q in, O and LSE out, through the public operator
+    import tilefusion_b200 as tilefusion
 
-        def step():
-            rc = lib.tf_decode(ptrs[0], ptrs[1], ptrs[2], ptrs[3], ptrs[4], ptrs[5], ws.numel() * 4,
-                               C.byref(d), stream)
-            if rc != 0:
-                _cabi.check(rc)
+    e2e_steps = max(1, min(steps, 5))
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty(o.shape, dtype=o.dtype).pin_memory()
 
-        mult = world if w["scaling"] == "weak" else 1
-        hkv = w.get("Hkv", w["H"])
-        total_units = decode_bytes(w["B"] * mult, hkv, w["L"], w["D"])
-        local_units = decode_bytes(w["B"], hkv, w["L"], w["D"])
-        d.heads_kv = hkv
-        launches_per_step = 2
+    def e2e_step():
+        out, _ = tilefusion.ops.flash_decoding(hq.to(device, non_blocking=True), hk.to(device, non_blocking=True),
+                                               hv.to(device, non_blocking=True), 512, 0, scale)
+        ho.copy_(out, non_blocking=True)
 
-    clocks = []
-    secs = time_steps(step, steps, warmup, device, world, clocks)
-    value = total_units * steps / secs / 1e9
-    pk = peaks()
-    ach = local_units * steps / secs / 1e9
-    roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-            "frac": ach / pk["hbm_gbs"], "traffic": ncu_traffic(w, w["B"] * w["H"]) if not sharded else None,
-            "algorithmic_bytes": local_units, "kernel": ("attn_fwd_pair_kernel in split-KV mode (+ combine)" if "Hkv" in w
-                                                   else "decode_split_kernel (+ combine)"),
-            "peak_source": pk["source"] + " (torch copy, read+write)", "frac_of_nominal_8000": ach / 8000.0}
-    res = dict(value=value, unit="GB/s", secs=secs, clocks=clocks[0], roofline=roof,
-               launches=launches_per_step * steps)
-    if sharded:
-        res["transport"] = dec.transport
-
-    if not sharded and not args.profile:
-        from oracle import attention_oracle as orc
-
-        grp = w["H"] // w.get("Hkv", w["H"])
-        ref, lse_ref = orc.decode_fp32(q[:1, :2].cpu(), k[:1, :1].cpu().expand(-1, 2, -1, -1) if grp > 1 else k[:1, :2].cpu(),
-                                       v[:1, :1].cpu().expand(-1, 2, -1, -1) if grp > 1 else v[:1, :2].cpu(), scale)
-        res["parity"] = {"max_abs": orc.max_abs(o[:1, :2].cpu(), ref),
-                         "lse_abs": orc.max_abs(lse[:1, :2].cpu(), lse_ref),
-                         "checked": "two (batch, head) rows of the timed output vs the fp32 oracle"}
-        # end to end: pinned host K/V/Q in, O and LSE out, through the public operator
-        import tilefusion_b200 as tilefusion
-
-        e2e_steps = max(1, min(steps, 5))
-        hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
-        ho = torch.empty(o.shape, dtype=o.dtype).pin_memory()
-
-        def e2e_step():
-            out, _ = tilefusion.ops.flash_decoding(hq.to(device, non_blocking=True), hk.to(device, non_blocking=True),
-                                                   hv.to(device, non_blocking=True), 512, 0, scale)
-            ho.copy_(out, non_blocking=True)
-
-        e2e_secs = time_steps(e2e_step, e2e_steps, 3, device, world)
-        res["e2e"] = {"value": total_units * e2e_steps / e2e_secs / 1e9, "unit": "GB/s",
-                      "h2d_bytes_per_step": (q.numel() + 2 * k.numel()) * 2,
-                      "d2h_bytes_per_step": o.numel() * 2, "steps": e2e_steps}
+    e2e_secs, _ = time_steps(e2e_step, e2e_steps, 2, device, world, max_repeats=1)
+    res["e2e"] = {"value": total_units * e2e_steps / e2e_secs / 1e9, "unit": "GB/s",
+                  "h2d_bytes_per_step": (q.numel() + 2 * k.numel()) * 2,
+                  "d2h_bytes_per_step": o.numel() * 2, "steps": e2e_steps}
     return res
+
+
+def secondary_object(wname, res, steps, world):
+    """Compact form of a secondary workload's result for the default line."""
+    obj = {"workload": wname, "value": res["value"], "unit": res["unit"], "value_per_gpu": res["value"] / world,
+           "steps": steps, "ms_per_step": res["secs"] / steps * 1e3, "repeats": res["info"]["repeats"],
+           "roofline": res["roofline"], "clocks": {k: v for k, v in res["info"]["clocks"].items() if k != "sm_mhz_all"},
+           "gpu_launches": res["launches"]}
+    for key in ("e2e", "parity", "transport", "transport_note"):
+        if key in res and res[key] not in (None, ""):
+            obj[key] = res[key]
+    return obj
 
 
 def main():
@@ -543,10 +730,11 @@ def main():
     ap.add_argument("--causal", action="store_true",
                     help="prefill workloads: mask key index > query index (FLOPs counted over unmasked pairs)")
     ap.add_argument("--transport", default=None, choices=["p2p", "nccl"],
-                    help="KV-sharded decode: fused peer-memory gather (default) or NCCL all-gather")
-    ap.add_argument("--no-secondary", action="store_true", help="skip the decode line and CPU baseline")
+                    help="KV-sharded decode: only this transport (default: both, peer-memory exchange first)")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the decode / decode_c4 / prefill_c5 / causal objects and the CPU baseline")
     ap.add_argument("--profile", action="store_true",
-                    help="device-timed steps only (no end-to-end pass, parity check, decode line or CPU "
+                    help="device-timed steps only (no end-to-end pass, parity check, secondary objects or CPU "
                          "baseline): the command to put under ncu")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -571,8 +759,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
-    runner = run_prefill if w["kind"] == "prefill" else run_decode
-    res = runner(args, w, args.workload, device, rank, world)
+    if w["kind"] == "prefill":
+        res = run_prefill(args, w, args.workload, device, rank, world, causal=args.causal)
+    else:
+        res = run_decode(args, w, args.workload, device, rank, world)
 
     line = {
         "metric": metric_name(w), "value": res["value"], "unit": res["unit"], "n_gpus": world,
@@ -581,29 +771,38 @@ def main():
         "dtype": "f16" if w["dtype"] == "fp16" else "bf16", "data": "synthetic",
         "config": workload_config(w, args.workload, world, args.causal and w["kind"] == "prefill"),
         "value_per_gpu": res["value"] / world,
-        "clocks": res["clocks"], "gpu_launches": res["launches"],
+        "clocks": res["info"]["clocks"], "repeats": res["info"]["repeats"],
+        "region_ms_per_step": res["info"]["region_ms_per_step"], "gpu_launches": res["launches"],
         "roofline": res["roofline"],
     }
-    if "e2e" in res:
-        line["e2e"] = res["e2e"]
-    if "parity" in res:
-        line["parity"] = res["parity"]
+    for key in ("e2e", "parity"):
+        if key in res:
+            line[key] = res[key]
     if "transport" in res:
         line["config"]["transport"] = res["transport"]
+    if "by_transport" in res:
+        line["by_transport"] = {t: secondary_object(args.workload, r, args.steps, world)
+                                for t, r in res["by_transport"].items()}
 
-    if not args.no_secondary and w["kind"] == "prefill":
-        # the other half of the metric: decode GB/s (config 3 on one GPU per rank;
-        # config 4 sharded over the ranks when there is more than one)
-        dname = "decode_c3" if world == 1 else "decode_c4"
-        dres = run_decode(args, WORKLOADS[dname], dname, device, rank, world,
-                          steps=max(10, min(args.steps, 50)), warmup=3)
-        line["decode"] = {"workload": dname, "value": dres["value"], "unit": "GB/s",
-                          "value_per_gpu": dres["value"] / world,
-                          "ms_per_step": dres["secs"] / max(10, min(args.steps, 50)) * 1e3,
-                          "roofline": dres["roofline"], "clocks": dres["clocks"]}
-        for key in ("e2e", "parity", "transport"):
-            if key in dres:
-                line["decode"][key] = dres[key]
+    if not args.no_secondary and args.workload == "prefill_c2" and not args.causal:
+        # the rest of the metric, every object at every N
+        sec_steps = max(10, min(args.steps, 50))
+        dres = run_decode(args, WORKLOADS["decode_c3"], "decode_c3", device, rank, world, steps=sec_steps, warmup=3)
+        line["decode"] = secondary_object("decode_c3", dres, sec_steps, world)
+        torch.cuda.empty_cache()
+        c4 = run_decode(args, WORKLOADS["decode_c4"], "decode_c4", device, rank, world, steps=sec_steps, warmup=3)
+        line["decode_c4"] = secondary_object("decode_c4", c4, sec_steps, world)
+        line["decode_c4"]["by_transport"] = {t: secondary_object("decode_c4", r, sec_steps, world)
+                                             for t, r in c4["by_transport"].items()}
+        torch.cuda.empty_cache()
+        c5_steps = max(3, min(args.steps, 6 * world))
+        c5 = run_prefill(args, WORKLOADS["prefill_c5"], "prefill_c5", device, rank, world, steps=c5_steps, warmup=3,
+                         with_e2e=False)
+        line["prefill_c5"] = secondary_object("prefill_c5", c5, c5_steps, world)
+        torch.cuda.empty_cache()
+        cz = run_prefill(args, w, "prefill_c2", device, rank, world, causal=True, with_e2e=False)
+        line["causal"] = secondary_object("prefill_c2+causal", cz, args.steps, world)
+        line["causal"]["flops_counted"] = "unmasked (query, key) pairs only"
 
     if rank == 0 and world == 1 and not args.no_secondary:
         line["cpu_baseline"] = cpu_baseline(w)
