@@ -57,8 +57,11 @@ typedef struct TfAttnDesc {
   int32_t heads;        /* H                                                  */
   int32_t len_q;        /* Lq >= 1                                            */
   int32_t len_kv;       /* Lk >= 1                                            */
-  int32_t head_dim;     /* D  in {64, 128}                                    */
-  int32_t head_dim_v;   /* Dv, must equal D                                   */
+  int32_t head_dim;     /* D:  a multiple of 8 in [8, 256]                    */
+  int32_t head_dim_v;   /* Dv: a multiple of 8 in [8, 256]; may differ from D.
+                           Kernels are compiled for 64, 128 and 256; other
+                           widths run zero-padded on the next one (TMA fills
+                           the padding), which is exact.                      */
   int32_t causal;       /* 1: mask key index > query index (top-left aligned,
                            include/cell/mask.hpp:19-113)                      */
   float softmax_scale;  /* multiplies Q K^T before the softmax                */
@@ -131,6 +134,7 @@ typedef struct TfAttnPlan {
   int32_t grid;
   int32_t k_mn_major;   /* 1 when K is read as [D, Lk]                        */
   int32_t v_mn_major;   /* 1 when V is read as [Lk, Dv]                       */
+  int32_t head_dim_kernel; /* compiled head dim the problem runs on (64/128/256) */
   uint64_t smem_bytes;
 } TfAttnPlan;
 
@@ -160,7 +164,8 @@ TF_EXPORT int tf_attn_fwd(const void* q, const void* k, const void* v, void* o,
  * arguments the reference bakes in as template constants
  * (src/kernels/flash_attn.cu:16-55, :87-99) and for its per-shape JIT cache
  * (src/jit/compiler.cc:123-145): variants here are compiled ahead of time and
- * looked up by (dtype, head_dim).
+ * looked up by (dtype, head_dim bucket); sequence lengths, scale and mask are
+ * run-time arguments, and head dims between the compiled ones are zero-padded.
  */
 TF_EXPORT int tf_attn_plan(const TfAttnDesc* desc, TfAttnPlan* plan);
 
@@ -172,8 +177,8 @@ TF_EXPORT int tf_attn_plan(const TfAttnDesc* desc, TfAttnPlan* plan);
  * src/kernels/fused_two_gemms.cu:66-144; kernel
  * include/kernels/fused_two_gemms_device.cuh:114-214) with the operand layouts
  * of that operator: A and D row-major, B given as [n, k] and C as [p, n]
- * ("column-major" B and C).  ld* are row strides in elements.  This variant
- * requires k == p in {64, 128}; m and n are arbitrary.
+ * ("column-major" B and C).  ld* are row strides in elements.  k and p are
+ * multiples of 8 up to 256 (they may differ), n a multiple of 8, m arbitrary.
  */
 TF_EXPORT int tf_fused_two_gemms(const void* a, const void* b, const void* c, void* d,
                                  int32_t m, int32_t n, int32_t k, int32_t p, int32_t dtype,

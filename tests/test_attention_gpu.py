@@ -128,6 +128,65 @@ def test_shapes(shape, dtype, tile_q):
     assert device_status() == 0
 
 
+WIDTHS = [
+    # B, H, Lq, Lk, D, Dv, causal, tile_q
+    (1, 2, 200, 304, 256, 256, False, 0),    # the widest compiled kernel (one CTA per SM, 512 TMEM columns)
+    (2, 2, 384, 640, 256, 256, True, 0),
+    (1, 3, 130, 264, 192, 192, False, 0),    # between compiled widths: zero-padded by TMA
+    (1, 2, 256, 256, 96, 96, False, 128),
+    (2, 37, 512, 512, 96, 96, True, 256),    # ... also on the two-tile kernel (148 items)
+    (1, 2, 100, 200, 40, 40, False, 0),
+    (1, 2, 257, 384, 64, 128, False, 0),     # Dv != D
+    (1, 2, 257, 384, 128, 64, True, 0),
+    (1, 2, 128, 512, 72, 200, False, 0),
+    (2, 37, 512, 256, 128, 64, False, 256),
+    (1, 1, 64, 128, 8, 8, False, 0),
+]
+
+
+@pytest.mark.parametrize("case", WIDTHS, ids=lambda c: "x".join(map(str, c)))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("k_order,v_order", [("LD", "LD"), ("DL", "DL")])
+def test_head_dims_beyond_the_compiled_ones(case, dtype, k_order, v_order):
+    """TileFusion's JIT bakes any head dims into a kernel (src/kernels/flash_attn.cu:73-99).
+    Here kernels exist for 64, 128 and 256; every other multiple of 8 up to 256, and
+    Dv != D, runs on the next one with the padding filled by TMA -- in both memory
+    layouts of K and V, with strided rows, and with nothing written beyond Dv."""
+    from cabi_helpers import attn_fwd, device_status
+
+    b, h, lq, lk, d, dv, causal, tile_q = case
+    q, k, v = orc.seeded_inputs(13, (b, h, lq, d), (b, h, lk, d), (b, h, lk, dv), 1.0, dtype)
+    scale = 1.0 / math.sqrt(d)
+    o, lse = attn_fwd(q.cuda(), _layout(k.cuda(), k_order), _layout(v.cuda(), v_order), scale, causal, tile_q=tile_q)
+    assert o.shape == (b, h, lq, dv)
+    ref, lse_ref = orc.attention_fp32(q, k, v, scale, causal)
+    _check(o, lse, ref, lse_ref, dtype)
+    assert device_status() == 0
+
+
+def test_narrow_output_leaves_its_neighbours_alone():
+    """O rows narrower than the kernel's width, inside a wider buffer: the columns
+    beyond Dv belong to the caller and must keep their contents (row-store and
+    TMA-store epilogues alike)."""
+    import ctypes as C
+
+    from cabi_helpers import attn_desc
+    from tilefusion_b200 import _cabi
+
+    b, h, lq, lk, d, dv = 1, 2, 300, 256, 64, 40
+    q, k, v = orc.seeded_inputs(14, (b, h, lq, d), (b, h, lk, d), (b, h, lk, dv), 1.0)
+    ref, _ = orc.attention_fp32(q, k, v, 0.125, False)
+    for tile_q in (128, 256):
+        wide = torch.full((b, h, lq, 64), 7.0, dtype=torch.float16, device="cuda")
+        o = wide[..., :dv]
+        qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+        desc = attn_desc(qc, kc, vc, o, 0.125, False, tile_q, 128)
+        _cabi.check(_cabi.lib().tf_attn_fwd(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), None,
+                                            C.byref(desc), torch.cuda.current_stream().cuda_stream))
+        assert orc.max_abs(o.cpu(), ref) <= MAX_ABS and orc.rel_l2(o.cpu(), ref) <= REL_L2_FP16
+        assert (wide[..., dv:] == 7.0).all()
+
+
 @pytest.mark.parametrize("tile_q", TILE_Q)
 def test_large_scores_exercise_rescale(tile_q):
     """Row maxima that grow tile after tile force the O rescale path."""

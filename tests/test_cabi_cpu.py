@@ -30,7 +30,7 @@ def test_struct_layouts_match_header():
     assert C.sizeof(_cabi.TfAttnDesc) == 12 * 4 + 14 * 8
     assert C.sizeof(_cabi.TfDecodeDesc) == 8 * 4 + 8 * 8 + 2 * 4 + 8 + 2 * 4 + 2 * 8
     assert C.sizeof(_cabi.TfDecodePlan) == 6 * 4 + 8
-    assert C.sizeof(_cabi.TfAttnPlan) == 6 * 4 + 8
+    assert C.sizeof(_cabi.TfAttnPlan) == 7 * 4 + 4 + 8
     for struct, cname in [(_cabi.TfAttnDesc, "TfAttnDesc"), (_cabi.TfDecodeDesc, "TfDecodeDesc"),
                           (_cabi.TfDecodePlan, "TfDecodePlan"), (_cabi.TfAttnPlan, "TfAttnPlan")]:
         body = re.search(r"typedef struct " + cname + r" \{(.*?)\} " + cname, HEADER, re.S).group(1)
@@ -93,8 +93,23 @@ def test_attn_plan_and_layout_detection(native_lib):
     assert (plan.k_mn_major, plan.v_mn_major) == (1, 1)
 
 
+def test_head_dims_run_on_the_next_compiled_width(native_lib):
+    """Kernels are compiled for head dims 64, 128 and 256; anything else that is a
+    multiple of 8 runs zero-padded on the next one, and Dv may differ from D."""
+    plan = _cabi.TfAttnPlan()
+    for d, dv, kernel in [(64, 64, 64), (40, 40, 64), (96, 96, 128), (128, 128, 128), (64, 128, 128),
+                          (128, 64, 128), (192, 192, 256), (256, 256, 256), (72, 200, 256), (8, 8, 64)]:
+        desc = _attn_desc(head_dim=d, head_dim_v=dv)
+        assert native_lib.tf_attn_plan(C.byref(desc), C.byref(plan)) == 0, (d, dv)
+        assert plan.head_dim_kernel == kernel
+        if kernel == 256:          # S (128) + O (256) fill tensor memory: one Q tile per CTA, one CTA per SM
+            assert (plan.tile_q, plan.ctas_per_sm) == (128, 1)
+        assert 0 < plan.smem_bytes * plan.ctas_per_sm <= 227 * 1024
+
+
 @pytest.mark.parametrize("field,value,code,needle", [
-    ("head_dim", 96, _cabi.TF_ERR_UNSUPPORTED, "head_dim"),
+    ("head_dim", 100, _cabi.TF_ERR_UNSUPPORTED, "multiples of 8"),
+    ("head_dim", 264, _cabi.TF_ERR_UNSUPPORTED, "multiples of 8"),
     ("dtype", 7, _cabi.TF_ERR_UNSUPPORTED, "half-precision"),
     ("len_kv", 0, _cabi.TF_ERR_BAD_ARG, "positive"),
     ("softmax_scale", -1.0, _cabi.TF_ERR_UNSUPPORTED, "softmax_scale"),
@@ -196,8 +211,12 @@ def test_fused_two_gemms_validation(native_lib):
     buf = (C.c_char * 64)()
     p = C.addressof(buf)
     p += (-p) % 16
-    rc = native_lib.tf_fused_two_gemms(p, p, p, p, 64, 64, 96, 96, _cabi.TF_F16, 96, 96, 96, 96, None)
-    assert rc == _cabi.TF_ERR_UNSUPPORTED and "k == p" in native_lib.tf_last_error().decode()
+    rc = native_lib.tf_fused_two_gemms(p, p, p, p, 64, 64, 100, 96, _cabi.TF_F16, 104, 104, 64, 96, None)
+    assert rc == _cabi.TF_ERR_UNSUPPORTED and "multiples of 8" in native_lib.tf_last_error().decode()
+    rc = native_lib.tf_fused_two_gemms(p, p, p, p, 64, 64, 64, 264, _cabi.TF_F16, 64, 64, 64, 264, None)
+    assert rc == _cabi.TF_ERR_UNSUPPORTED and "multiples of 8" in native_lib.tf_last_error().decode()
+    rc = native_lib.tf_fused_two_gemms(p, p, p, p, 64, 60, 64, 64, _cabi.TF_F16, 64, 64, 64, 64, None)
+    assert rc == _cabi.TF_ERR_UNSUPPORTED and "n to be a multiple of 8" in native_lib.tf_last_error().decode()
     rc = native_lib.tf_fused_two_gemms(p, p, p, p, 64, 64, 64, 64, _cabi.TF_F16, 32, 64, 64, 64, None)
     assert rc == _cabi.TF_ERR_BAD_ARG and "leading dimension" in native_lib.tf_last_error().decode()
 

@@ -34,8 +34,11 @@ def test_reference_case_through_python_api():
     assert torch.allclose(out, a @ b.t() @ c.t(), rtol=1e-3, atol=1e-3)
 
 
-@pytest.mark.parametrize("m,n,k,p", [(128, 128, 128, 128), (300, 200, 64, 64), (1, 1, 128, 128),
-                                     (1000, 1024, 128, 128), (64, 77, 64, 64)])
+@pytest.mark.parametrize("m,n,k,p", [(128, 128, 128, 128), (300, 200, 64, 64), (1, 8, 128, 128),
+                                     (1000, 1024, 128, 128), (64, 77, 64, 64),
+                                     # k != p and widths between / above the compiled 64, 128, 256
+                                     (256, 128, 64, 128), (200, 264, 128, 64), (130, 96, 96, 96), (256, 256, 256, 256),
+                                     (100, 512, 192, 72), (64, 64, 8, 256)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
 def test_shapes_through_cabi(m, n, k, p, dtype):
     from cabi_helpers import device_status
@@ -63,7 +66,7 @@ def test_shapes_through_cabi(m, n, k, p, dtype):
 def test_unsupported_widths_are_reported():
     from tilefusion_b200 import _cabi
 
-    x = torch.zeros(64, 96, dtype=torch.float16, device="cuda")
-    rc = _cabi.lib().tf_fused_two_gemms(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), 64, 64, 96, 96,
-                                        _cabi.TF_F16, 96, 96, 96, 96, None)
-    assert rc == _cabi.TF_ERR_UNSUPPORTED and "k == p" in _cabi.lib().tf_last_error().decode()
+    x = torch.zeros(64, 264, dtype=torch.float16, device="cuda")
+    rc = _cabi.lib().tf_fused_two_gemms(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), 64, 64, 264, 264,
+                                        _cabi.TF_F16, 264, 264, 264, 264, None)
+    assert rc == _cabi.TF_ERR_UNSUPPORTED and "multiples of 8" in _cabi.lib().tf_last_error().decode()

@@ -81,7 +81,7 @@ class TfAttnPlan(C.Structure):
     _fields_ = [
         ("tile_q", C.c_int32), ("tile_kv", C.c_int32), ("ctas_per_sm", C.c_int32),
         ("grid", C.c_int32), ("k_mn_major", C.c_int32), ("v_mn_major", C.c_int32),
-        ("smem_bytes", C.c_uint64),
+        ("head_dim_kernel", C.c_int32), ("smem_bytes", C.c_uint64),
     ]
 
 

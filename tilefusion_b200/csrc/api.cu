@@ -105,10 +105,11 @@ int check_attn_desc(const TfAttnDesc* d) {
   if (d->batch < 1 || d->heads < 1 || d->len_q < 1 || d->len_kv < 1)
     return fail(TF_ERR_BAD_ARG, "batch, heads, len_q and len_kv must be positive (got %d, %d, %d, %d)",
                 d->batch, d->heads, d->len_q, d->len_kv);
-  if (d->head_dim != 64 && d->head_dim != 128)
-    return fail(TF_ERR_UNSUPPORTED, "head_dim %d has no compiled variant (64 and 128 do)", d->head_dim);
-  if (d->head_dim_v != d->head_dim)
-    return fail(TF_ERR_UNSUPPORTED, "head_dim_v (%d) must equal head_dim (%d)", d->head_dim_v, d->head_dim);
+  if (d->head_dim < 8 || d->head_dim > 256 || d->head_dim % 8 != 0 || d->head_dim_v < 8 || d->head_dim_v > 256 ||
+      d->head_dim_v % 8 != 0)
+    return fail(TF_ERR_UNSUPPORTED,
+                "head_dim (%d) and head_dim_v (%d) must be multiples of 8 in [8, 256] (kernels are compiled for "
+                "64, 128 and 256; other widths run zero-padded on the next one)", d->head_dim, d->head_dim_v);
   if (!(d->softmax_scale > 0.f) || !std::isfinite(d->softmax_scale))
     return fail(TF_ERR_UNSUPPORTED, "softmax_scale must be positive and finite");
   if (d->heads > 65535 || d->batch > 65535) return fail(TF_ERR_UNSUPPORTED, "batch and heads must each be <= 65535");
@@ -138,7 +139,10 @@ struct AttnLaunch {
 
 int prepare_attn(const void* q, const void* k, const void* v, void* o, float* lse, const TfAttnDesc* d,
                  const TfAttnPlan& plan, AttnLaunch* out) {
-  const int D = d->head_dim;
+  // The tensor maps carry the true head dims; boxes are as wide as the kernel's
+  // bucket, and TMA zero-fills (loads) or clips (stores) what lies beyond.
+  const int D = d->head_dim, Dv = d->head_dim_v;
+  const int bucket = plan.head_dim_kernel;
   const uint64_t B = d->batch, H = d->heads;
   {
     const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->len_q, H, B};
@@ -152,22 +156,22 @@ int prepare_attn(const void* q, const void* k, const void* v, void* o, float* ls
   } else {
     const uint64_t dims[4] = {(uint64_t)d->len_kv, (uint64_t)D, H, B};
     const int64_t str[3] = {d->k_stride_d, d->k_stride_h, d->k_stride_b};
-    if (int rc = encode_map(&out->mk, d->dtype, k, dims, str, 64, D, "K (stored [D, Lk])")) return rc;
+    if (int rc = encode_map(&out->mk, d->dtype, k, dims, str, 64, bucket, "K (stored [D, Lk])")) return rc;
   }
   if (plan.v_mn_major) {
-    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->len_kv, H, B};
+    const uint64_t dims[4] = {(uint64_t)Dv, (uint64_t)d->len_kv, H, B};
     const int64_t str[3] = {d->v_stride_l, d->v_stride_h, d->v_stride_b};
     if (int rc = encode_map(&out->mv, d->dtype, v, dims, str, 64, tfb::kAttnTile, "V")) return rc;
   } else {
-    const uint64_t dims[4] = {(uint64_t)d->len_kv, (uint64_t)D, H, B};
+    const uint64_t dims[4] = {(uint64_t)d->len_kv, (uint64_t)Dv, H, B};
     const int64_t str[3] = {d->v_stride_d, d->v_stride_h, d->v_stride_b};
-    if (int rc = encode_map(&out->mv, d->dtype, v, dims, str, 64, D, "V (stored [Dv, Lk])")) return rc;
+    if (int rc = encode_map(&out->mv, d->dtype, v, dims, str, 64, bucket, "V (stored [Dv, Lk])")) return rc;
   }
   {
     // The output leaves through a TMA store when its layout can be described
     // by a tensor map (16-byte aligned base, positive strides); otherwise the
     // kernels fall back to per-row stores.
-    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)d->len_q, H, B};
+    const uint64_t dims[4] = {(uint64_t)Dv, (uint64_t)d->len_q, H, B};
     const int64_t str[3] = {d->o_stride_l, d->o_stride_h, d->o_stride_b};
     bool ok = reinterpret_cast<uintptr_t>(o) % 16 == 0;
     for (int i = 0; i < 3; ++i) ok = ok && (dims[i + 1] == 1 || (str[i] > 0 && str[i] % 8 == 0));
@@ -184,6 +188,7 @@ int prepare_attn(const void* q, const void* k, const void* v, void* o, float* ls
   args.lse = lse;
   args.len_q = d->len_q;
   args.len_kv = d->len_kv;
+  args.dim_v = Dv;
   args.causal = d->causal ? 1 : 0;
   args.k_mn_major = plan.k_mn_major;
   args.v_mn_major = plan.v_mn_major;
@@ -328,7 +333,10 @@ int run_attn(const void* q, const void* k, const void* v, void* o, float* lse, c
              const TfAttnPlan& plan, cudaStream_t stream) {
   AttnLaunch L;
   if (int rc = prepare_attn(q, k, v, o, lse, d, plan, &L)) return rc;
-  return plan.tile_q == 256 ? launch_attn_pair<T, D>(L, d, plan, stream) : launch_attn<T, D>(L, d, stream);
+  if constexpr (D <= 128) {
+    if (plan.tile_q == 256) return launch_attn_pair<T, D>(L, d, plan, stream);
+  }
+  return launch_attn<T, D>(L, d, stream);
 }
 
 int check_decode_desc(const TfDecodeDesc* d) {
@@ -674,10 +682,12 @@ int tf_attn_plan(const TfAttnDesc* desc, TfAttnPlan* plan) {
   if (plan == nullptr) return fail(TF_ERR_BAD_ARG, "plan is null");
   if (int rc = check_attn_desc(desc)) return rc;
   tfb::plan_attn(*desc, sm_count(), plan);
+  const int bucket = plan->head_dim_kernel;
   if (plan->tile_q == 256)
-    plan->smem_bytes = desc->head_dim == 128 ? tfb::AttnPairSmem<128>::kBytes : tfb::AttnPairSmem<64>::kBytes;
+    plan->smem_bytes = bucket == 128 ? tfb::AttnPairSmem<128>::kBytes : tfb::AttnPairSmem<64>::kBytes;
   else
-    plan->smem_bytes = desc->head_dim == 128 ? tfb::AttnSmem<128>::kBytes : tfb::AttnSmem<64>::kBytes;
+    plan->smem_bytes = bucket == 256 ? tfb::AttnSmem<256>::kBytes
+                                     : bucket == 128 ? tfb::AttnSmem<128>::kBytes : tfb::AttnSmem<64>::kBytes;
   return TF_OK;
 }
 
@@ -691,11 +701,17 @@ int tf_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   TfAttnPlan plan;
   tfb::plan_attn(*desc, sm_count(), &plan);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (desc->head_dim == 128)
-    return desc->dtype == TF_F16 ? run_attn<__half, 128>(q, k, v, o, lse, desc, plan, s)
-                                 : run_attn<__nv_bfloat16, 128>(q, k, v, o, lse, desc, plan, s);
-  return desc->dtype == TF_F16 ? run_attn<__half, 64>(q, k, v, o, lse, desc, plan, s)
-                               : run_attn<__nv_bfloat16, 64>(q, k, v, o, lse, desc, plan, s);
+  switch (plan.head_dim_kernel) {
+    case 256:
+      return desc->dtype == TF_F16 ? run_attn<__half, 256>(q, k, v, o, lse, desc, plan, s)
+                                   : run_attn<__nv_bfloat16, 256>(q, k, v, o, lse, desc, plan, s);
+    case 128:
+      return desc->dtype == TF_F16 ? run_attn<__half, 128>(q, k, v, o, lse, desc, plan, s)
+                                   : run_attn<__nv_bfloat16, 128>(q, k, v, o, lse, desc, plan, s);
+    default:
+      return desc->dtype == TF_F16 ? run_attn<__half, 64>(q, k, v, o, lse, desc, plan, s)
+                                   : run_attn<__nv_bfloat16, 64>(q, k, v, o, lse, desc, plan, s);
+  }
 }
 
 int tf_fused_two_gemms(const void* a, const void* b, const void* c, void* d, int32_t m, int32_t n, int32_t k,
@@ -706,8 +722,10 @@ int tf_fused_two_gemms(const void* a, const void* b, const void* c, void* d, int
   if (m < 1 || n < 1 || k < 1 || p < 1) return fail(TF_ERR_BAD_ARG, "m, n, k and p must be positive");
   if (dtype != TF_F16 && dtype != TF_BF16)
     return fail(TF_ERR_UNSUPPORTED, "the inputs and output must be half-precision (fp16 or bf16); got dtype code %d", dtype);
-  if (k != p || (k != 64 && k != 128))
-    return fail(TF_ERR_UNSUPPORTED, "fused_two_gemms needs k == p in {64, 128} (got k=%d, p=%d)", k, p);
+  if (k % 8 != 0 || p % 8 != 0 || k > 256 || p > 256)
+    return fail(TF_ERR_UNSUPPORTED, "fused_two_gemms needs k and p to be multiples of 8 up to 256 (got k=%d, p=%d)", k, p);
+  if (n % 8 != 0)
+    return fail(TF_ERR_UNSUPPORTED, "fused_two_gemms needs n to be a multiple of 8 (rows of C are read in 16-byte units; got n=%d)", n);
   if (lda < k || ldb < k || ldc < n || ldd < p) return fail(TF_ERR_BAD_ARG, "a leading dimension is smaller than its row");
   if (!aligned16(d) || ldd % 8 != 0) return fail(TF_ERR_UNSUPPORTED, "d must be 16-byte aligned with ldd a multiple of 8");
   if (int rc = tfb::ensure_device_ready()) return rc;
@@ -716,7 +734,8 @@ int tf_fused_two_gemms(const void* a, const void* b, const void* c, void* d, int
   desc.batch = desc.heads = 1;
   desc.len_q = m;
   desc.len_kv = n;
-  desc.head_dim = desc.head_dim_v = k;
+  desc.head_dim = k;
+  desc.head_dim_v = p;
   desc.softmax_scale = 1.f;
   desc.tile_q = 128;
   desc.tile_kv = 128;
@@ -731,9 +750,14 @@ int tf_fused_two_gemms(const void* a, const void* b, const void* c, void* d, int
   AttnLaunch L;
   if (int rc = prepare_attn(a, b, c, d, nullptr, &desc, plan, &L)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (k == 128)
-    return dtype == TF_F16 ? launch_two_gemms<__half, 128>(L, &desc, s) : launch_two_gemms<__nv_bfloat16, 128>(L, &desc, s);
-  return dtype == TF_F16 ? launch_two_gemms<__half, 64>(L, &desc, s) : launch_two_gemms<__nv_bfloat16, 64>(L, &desc, s);
+  switch (plan.head_dim_kernel) {
+    case 256:
+      return dtype == TF_F16 ? launch_two_gemms<__half, 256>(L, &desc, s) : launch_two_gemms<__nv_bfloat16, 256>(L, &desc, s);
+    case 128:
+      return dtype == TF_F16 ? launch_two_gemms<__half, 128>(L, &desc, s) : launch_two_gemms<__nv_bfloat16, 128>(L, &desc, s);
+    default:
+      return dtype == TF_F16 ? launch_two_gemms<__half, 64>(L, &desc, s) : launch_two_gemms<__nv_bfloat16, 64>(L, &desc, s);
+  }
 }
 
 int tf_decode_plan(const TfDecodeDesc* desc, TfDecodePlan* plan) {

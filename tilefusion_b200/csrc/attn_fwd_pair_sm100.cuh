@@ -640,7 +640,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         if (row == 0) {
 #pragma unroll
           for (int blk = 0; blk < kBlocks; ++blk)
-            tma_store_4d(&map_o, stage_out + blk * S::kBlockBytes, blk * 64, q0, h, b);
+            if (blk * 64 < args.dim_v)               // (a block of pure zero padding is not stored)
+              tma_store_4d(&map_o, stage_out + blk * S::kBlockBytes, blk * 64, q0, h, b);
           bulk_commit_group();
         }
       } else {
@@ -659,6 +660,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         if (row_valid) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
+            if (c * 32 + v * 8 >= args.dim_v) continue;      // zero padding of a smaller head dim
             uint4 out;
             out.x = pack2<T>(__uint_as_float(orow[v * 8 + 0]) * inv_l,
                              __uint_as_float(orow[v * 8 + 1]) * inv_l);

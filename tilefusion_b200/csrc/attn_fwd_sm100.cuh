@@ -36,6 +36,7 @@ struct AttnFwdArgs {
   float* lse;            // may be null
   int len_q;
   int len_kv;
+  int dim_v;             // columns of O actually stored (<= the kernel's D; the rest is zero padding)
   int causal;
   int k_mn_major;        // K stored [D, Lk]
   int v_mn_major;        // V stored [Lk, Dv]
@@ -67,14 +68,21 @@ enum AttnWaitCode {
 // the intermediate product rounded to 16 bits, i.e. the same two MMAs with the
 // softmax stage replaced by a conversion.  Q = A [M, K], K = B [N, K],
 // V = C stored [P, N], O = D [M, P]; K == P == the template's D.
+//
+// D is the head-dim bucket the kernel is compiled for (64, 128 or 256).  A
+// problem whose head dims are smaller runs on the next bucket: the tensor maps
+// carry the true extents, TMA fills the missing columns of Q, K and V with
+// zeros (which changes neither Q K^T nor P V), and only the first dim_v columns
+// of O are stored.  D = 256 takes all 512 TMEM columns (S 128 + O 256) and 192
+// KB of shared memory, so one CTA per SM.
 template <typename T, int D, bool kNoSoftmax = false>
-__global__ void __launch_bounds__(kAttnThreads, 2)
+__global__ void __launch_bounds__(kAttnThreads, D <= 128 ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
                 const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const AttnFwdArgs args) {
   using S = AttnSmem<D>;
   constexpr int kIsBf16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-  constexpr int kTmemCols = 256;         // S: 128, O: D (<= 128)
+  constexpr int kTmemCols = D <= 128 ? 256 : 512;   // S: 128, O: D; a power of two
   constexpr int kColS = 0, kColP = 0, kColO = 128;
   constexpr int kBlocks = D / 64;        // 64-element swizzle blocks per row
 
@@ -396,6 +404,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         if (row_valid) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
+            if (c * 32 + v * 8 >= args.dim_v) continue;      // zero padding of a smaller head dim
             uint4 out;
             out.x = pack2<T>(__uint_as_float(orow[v * 8 + 0]) * inv_l,
                              __uint_as_float(orow[v * 8 + 1]) * inv_l);

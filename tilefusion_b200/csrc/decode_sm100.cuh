@@ -26,13 +26,18 @@
 // all-gather).
 //
 // KV sharded across GPUs: with DecodeFuseArgs set, decode_split_kernel carries
-// the exchange itself.  The CTA that finishes the last split of a (b, h) merges
-// that row's partials and stores the merged (O, m, l) row straight into the
-// gather area of every rank through peer-mapped pointers; the CTA that
-// completes the rank's last row raises this rank's flag on every peer; and
-// CTAs then wait (bounded) for all ranks' flags and write the final O / LSE
-// for their rows -- split, all-gather and combine in one launch.  Only plain
-// peer stores and system-scope release/acquire touch peer memory.
+// the exchange itself.  A tenth warp (the "merger") of every CTA counts the
+// CTA's finished items into a per-(b, h) arrival counter; the merger that
+// counts a row's last split merges that row's partials and stores the merged
+// (O, m, l) row straight into the gather area of every rank through
+// peer-mapped pointers; the one that completes the rank's last row raises this
+// rank's flag on every peer; and the CTAs then wait (bounded) for all ranks'
+// flags and write the final O / LSE for their rows -- split, all-gather and
+// combine in one launch.  The consumers only signal "item written" on an
+// mbarrier and go on streaming: the device-scope fence and the atomic round
+// trip an arrival costs (tens of microseconds per item when paid by the
+// consumers of a saturated SM) are the merger's, and it batches them.  Only
+// plain peer stores and system-scope release/acquire touch peer memory.
 #pragma once
 
 #include <type_traits>
@@ -43,7 +48,8 @@ namespace tfb {
 
 constexpr int kDecKeysPerStage = 128;
 constexpr int kDecConsumerThreads = 256;
-constexpr int kDecThreads = kDecConsumerThreads + 32;
+constexpr int kDecThreads = kDecConsumerThreads + 64;   // + producer warp + merger warp
+constexpr int kDecDoneSlots = 8;                        // items the consumers may be ahead of the merger
 constexpr int kDecMaxChunk = 1024;        // keys; bounds the score buffers
 
 // Fused merge / exchange / final combine of a KV-sharded decode step (all
@@ -104,11 +110,12 @@ struct DecodeSmem {
   static constexpr int kGroups = kDecConsumerThreads / (D / 8);
   static constexpr int kOffWarp = kOffRed + kGroups * D * 4;            // 16 fp32 scratch
   static constexpr int kOffBar = kOffWarp + 64;                         // 2*kStages mbarriers
-  static constexpr int kOffAbort = kOffBar + 2 * kStages * 8;            // abort flag, then two flag words of the fused tail
+  static constexpr int kOffDone = kOffBar + 2 * kStages * 8;            // kDecDoneSlots "item written" + as many "slot free" mbarriers
+  static constexpr int kOffAbort = kOffDone + 2 * kDecDoneSlots * 8;    // abort flag, then the gave-up flag of the final phase
   static constexpr int kBytes = kOffAbort + 16 + 128;                   // + alignment slack
 };
 
-enum DecodeWaitCode { kWaitDecEmpty = 201, kWaitDecFullK = 202, kWaitDecFullV = 203 };
+enum DecodeWaitCode { kWaitDecEmpty = 201, kWaitDecFullK = 202, kWaitDecFullV = 203, kWaitDecDone = 204, kWaitDecFree = 205 };
 enum CombineWaitCode { kWaitGatherFlag = 401 };
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
@@ -160,10 +167,12 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
   float* red = reinterpret_cast<float*>(smem_gen + S::kOffRed);
   float* warp_scratch = reinterpret_cast<float*>(smem_gen + S::kOffWarp);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
-  volatile int* s_last = abort_flag + 1;       // this CTA finished the last split of the current row
-  volatile int* s_gave_up = abort_flag + 2;    // the wait for the peers' flags ran out
+  volatile int* s_gave_up = abort_flag + 1;    // the wait for the peers' flags ran out
   const uint32_t bar_full = smem_base + S::kOffBar;
   const uint32_t bar_empty = smem_base + S::kOffBar + kStages * 8;
+  const uint32_t bar_done = smem_base + S::kOffDone;                      // [kDecDoneSlots] item n is in global memory
+  const uint32_t bar_free = smem_base + S::kOffDone + kDecDoneSlots * 8;  // [kDecDoneSlots] the merger has taken item n
+  const bool fused = args.fuse.row_arrivals != nullptr;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -174,8 +183,11 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
       mbar_init(bar_full + s * 8, 1);
       mbar_init(bar_empty + s * 8, kDecConsumerThreads / 32);
     }
+    for (int s = 0; s < kDecDoneSlots; ++s) {
+      mbar_init(bar_done + s * 8, kDecConsumerThreads / 32);
+      mbar_init(bar_free + s * 8, 1);
+    }
     *abort_flag = 0;
-    *s_last = 0;
     *s_gave_up = 0;
     mbar_fence_init();
   }
@@ -184,7 +196,91 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
   const int chunk = args.kv_chunk;
   const int keys_per_split = chunk * args.chunks_per_split;
 
-  if (warp == kDecConsumerThreads / 32) {
+  if (warp == kDecConsumerThreads / 32 + 1) {
+    // -------------------------------------------------------------- merger --
+    // Counts this CTA's finished items into the per-row arrival counters, merges
+    // the rows it completes and sends them out.  Items are taken in batches: one
+    // device-scope fence covers every item the consumers have signalled so far.
+    if (fused) {
+      const DecodeFuseArgs& f = args.fuse;
+      constexpr int kVec = D / 32;                     // output dims per lane
+      bool ok = true;
+      uint32_t n = 0;                                  // items of this CTA taken so far
+      for (int item = blockIdx.x; ok && item < args.items;) {
+        // the next item, then every further one that is already written
+        ok = mbar_wait_warp(bar_done + (n % kDecDoneSlots) * 8, (n / kDecDoneSlots) & 1, abort_flag, kWaitDecDone);
+        if (!ok) break;
+        int batch = 1;
+        while (batch < kDecDoneSlots && item + batch * (int)gridDim.x < args.items &&
+               __all_sync(0xffffffffu, mbar_try_wait(bar_done + ((n + batch) % kDecDoneSlots) * 8,
+                                                     ((n + batch) / kDecDoneSlots) & 1)))
+          ++batch;
+        if (lane == 0)
+          for (int i = 0; i < batch; ++i) mbar_arrive(bar_free + ((n + i) % kDecDoneSlots) * 8);
+        __threadfence();                               // the consumers' partial rows, before they are counted
+        for (int i = 0; i < batch; ++i, item += gridDim.x) {
+          const int bh = item / args.num_splits;
+          unsigned last = 0;
+          if (lane == 0) last = (atomicAdd(f.row_arrivals + bh, 1u) == (unsigned)args.num_splits - 1u) ? 1u : 0u;
+          if (__shfl_sync(0xffffffffu, last, 0) == 0) continue;
+          // ---- this arrival completed row bh: merge its splits (written by other SMs: read past L1) ----
+          __threadfence();
+          const float* ml = args.part_ml + (long long)bh * args.num_splits * 2;
+          const float* po = args.part_o + (long long)bh * args.num_splits * D + lane * kVec;
+          float m = -INFINITY;
+          for (int p = lane; p < args.num_splits; p += 32) m = fmaxf(m, __ldcg(ml + 2 * p));
+#pragma unroll
+          for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+          float acc_o[kVec], l = 0.f;
+#pragma unroll
+          for (int e = 0; e < kVec; ++e) acc_o[e] = 0.f;
+#pragma unroll 4
+          for (int p = 0; p < args.num_splits; ++p) {
+            const float2 mlp = __ldcg(reinterpret_cast<const float2*>(ml + 2 * p));
+            const float w = (mlp.x == -INFINITY) ? 0.f : fast_exp2(mlp.x - m);
+            l = fmaf(mlp.y, w, l);
+            if constexpr (kVec == 4) {
+              const float4 x = __ldcg(reinterpret_cast<const float4*>(po + (long long)p * D));
+              acc_o[0] = fmaf(x.x, w, acc_o[0]);
+              acc_o[1] = fmaf(x.y, w, acc_o[1]);
+              acc_o[2] = fmaf(x.z, w, acc_o[2]);
+              acc_o[3] = fmaf(x.w, w, acc_o[3]);
+            } else {
+              const float2 x = __ldcg(reinterpret_cast<const float2*>(po + (long long)p * D));
+              acc_o[0] = fmaf(x.x, w, acc_o[0]);
+              acc_o[1] = fmaf(x.y, w, acc_o[1]);
+            }
+          }
+          const int n_dst = f.peer_bases != nullptr ? f.n_peers : 1;
+          for (int p = 0; p < n_dst; ++p) {
+            float* base = f.peer_bases != nullptr ? f.peer_bases[p] + f.slot_offset : f.out_slot;
+            float* dst = base + (long long)bh * D + lane * kVec;
+            if constexpr (kVec == 4) {
+              *reinterpret_cast<float4*>(dst) = make_float4(acc_o[0], acc_o[1], acc_o[2], acc_o[3]);
+            } else {
+              *reinterpret_cast<float2*>(dst) = make_float2(acc_o[0], acc_o[1]);
+            }
+            if (lane == 0)
+              *reinterpret_cast<float2*>(base + (long long)f.rows * D + (long long)bh * 2) = make_float2(m, l);
+          }
+          __threadfence_system();                      // my peer stores are performed before the row is counted
+          __syncwarp();
+          if (lane == 0) {
+            f.row_arrivals[bh] = 0;                    // re-armed for the next step
+            if (atomicAdd(f.rows_done, 1u) == (unsigned)f.rows - 1u) {
+              // the rank's last row: re-arm the counter and raise this rank's flag everywhere
+              *f.rows_done = 0;
+              __threadfence_system();
+              if (f.peer_bases != nullptr)
+                for (int p = 0; p < f.n_peers; ++p)
+                  st_release_sys(reinterpret_cast<unsigned*>(f.peer_bases[p] + f.flag_offset) + f.my_rank, f.step);
+            }
+          }
+        }
+        n += batch;
+      }
+    }
+  } else if (warp == kDecConsumerThreads / 32) {
     // ------------------------------------------------------------ producer --
     if (lane == 0) {
       const uint64_t policy = l2_policy_evict_first();
@@ -245,6 +341,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
     const int g = tid % kLpr;        // which 8 head dims this lane owns
     const int r = tid / kLpr;        // key group
     uint32_t stage = 0, phase = 0;
+    uint32_t n_done = 0;             // items this CTA has handed to the merger warp
     bool ok = true;
 
     // Index (within the kKpt keys this thread touches per stage) of the key
@@ -438,54 +535,18 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
         args.part_ml[(long long)item * 2 + 1] = l;
       }
 
-      if (args.fuse.row_arrivals != nullptr) {
-        // ---- fused merge: whoever finishes a row's last split merges the row ----
-        const DecodeFuseArgs& f = args.fuse;
-        __threadfence();                 // this item's partial row is visible device-wide ...
-        consumer_sync();
-        if (tid == 0)                    // ... before its arrival is counted
-          *s_last = (atomicAdd(f.row_arrivals + bh, 1u) == (unsigned)args.num_splits - 1u) ? 1 : 0;
-        consumer_sync();
-        if (*s_last) {
-          __threadfence();
-          if (tid < D) {
-            // (partial rows written by other SMs: read past L1)
-            const float* ml = args.part_ml + (long long)bh * args.num_splits * 2;
-            const float* po = args.part_o + (long long)bh * args.num_splits * D;
-            float m = -INFINITY;
-            for (int p = 0; p < args.num_splits; ++p) m = fmaxf(m, __ldcg(ml + 2 * p));
-            float acc_o = 0.f, l = 0.f;
-            for (int p = 0; p < args.num_splits; ++p) {
-              const float mp = __ldcg(ml + 2 * p), lp = __ldcg(ml + 2 * p + 1);
-              const float w = (mp == -INFINITY) ? 0.f : fast_exp2(mp - m);
-              l = fmaf(lp, w, l);
-              acc_o = fmaf(__ldcg(po + (long long)p * D + tid), w, acc_o);
-            }
-            const int n_dst = f.peer_bases != nullptr ? f.n_peers : 1;
-            for (int p = 0; p < n_dst; ++p) {
-              float* base = f.peer_bases != nullptr ? f.peer_bases[p] + f.slot_offset : f.out_slot;
-              base[(long long)bh * D + tid] = acc_o;
-              if (tid == 0) {
-                float* mlp = base + (long long)f.rows * D + (long long)bh * 2;
-                mlp[0] = m;
-                mlp[1] = l;
-              }
-            }
-          }
-          if (tid == 0) f.row_arrivals[bh] = 0;      // re-armed for the next step
-          __threadfence_system();                    // my peer stores are performed before the row is counted
-          consumer_sync();
-          if (tid == 0) {
-            if (atomicAdd(f.rows_done, 1u) == (unsigned)f.rows - 1u) {
-              // the rank's last row: re-arm the counter and raise this rank's flag everywhere
-              *f.rows_done = 0;
-              __threadfence_system();
-              if (f.peer_bases != nullptr)
-                for (int p = 0; p < f.n_peers; ++p)
-                  st_release_sys(reinterpret_cast<unsigned*>(f.peer_bases[p] + f.flag_offset) + f.my_rank, f.step);
-            }
-          }
-        }
+      if (fused) {
+        // Tell the merger warp that this item's partial row is written (one arrival
+        // per warp; the arrival orders the warp's stores before it).  The slot must
+        // have been taken kDecDoneSlots items ago, which it always has unless the
+        // merger is that far behind.
+        if (n_done >= kDecDoneSlots)
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_free + (n_done % kDecDoneSlots) * 8,
+                                                 ((n_done / kDecDoneSlots) - 1) & 1, abort_flag, kWaitDecFree));
+        if (!ok) break;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_done + (n_done % kDecDoneSlots) * 8);
+        ++n_done;
       }
     }
 

@@ -13,6 +13,7 @@ constexpr AttnVariant kAttnVariants[] = {
     {TF_F16, 64, 256, 128, 1},  {TF_BF16, 64, 256, 128, 1},
     {TF_F16, 128, 128, 128, 2}, {TF_BF16, 128, 128, 128, 2},
     {TF_F16, 64, 128, 128, 2},  {TF_BF16, 64, 128, 128, 2},
+    {TF_F16, 256, 128, 128, 1}, {TF_BF16, 256, 128, 128, 1},
     {0, 0, 0, 0, 0},
 };
 constexpr int kDecodeCtasPerSm = 2;
@@ -20,6 +21,11 @@ constexpr int kDecodeStages = 3;
 }  // namespace
 
 const AttnVariant* attn_variants() { return kAttnVariants; }
+
+int head_dim_bucket(int head_dim, int head_dim_v) {
+  const int need = std::max(head_dim, head_dim_v);
+  return need <= 64 ? 64 : need <= 128 ? 128 : 256;
+}
 
 void plan_attn(const TfAttnDesc& d, int sm_count, TfAttnPlan* plan) {
   // Heuristic: a single Q tile cannot use the two-tile schedule, and a problem
@@ -32,15 +38,22 @@ void plan_attn(const TfAttnDesc& d, int sm_count, TfAttnPlan* plan) {
   const int64_t singles = bh * ((d.len_q + 127) / 128);
   const bool few_pairs = pairs < sm_count && !(pairs * 4 >= (int64_t)sm_count * 3 && d.len_kv >= 2048);
   const int want_tile_q = (d.len_q <= 128 || (few_pairs && singles > pairs)) ? 128 : 256;
+  // Kernels exist for head dims 64, 128 and 256; a problem runs on the smallest
+  // one that holds both of its head dims, zero-padded (TMA fills the padding).
+  const int bucket = head_dim_bucket(d.head_dim, d.head_dim_v);
   const AttnVariant* best = nullptr;
+  const AttnVariant* any = nullptr;
   const AttnVariant* hinted = nullptr;
   for (const AttnVariant* v = kAttnVariants; v->head_dim != 0; ++v) {
-    if (v->dtype != d.dtype || v->head_dim != d.head_dim) continue;
+    if (v->dtype != d.dtype || v->head_dim != bucket) continue;
+    if (any == nullptr) any = v;
     if (v->tile_q == want_tile_q && best == nullptr) best = v;
     // A caller's tile hint wins when it names a compiled variant.
     if (d.tile_q == v->tile_q && d.tile_kv == v->tile_kv && hinted == nullptr) hinted = v;
   }
+  if (best == nullptr) best = any;       // (head dim 256 has the one-tile kernel only)
   if (hinted != nullptr) best = hinted;
+  plan->head_dim_kernel = bucket;
   plan->tile_q = best->tile_q;
   plan->tile_kv = best->tile_kv;
   plan->ctas_per_sm = best->ctas_per_sm;

@@ -25,6 +25,9 @@ struct AttnVariant {
 // The table of compiled prefill variants (terminated by head_dim == 0).
 const AttnVariant* attn_variants();
 
+// Compiled head dim (64, 128 or 256) that a problem with these head dims runs on.
+int head_dim_bucket(int head_dim, int head_dim_v);
+
 // Fills `plan` for `desc` on a GPU with `sm_count` SMs.  `desc` must have been
 // validated by the caller.
 void plan_attn(const TfAttnDesc& desc, int sm_count, TfAttnPlan* plan);
