@@ -160,6 +160,24 @@ TF_EXPORT int tf_attn_fwd(const void* q, const void* k, const void* v, void* o,
                           float* lse, const TfAttnDesc* desc, void* stream);
 
 /*
+ * Attention backward: dQ, dK, dV from Q, K, V, O, dO and the log-sum-exp rows
+ * (`lse`, fp32 [B,H,Lq], as tf_attn_fwd writes them).  No counterpart in the
+ * reference, which has no backward pass; the forward's operand conventions are
+ * kept.  `desc` describes the forward problem; K and V are read as [Lk, D] /
+ * [Lk, Dv] (k_stride_d == v_stride_d == 1), head_dim == head_dim_v in
+ * {64, 128}.  d_o is laid out like o (o's strides), dq like q, dk like k, dv
+ * like v.  P and dS are rounded to the 16-bit type before the second products,
+ * accumulation is fp32, results are deterministic (no atomics).  `workspace`
+ * (tf_attn_bwd_workspace_bytes: B*H*Lq fp32 for the delta rows) is scratch.
+ * Three launches on `stream`, asynchronous.
+ */
+TF_EXPORT int tf_attn_bwd(const void* q, const void* k, const void* v, const void* o,
+                          const void* d_o, const float* lse, void* dq, void* dk, void* dv,
+                          const TfAttnDesc* desc, void* workspace, uint64_t workspace_bytes,
+                          void* stream);
+TF_EXPORT uint64_t tf_attn_bwd_workspace_bytes(const TfAttnDesc* desc);
+
+/*
  * Tile plan the registry would use for `desc`.  Stands in for the tile
  * arguments the reference bakes in as template constants
  * (src/kernels/flash_attn.cu:16-55, :87-99) and for its per-shape JIT cache

@@ -152,6 +152,22 @@ def decode_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     return attention_fp32(q, k, v, scale, causal=False)
 
 
+def attention_bwd_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, d_o: torch.Tensor, scale: float,
+                       causal: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of ``attention_fp32`` with respect to q, k and v for the upstream
+    gradient ``d_o``, by reverse-mode differentiation of that same closed form in
+    fp32 on the host.  TileFusion has no backward pass and therefore pins nothing
+    here; the reference point is the gradient of the expression that its
+    ``FlashAttentionRef`` class pins for the forward.  q ``[..., Lq, D]``,
+    k/v ``[..., Lk, D]``, d_o ``[..., Lq, Dv]``; returns fp32 (dq, dk, dv)."""
+    qf = q.detach().float().requires_grad_(True)
+    kf = k.detach().float().requires_grad_(True)
+    vf = v.detach().float().requires_grad_(True)
+    out, _ = attention_fp32(qf, kf, vf, scale, causal)
+    out.backward(d_o.float())
+    return qf.grad, kf.grad, vf.grad
+
+
 def fused_two_gemms_fp32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
     """``(A @ B^T) @ C^T`` as TileFusion's test states it
     (``tests/python/test_fused_two_gemms.py:100``: ``input_a @ input_b.t() @ input_c.t()``

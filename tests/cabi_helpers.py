@@ -52,6 +52,24 @@ def attn_fwd(q, k, v, scale, causal=False, want_lse=True, poison=True, tile_q=0)
     return o, (lse if want_lse else None)
 
 
+def attn_bwd(q, k, v, o, d_o, lse, scale, causal=False):
+    """Runs tf_attn_bwd; q/o/d_o [B,H,Lq,D], k/v [B,H,Lk,D] (rows contiguous), lse [B,H,Lq].
+    Returns (dq, dk, dv), NaN-filled before the call."""
+    lib = _cabi.lib()
+    d_o = d_o.contiguous() if d_o.stride() != o.stride() else d_o
+    # dq / dk / dv take the strides of q / k / v (the entry point's convention)
+    dq, dk, dv = (torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=t.device).fill_(float("nan"))
+                  for t in (q, k, v))
+    d = attn_desc(q, k, v, o, scale, causal)
+    need = lib.tf_attn_bwd_workspace_bytes(C.byref(d))
+    ws = torch.empty(max(1, need // 4), dtype=torch.float32, device=q.device)
+    rc = lib.tf_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
+                         dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), C.byref(d), ws.data_ptr(), ws.numel() * 4,
+                         _stream())
+    _cabi.check(rc)
+    return dq, dk, dv
+
+
 def decode_desc(q, k, v, o=None, scale=None, kv_chunk=512, num_splits=0) -> _cabi.TfDecodeDesc:
     """q [B,H,1,D], k/v [B,H,Lk,D]."""
     d = _cabi.TfDecodeDesc()

@@ -32,7 +32,7 @@ EXPORTED = (
     "tf_decode_partial_scatter", "tf_decode_gathered_wait", "tf_fused_two_gemms",
     "tf_shard_head_slice", "tf_shard_kv_slice", "tf_prefill_sharded", "tf_shard_unique_id",
     "tf_shard_create", "tf_shard_transport", "tf_shard_note", "tf_decode_sharded", "tf_shard_destroy",
-    "tf_device_status_peek", "tf_set_wait_limit_ms",
+    "tf_device_status_peek", "tf_set_wait_limit_ms", "tf_attn_bwd", "tf_attn_bwd_workspace_bytes",
 )
 TF_NCCL_ID_BYTES = 128
 TF_TRANSPORT_AUTO, TF_TRANSPORT_P2P, TF_TRANSPORT_NCCL = 0, 1, 2
@@ -112,6 +112,8 @@ def lib() -> C.CDLL:
     fp = C.c_void_p  # float* passed as raw addresses
     handle.tf_attn_fwd.argtypes = [vp, vp, vp, vp, fp, C.POINTER(TfAttnDesc), vp]
     handle.tf_attn_plan.argtypes = [C.POINTER(TfAttnDesc), C.POINTER(TfAttnPlan)]
+    handle.tf_attn_bwd.argtypes = [vp, vp, vp, vp, vp, fp, vp, vp, vp, C.POINTER(TfAttnDesc), vp, u64, vp]
+    handle.tf_attn_bwd_workspace_bytes.argtypes = [C.POINTER(TfAttnDesc)]
     handle.tf_decode_plan.argtypes = [C.POINTER(TfDecodeDesc), C.POINTER(TfDecodePlan)]
     handle.tf_decode_split.argtypes = [vp, vp, vp, vp, u64, C.POINTER(TfDecodeDesc), vp]
     handle.tf_decode_combine.argtypes = [
@@ -142,9 +144,10 @@ def lib() -> C.CDLL:
     handle.tf_decode_sharded.argtypes = [vp, vp, vp, vp, vp, fp, C.POINTER(TfDecodeDesc), vp]
     handle.tf_shard_destroy.argtypes = [vp]
     for name in EXPORTED:
-        if name not in ("tf_last_error", "tf_decode_static_capacity", "tf_shard_note"):
+        if name not in ("tf_last_error", "tf_decode_static_capacity", "tf_shard_note", "tf_attn_bwd_workspace_bytes"):
             getattr(handle, name).restype = C.c_int
     handle.tf_decode_static_capacity.restype = C.c_uint64
+    handle.tf_attn_bwd_workspace_bytes.restype = C.c_uint64
     _lib = handle
     return handle
 

@@ -18,6 +18,7 @@
 
 #include "attn_fwd_sm100.cuh"
 #include "attn_fwd_pair_sm100.cuh"
+#include "attn_bwd_sm100.cuh"
 #include "decode_sm100.cuh"
 #include "internal.h"
 #include "registry.h"
@@ -337,6 +338,81 @@ int run_attn(const void* q, const void* k, const void* v, void* o, float* lse, c
     if (plan.tile_q == 256) return launch_attn_pair<T, D>(L, d, plan, stream);
   }
   return launch_attn<T, D>(L, d, stream);
+}
+
+// Backward: delta rows, then the dK/dV kernel (one CTA per key tile) and the dQ
+// kernel (one CTA per query tile).
+template <typename T, int D>
+int launch_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                    void* dq, void* dk, void* dv, float* delta, const TfAttnDesc* d, cudaStream_t stream) {
+  using Smem = tfb::AttnBwdSmem<D>;
+  const uint64_t B = d->batch, H = d->heads;
+  CUtensorMap mq, mk, mv, mdo;
+  {
+    const uint64_t dq_dims[4] = {(uint64_t)D, (uint64_t)d->len_q, H, B};
+    const uint64_t dk_dims[4] = {(uint64_t)D, (uint64_t)d->len_kv, H, B};
+    const int64_t qs[3] = {d->q_stride_l, d->q_stride_h, d->q_stride_b};
+    const int64_t ks[3] = {d->k_stride_l, d->k_stride_h, d->k_stride_b};
+    const int64_t vs[3] = {d->v_stride_l, d->v_stride_h, d->v_stride_b};
+    const int64_t os[3] = {d->o_stride_l, d->o_stride_h, d->o_stride_b};
+    if (int rc = encode_map(&mq, d->dtype, q, dq_dims, qs, 64, tfb::kAttnTile, "Q")) return rc;
+    if (int rc = encode_map(&mk, d->dtype, k, dk_dims, ks, 64, tfb::kAttnTile, "K")) return rc;
+    if (int rc = encode_map(&mv, d->dtype, v, dk_dims, vs, 64, tfb::kAttnTile, "V")) return rc;
+    if (int rc = encode_map(&mdo, d->dtype, d_o, dq_dims, os, 64, tfb::kAttnTile, "dO")) return rc;
+  }
+  const long long rows = (long long)B * H * d->len_q;
+  tfb::AttnBwdDeltaArgs da;
+  da.o = o;
+  da.d_o = d_o;
+  da.delta = delta;
+  da.len_q = d->len_q;
+  da.heads = d->heads;
+  da.rows = rows;
+  da.o_stride_b = da.do_stride_b = d->o_stride_b;
+  da.o_stride_h = da.do_stride_h = d->o_stride_h;
+  da.o_stride_l = da.do_stride_l = d->o_stride_l;
+  tfb::attn_bwd_delta_kernel<T, D><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(da);
+  TF_CUDA_TRY(cudaGetLastError());
+
+  tfb::AttnBwdArgs a;
+  a.lse = lse;
+  a.delta = delta;
+  a.dq = dq;
+  a.dk = dk;
+  a.dv = dv;
+  a.len_q = d->len_q;
+  a.len_kv = d->len_kv;
+  a.causal = d->causal ? 1 : 0;
+  a.scale = d->softmax_scale;
+  a.scale_log2 = d->softmax_scale * 1.4426950408889634f;
+  a.dq_stride_b = d->q_stride_b;
+  a.dq_stride_h = d->q_stride_h;
+  a.dq_stride_l = d->q_stride_l;
+  a.dk_stride_b = d->k_stride_b;
+  a.dk_stride_h = d->k_stride_h;
+  a.dk_stride_l = d->k_stride_l;
+  a.dv_stride_b = d->v_stride_b;
+  a.dv_stride_h = d->v_stride_h;
+  a.dv_stride_l = d->v_stride_l;
+  a.row_stride_b = (long long)d->heads * d->len_q;
+  a.row_stride_h = d->len_q;
+  auto dkv = tfb::attn_bwd_kernel<T, D, true>;
+  auto dqk = tfb::attn_bwd_kernel<T, D, false>;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  TF_CUDA_TRY(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    TF_CUDA_TRY(cudaFuncSetAttribute(dkv, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
+    TF_CUDA_TRY(cudaFuncSetAttribute(dqk, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
+    configured_device = dev;
+  }
+  const int n_q_tiles = (d->len_q + tfb::kAttnTile - 1) / tfb::kAttnTile;
+  const int n_kv_tiles = (d->len_kv + tfb::kAttnTile - 1) / tfb::kAttnTile;
+  dkv<<<dim3(n_kv_tiles, d->heads, d->batch), tfb::kAttnThreads, Smem::kBytes, stream>>>(mq, mk, mv, mdo, a);
+  TF_CUDA_TRY(cudaGetLastError());
+  dqk<<<dim3(n_q_tiles, d->heads, d->batch), tfb::kAttnThreads, Smem::kBytes, stream>>>(mq, mk, mv, mdo, a);
+  TF_CUDA_TRY(cudaGetLastError());
+  return TF_OK;
 }
 
 int check_decode_desc(const TfDecodeDesc* d) {
@@ -712,6 +788,45 @@ int tf_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
       return desc->dtype == TF_F16 ? run_attn<__half, 64>(q, k, v, o, lse, desc, plan, s)
                                    : run_attn<__nv_bfloat16, 64>(q, k, v, o, lse, desc, plan, s);
   }
+}
+
+uint64_t tf_attn_bwd_workspace_bytes(const TfAttnDesc* desc) {
+  if (desc == nullptr || desc->batch < 1 || desc->heads < 1 || desc->len_q < 1) return 0;
+  return (uint64_t)desc->batch * desc->heads * desc->len_q * sizeof(float);
+}
+
+int tf_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                void* dq, void* dk, void* dv, const TfAttnDesc* desc, void* workspace, uint64_t workspace_bytes,
+                void* stream) {
+  if (int rc = check_attn_desc(desc)) return rc;
+  if (desc->head_dim != desc->head_dim_v || (desc->head_dim != 64 && desc->head_dim != 128))
+    return fail(TF_ERR_UNSUPPORTED, "the backward pass is compiled for head_dim == head_dim_v in {64, 128} (got %d, %d)",
+                desc->head_dim, desc->head_dim_v);
+  if (desc->k_stride_d != 1 || desc->v_stride_d != 1)
+    return fail(TF_ERR_UNSUPPORTED, "the backward pass reads K as [Lk, D] and V as [Lk, Dv] (rows contiguous)");
+  if (q == nullptr || k == nullptr || v == nullptr || o == nullptr || d_o == nullptr || lse == nullptr ||
+      dq == nullptr || dk == nullptr || dv == nullptr)
+    return fail(TF_ERR_BAD_ARG, "q, k, v, o, d_o, lse, dq, dk and dv must be non-null");
+  if (!aligned16(o) || !aligned16(d_o) || !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
+    return fail(TF_ERR_UNSUPPORTED, "o, d_o, dq, dk and dv must be 16-byte aligned");
+  const int64_t st[] = {desc->q_stride_b, desc->q_stride_h, desc->q_stride_l, desc->k_stride_b, desc->k_stride_h,
+                        desc->k_stride_l, desc->v_stride_b, desc->v_stride_h, desc->v_stride_l};
+  for (int64_t x : st)
+    if (x % 8 != 0 || x < 0) return fail(TF_ERR_UNSUPPORTED, "strides must be non-negative multiples of 8 elements (16 bytes)");
+  if (workspace == nullptr || !aligned16(workspace)) return fail(TF_ERR_BAD_ARG, "workspace must be non-null and 16-byte aligned");
+  const uint64_t need = tf_attn_bwd_workspace_bytes(desc);
+  if (workspace_bytes < need)
+    return fail(TF_ERR_WORKSPACE, "workspace holds %llu bytes but %llu are needed", (unsigned long long)workspace_bytes,
+                (unsigned long long)need);
+  if (int rc = tfb::ensure_device_ready()) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* delta = static_cast<float*>(workspace);
+  if (desc->head_dim == 128)
+    return desc->dtype == TF_F16
+               ? launch_attn_bwd<__half, 128>(q, k, v, o, d_o, lse, dq, dk, dv, delta, desc, s)
+               : launch_attn_bwd<__nv_bfloat16, 128>(q, k, v, o, d_o, lse, dq, dk, dv, delta, desc, s);
+  return desc->dtype == TF_F16 ? launch_attn_bwd<__half, 64>(q, k, v, o, d_o, lse, dq, dk, dv, delta, desc, s)
+                               : launch_attn_bwd<__nv_bfloat16, 64>(q, k, v, o, d_o, lse, dq, dk, dv, delta, desc, s);
 }
 
 int tf_fused_two_gemms(const void* a, const void* b, const void* c, void* d, int32_t m, int32_t n, int32_t k,

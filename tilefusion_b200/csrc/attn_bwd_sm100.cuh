@@ -1,0 +1,400 @@
+// Attention backward for sm_100a: dQ, dK, dV from Q, K, V, O, dO and the
+// log-sum-exp rows the forward kernels emit.  TileFusion has no backward pass
+// (its attention path ends at include/kernels/flash_attention_device.cuh:130-312);
+// this extends the path with the same building blocks as the forward kernel in
+// attn_fwd_sm100.cuh: TMA tile loads with 128-byte swizzle, tcgen05.mma with
+// accumulators in tensor memory, one thread per tile row for the element-wise
+// stage, every wait bounded.
+//
+// Per (batch, head), with s = softmax_scale:
+//   P  = exp(s Q K^T - LSE)            (recomputed tile by tile, never stored)
+//   dV = P^T dO          dP = dO V^T          delta_i = sum_d dO_id O_id
+//   dS = P o (dP - delta) * s          dQ = dS K          dK = dS^T Q
+// Three kernels:
+//   attn_bwd_delta_kernel   delta rows (fp32), one warp per query row;
+//   attn_bwd_dkv_kernel     one CTA per 128-key tile, loops over the query tiles:
+//                           S^T = K Q^T and dP^T = V dO^T into tensor memory
+//                           (keys on the 128 lanes), threads turn them into P^T
+//                           and dS^T (16-bit, written over the fp32 tiles they
+//                           came from) and the second pair of MMAs reads those as
+//                           TMEM A operands: dV += P^T dO, dK += dS^T Q.  The dO
+//                           and Q tiles in shared memory serve both pairs: as
+//                           K-major B operands of the first and MN-major B
+//                           operands of the second, so nothing is transposed;
+//   attn_bwd_dq_kernel      one CTA per 128-query tile, loops over the key tiles:
+//                           S = Q K^T, dP = dO V^T, dS over dP, dQ += dS K.
+// TMEM: S|dP|dV|dK = 128+128+D+D columns (dK/dV kernel), S|dP|dQ (dQ kernel).
+// P and dS are rounded to the 16-bit input type before the second MMAs, all
+// accumulation is fp32.  The two kernels recompute S and dP independently (7
+// tile products per tile pair instead of 5), which keeps dQ free of atomics and
+// the results deterministic.
+#pragma once
+
+#include <type_traits>
+
+#include "attn_fwd_sm100.cuh"
+
+namespace tfb {
+
+struct AttnBwdArgs {
+  const float* lse;        // [B, H, Lq] natural log, as written by the forward
+  const float* delta;      // [B, H, Lq]
+  void* dq;
+  void* dk;
+  void* dv;
+  int len_q;
+  int len_kv;
+  int causal;
+  float scale;             // softmax_scale
+  float scale_log2;        // softmax_scale * log2(e)
+  long long dq_stride_b, dq_stride_h, dq_stride_l;
+  long long dk_stride_b, dk_stride_h, dk_stride_l;
+  long long dv_stride_b, dv_stride_h, dv_stride_l;
+  long long row_stride_b, row_stride_h;     // of lse and delta
+};
+
+struct AttnBwdDeltaArgs {
+  const void* o;
+  const void* d_o;
+  float* delta;
+  int len_q;
+  int heads;
+  long long rows;          // B * H * Lq
+  long long o_stride_b, o_stride_h, o_stride_l;
+  long long do_stride_b, do_stride_h, do_stride_l;
+};
+
+// delta[b, h, i] = sum_d O[b, h, i, d] * dO[b, h, i, d]; one warp per row.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const AttnBwdDeltaArgs a) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long bh = row / a.len_q;
+  const int i = (int)(row - bh * a.len_q);
+  const int b = (int)(bh / a.heads), h = (int)(bh - (long long)b * a.heads);
+  const T* o = reinterpret_cast<const T*>(a.o) + b * a.o_stride_b + h * a.o_stride_h + i * a.o_stride_l;
+  const T* g = reinterpret_cast<const T*>(a.d_o) + b * a.do_stride_b + h * a.do_stride_h + i * a.do_stride_l;
+  constexpr int kPerLane = D / 32;          // 2 or 4 elements
+  float acc = 0.f;
+  if constexpr (kPerLane == 4) {
+    const uint2 x = *reinterpret_cast<const uint2*>(o + lane * 4);
+    const uint2 y = *reinterpret_cast<const uint2*>(g + lane * 4);
+    const float2 x0 = unpack2<T>(x.x), x1 = unpack2<T>(x.y), y0 = unpack2<T>(y.x), y1 = unpack2<T>(y.y);
+    acc = x0.x * y0.x + x0.y * y0.y + x1.x * y1.x + x1.y * y1.y;
+  } else {
+    const uint32_t x = *reinterpret_cast<const uint32_t*>(o + lane * 2);
+    const uint32_t y = *reinterpret_cast<const uint32_t*>(g + lane * 2);
+    const float2 x0 = unpack2<T>(x), y0 = unpack2<T>(y);
+    acc = x0.x * y0.x + x0.y * y0.y;
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) a.delta[row] = acc;
+}
+
+template <int D>
+struct AttnBwdSmem {
+  static constexpr int kTileBytes = kAttnTile * D * 2;
+  static constexpr int kBlockBytes = kAttnTile * 128;
+  // fixed pair (K, V in the dK/dV kernel; Q, dO in the dQ kernel), then two slots of the streamed pair
+  static constexpr int kOffFixed = 0;
+  static constexpr int kOffStream = 2 * kTileBytes;
+  static constexpr int kOffRows = 6 * kTileBytes;               // lse2 / delta of the streamed tile: [2][2][128] fp32
+  static constexpr int kOffBar = kOffRows + 2 * 2 * kAttnTile * 4;
+  static constexpr int kOffTmemSlot = kOffBar + 64;
+  static constexpr int kOffAbort = kOffBar + 68;
+  static constexpr int kBytes = kOffBar + 128 + 1024;
+};
+
+enum AttnBwdWaitCode {
+  kBWaitFixed = 501, kBWaitStream = 502, kBWaitS = 503, kBWaitP = 504, kBWaitSlot = 505, kBWaitEpi = 506
+};
+
+__device__ __forceinline__ void bwd_rows_sync() {
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// Shared by the two kernels: which tensor plays which role is the only difference.
+//   kDkv = true : fixed = (K, V) of key tile `tile`;  streamed = (Q, dO) of query tiles
+//                 lanes = keys;   outputs dV (columns 256..) and dK
+//   kDkv = false: fixed = (Q, dO) of query tile `tile`; streamed = (K, V) of key tiles
+//                 lanes = queries; output dQ
+template <typename T, int D, bool kDkv>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                const AttnBwdArgs args) {
+  using S = AttnBwdSmem<D>;
+  constexpr int kIsBf16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr int kTmemCols = 512;
+  constexpr int kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 256 + D;
+  constexpr int kBlocks = D / 64;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sFix0 = smem_base + S::kOffFixed;                    // K (dkv) / Q (dq)
+  const uint32_t sFix1 = sFix0 + S::kTileBytes;                       // V (dkv) / dO (dq)
+  auto sStr0 = [&](int slot) { return smem_base + S::kOffStream + slot * 2 * S::kTileBytes; };   // Q / K
+  auto sStr1 = [&](int slot) { return sStr0(slot) + S::kTileBytes; };                            // dO / V
+  float* s_rows = reinterpret_cast<float*>(smem_gen + S::kOffRows);   // [slot][lse2 | delta][128]
+  const uint32_t bar_fix = smem_base + S::kOffBar + 0;
+  const uint32_t bar_str = smem_base + S::kOffBar + 8;     // [2]
+  const uint32_t bar_s = smem_base + S::kOffBar + 24;
+  const uint32_t bar_p = smem_base + S::kOffBar + 32;
+  const uint32_t bar_o = smem_base + S::kOffBar + 40;      // [2]
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kOffTmemSlot);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tile = blockIdx.x;
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int t0 = tile * kAttnTile;              // first key (dkv) / query (dq) of this CTA
+
+  // streamed tiles visited: [first, first + n)
+  const int n_q_tiles = (args.len_q + kAttnTile - 1) / kAttnTile;
+  const int n_kv_tiles = (args.len_kv + kAttnTile - 1) / kAttnTile;
+  int first = 0, n = 0;
+  if (kDkv) {
+    first = args.causal ? min(tile, n_q_tiles) : 0;      // query tiles below the diagonal see none of these keys
+    n = n_q_tiles - first;
+  } else {
+    n = args.causal ? min(n_kv_tiles, tile + 1) : n_kv_tiles;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_fix, 1);
+    mbar_init(bar_str, 1);
+    mbar_init(bar_str + 8, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_p, 128);
+    mbar_init(bar_o, 1);
+    mbar_init(bar_o + 8, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc<kTmemCols>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0 && n > 0) {
+      // ------------------------------------------------ TMA + MMA issuer ----
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      tma_prefetch_desc(&map_do);
+      const CUtensorMap* m_fix0 = kDkv ? &map_k : &map_q;
+      const CUtensorMap* m_fix1 = kDkv ? &map_v : &map_do;
+      const CUtensorMap* m_str0 = kDkv ? &map_q : &map_k;
+      const CUtensorMap* m_str1 = kDkv ? &map_do : &map_v;
+      auto load_tile = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int row0) {
+#pragma unroll
+        for (int blk = 0; blk < kBlocks; ++blk)
+          tma_load_4d(dst + blk * S::kBlockBytes, map, bar, blk * 64, row0, head, batch);
+      };
+      auto load_stream = [&](int it) {
+        const int slot = it & 1;
+        mbar_arrive_expect_tx(bar_str + slot * 8, 2 * S::kTileBytes);
+        load_tile(sStr0(slot), m_str0, bar_str + slot * 8, (first + it) * kAttnTile);
+        load_tile(sStr1(slot), m_str1, bar_str + slot * 8, (first + it) * kAttnTile);
+      };
+      // All operands are [128 rows][D] tiles, rows 128 B per 64-column block, 128-byte swizzle.
+      // As the K-major operand of a product over D (rows = the tile's own index):
+      auto desc_kmajor = [&](uint32_t tile_smem, int k) {
+        return make_smem_desc(tile_smem + (k >> 2) * S::kBlockBytes + (k & 3) * 32, 16, 1024);
+      };
+      // As the MN-major B operand of a product over the tile's rows (N = D):
+      auto desc_rows = [&](uint32_t tile_smem, int k) {
+        return make_smem_desc(tile_smem + k * 2048, S::kBlockBytes, 1024);
+      };
+      const uint32_t idesc_sd = make_idesc(128, 128, kIsBf16, 0, 0);
+      const uint32_t idesc_acc = make_idesc(128, D, kIsBf16, 0, 1);
+
+      mbar_arrive_expect_tx(bar_fix, 2 * S::kTileBytes);
+      load_tile(sFix0, m_fix0, bar_fix, t0);
+      load_tile(sFix1, m_fix1, bar_fix, t0);
+      load_stream(0);
+      if (n > 1) load_stream(1);
+
+      bool ok = mbar_wait(bar_fix, 0, abort_flag, kBWaitFixed);
+      for (int it = 0; ok && it < n; ++it) {
+        const int slot = it & 1;
+        ok = mbar_wait(bar_str + slot * 8, (it >> 1) & 1, abort_flag, kBWaitStream);
+        if (!ok) break;
+        tc_fence_after();
+        // first pair: lanes x streamed rows, contraction over D
+        //   dkv: S^T = K Q^T, dP^T = V dO^T        dq: S = Q K^T, dP = dO V^T
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_ss(tmem_base + kColS, desc_kmajor(sFix0, k), desc_kmajor(sStr0(slot), k), idesc_sd, k > 0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_ss(tmem_base + kColDP, desc_kmajor(sFix1, k), desc_kmajor(sStr1(slot), k), idesc_sd, k > 0);
+        umma_commit(bar_s);
+        // the other slot is free once the second pair of the previous iteration has read it
+        if (it >= 1 && it + 1 < n) {
+          ok = mbar_wait(bar_o + (slot ^ 1) * 8, ((it - 1) >> 1) & 1, abort_flag, kBWaitSlot);
+          if (!ok) break;
+          load_stream(it + 1);
+        }
+        ok = mbar_wait(bar_p, it & 1, abort_flag, kBWaitP);
+        if (!ok) break;
+        tc_fence_after();
+        // second pair: A from tensor memory (16-bit, 2 values per column), contraction over the streamed rows
+        if (kDkv) {
+#pragma unroll
+          for (int k = 0; k < kAttnTile / 16; ++k)      // dV += P^T dO
+            umma_ts(tmem_base + kColAcc0, tmem_base + kColS + k * 8, desc_rows(sStr1(slot), k), idesc_acc,
+                    (it > 0) || (k > 0));
+#pragma unroll
+          for (int k = 0; k < kAttnTile / 16; ++k)      // dK += dS^T Q
+            umma_ts(tmem_base + kColAcc1, tmem_base + kColDP + k * 8, desc_rows(sStr0(slot), k), idesc_acc,
+                    (it > 0) || (k > 0));
+        } else {
+#pragma unroll
+          for (int k = 0; k < kAttnTile / 16; ++k)      // dQ += dS K
+            umma_ts(tmem_base + kColAcc0, tmem_base + kColDP + k * 8, desc_rows(sStr0(slot), k), idesc_acc,
+                    (it > 0) || (k > 0));
+        }
+        umma_commit(bar_o + slot * 8);
+      }
+      if (!ok) {
+        // let copies still in flight land before the CTA gives up its shared memory
+        const unsigned long long t_start = global_timer_ns();
+        while (global_timer_ns() - t_start < 2000000ull) {
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------- element-wise warps ---
+    const int row = warp * 32 + lane;                       // lane of tensor memory == row of the fixed tile
+    const uint32_t t_lane = tmem_base + (uint32_t(warp * 32) << 16);
+    const int fixed_idx = t0 + row;                         // key index (dkv) / query index (dq)
+    const long long row_base = (long long)batch * args.row_stride_b + (long long)head * args.row_stride_h;
+    bool ok = true;
+
+    // dq: this thread's query row keeps its own lse2 / delta
+    float my_lse2 = 0.f, my_delta = 0.f;
+    if (!kDkv) {
+      const bool valid = fixed_idx < args.len_q;
+      my_lse2 = valid ? args.lse[row_base + fixed_idx] * 1.4426950408889634f : INFINITY;
+      my_delta = valid ? args.delta[row_base + fixed_idx] : 0.f;
+    }
+
+    for (int it = 0; it < n; ++it) {
+      const int s0 = (first + it) * kAttnTile;              // first streamed row (query for dkv, key for dq)
+      float* rows_lse2 = s_rows + (it & 1) * 2 * kAttnTile;
+      float* rows_delta = rows_lse2 + kAttnTile;
+      if (kDkv) {
+        // lse2 / delta of the streamed queries: one value per thread, shared through shared memory
+        const int qi = s0 + row;
+        const bool valid = qi < args.len_q;
+        rows_lse2[row] = valid ? args.lse[row_base + qi] * 1.4426950408889634f : INFINITY;   // P = 0 beyond len_q
+        rows_delta[row] = valid ? args.delta[row_base + qi] : 0.f;
+        bwd_rows_sync();
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_s, it & 1, abort_flag, kBWaitS));
+      if (!ok) break;
+      tc_fence_after();
+
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32], dp[32];
+        tmem_ld32(t_lane + kColS + c * 32, sr);
+        tmem_ld32(t_lane + kColDP + c * 32, dp);
+        tmem_wait_ld();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p[2], ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = s0 + c * 32 + i + e;            // streamed index of this element
+            float lse2, delta;
+            bool masked;
+            if (kDkv) {
+              lse2 = rows_lse2[c * 32 + i + e];
+              delta = rows_delta[c * 32 + i + e];
+              masked = args.causal && fixed_idx > col;      // key beyond the query
+            } else {
+              lse2 = my_lse2;
+              delta = my_delta;
+              masked = col >= args.len_kv || (args.causal && col > fixed_idx);
+            }
+            const float pe = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(sr[i + e]), args.scale_log2, -lse2));
+            p[e] = pe;
+            ds[e] = pe * (__uint_as_float(dp[i + e]) - delta) * args.scale;
+          }
+          pk[i >> 1] = pack2<T>(p[0], p[1]);
+          dk[i >> 1] = pack2<T>(ds[0], ds[1]);
+        }
+        // 16-bit P over the start of S, dS over the start of dP (the fp32 columns
+        // they replace have been read: chunk c lands in columns [16c, 16c + 16))
+        if (kDkv) tmem_st16(t_lane + kColS + c * 16, pk);
+        tmem_st16(t_lane + kColDP + c * 16, dk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p);
+    }
+
+    // ------------------------------------------------------------ epilogue --
+    if (ok && n > 0)
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_o + ((n - 1) & 1) * 8, ((n - 1) >> 1) & 1, abort_flag, kBWaitEpi));
+    if (ok) {
+      if (n > 0) tc_fence_after();
+      auto store_rows = [&](uint32_t col0, void* base, long long sb, long long sh, long long sl, int len) {
+        const bool row_valid = fixed_idx < len;
+        T* out = reinterpret_cast<T*>(base) + (long long)batch * sb + (long long)head * sh + (long long)fixed_idx * sl;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t acc[32];
+          if (n > 0) {
+            tmem_ld32(t_lane + col0 + c * 32, acc);
+            tmem_wait_ld();
+          } else {
+            // (causal, more keys than queries: a key tile no query can see gets zero gradients)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0u;
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o4;
+              o4.x = pack2<T>(__uint_as_float(acc[v * 8 + 0]), __uint_as_float(acc[v * 8 + 1]));
+              o4.y = pack2<T>(__uint_as_float(acc[v * 8 + 2]), __uint_as_float(acc[v * 8 + 3]));
+              o4.z = pack2<T>(__uint_as_float(acc[v * 8 + 4]), __uint_as_float(acc[v * 8 + 5]));
+              o4.w = pack2<T>(__uint_as_float(acc[v * 8 + 6]), __uint_as_float(acc[v * 8 + 7]));
+              *reinterpret_cast<uint4*>(out + c * 32 + v * 8) = o4;
+            }
+          }
+        }
+      };
+      if (kDkv) {
+        store_rows(kColAcc0, args.dv, args.dv_stride_b, args.dv_stride_h, args.dv_stride_l, args.len_kv);
+        store_rows(kColAcc1, args.dk, args.dk_stride_b, args.dk_stride_h, args.dk_stride_l, args.len_kv);
+      } else {
+        store_rows(kColAcc0, args.dq, args.dq_stride_b, args.dq_stride_h, args.dq_stride_l, args.len_q);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown --
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    __syncwarp();
+    tmem_dealloc<kTmemCols>(tmem_base);
+  }
+}
+
+}  // namespace tfb
