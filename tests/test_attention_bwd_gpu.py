@@ -102,6 +102,26 @@ def test_strided_views_and_linearity():
         assert orc.rel_l2(bb.float().cpu(), 2 * a.float().cpu()) <= 1e-3
 
 
+def test_autograd_through_the_python_operator():
+    """tilefusion_b200.ops.flash_attention_autograd in TileFusion's argument convention
+    (key given as [.., D, Lk]): .backward() runs the CUDA backward."""
+    import tilefusion_b200 as tilefusion
+
+    b, h, lq, lk, d = 2, 2, 192, 320, 128
+    q, k, v = orc.seeded_inputs(21, (b, h, lq, d), (b, h, lk, d), (b, h, lk, d), 0.8)
+    d_o = torch.randn(b, h, lq, d, generator=torch.Generator().manual_seed(22)).half()
+    scale = 1.0 / math.sqrt(d)
+    qc = q.cuda().requires_grad_(True)
+    kt = k.cuda().transpose(-1, -2).contiguous().requires_grad_(True)      # key as [.., D, Lk], its own storage
+    vc = v.cuda().requires_grad_(True)
+    out = tilefusion.ops.flash_attention_autograd(qc, kt, vc, scale, True)
+    out.backward(d_o.cuda())
+    rq, rk, rv = orc.attention_bwd_fp32(q, k, v, d_o, scale, True)
+    _check_grad("dQ", qc.grad, rq, torch.float16)
+    _check_grad("dK", kt.grad.transpose(-1, -2), rk, torch.float16)
+    _check_grad("dV", vc.grad, rv, torch.float16)
+
+
 def test_bad_arguments_are_reported():
     import ctypes as C
 

@@ -246,7 +246,7 @@ def test_torch_operator_schema_matches_tilefusion():
     assert str(torch.ops.tilefusion.fused_two_gemms.default._schema) == (
         "tilefusion::fused_two_gemms(Tensor A, Tensor B, Tensor C, Tensor(a!) D, "
         "int tm, int tn, int tk, int tp) -> ()")
-    for op in ("flash_attention_lse", "flash_decoding", "flash_decoding_partial", "flash_decoding_gathered",
+    for op in ("flash_attention_lse", "flash_attention_bwd", "flash_decoding", "flash_decoding_partial", "flash_decoding_gathered",
                "flash_decoding_partial_scatter", "flash_decoding_gathered_wait"):
         assert hasattr(torch.ops.tilefusion, op)
 

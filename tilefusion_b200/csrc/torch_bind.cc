@@ -161,6 +161,68 @@ void flash_attention_lse(const at::Tensor& Q, const at::Tensor& K, const at::Ten
   attention_impl(Q, K, V, O, &LSE, tile_length_q, tile_length_kv, softmax_scale, causal);
 }
 
+// Backward of flash_attention (no counterpart in the reference).  Operand
+// conventions of the forward operator: K [..., Lk, D], V^T [..., Dv, Lk] -- here
+// as a VIEW of a value stored [..., Lk, Dv], which is what
+// value.transpose(-1, -2) gives (the backward kernels read V rows).  dQ / dK /
+// dV^T are written in place and must have the shapes and strides of Q / K / V^T.
+void flash_attention_bwd(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, const at::Tensor& O,
+                         const at::Tensor& dO, const at::Tensor& LSE, at::Tensor& dQ, at::Tensor& dK, at::Tensor& dV,
+                         double softmax_scale, bool causal) {
+  const at::Tensor* all[] = {&Q, &K, &V, &O, &dO, &LSE, &dQ, &dK, &dV};
+  for (const at::Tensor* t : all) TORCH_CHECK(t->is_cuda(), "all tensors must be CUDA tensors");
+  TORCH_CHECK(Q.scalar_type() == K.scalar_type() && Q.scalar_type() == V.scalar_type() && Q.scalar_type() == O.scalar_type() &&
+                  Q.scalar_type() == dO.scalar_type() && Q.scalar_type() == dQ.scalar_type() &&
+                  Q.scalar_type() == dK.scalar_type() && Q.scalar_type() == dV.scalar_type(),
+              "Q, K, V, O, dO, dQ, dK and dV must share one dtype");
+  TORCH_CHECK(Q.dim() == K.dim() && Q.dim() == V.dim() && Q.dim() == O.dim(), "Q, K, V and O must have the same number of dimensions");
+  TORCH_CHECK(dO.sizes() == O.sizes() && dO.strides() == O.strides(), "dO must have the shape and strides of O");
+  TORCH_CHECK(dQ.sizes() == Q.sizes() && dQ.strides() == Q.strides(), "dQ must have the shape and strides of Q");
+  TORCH_CHECK(dK.sizes() == K.sizes() && dK.strides() == K.strides(), "dK must have the shape and strides of K");
+  TORCH_CHECK(dV.sizes() == V.sizes() && dV.strides() == V.strides(), "dV must have the shape and strides of V");
+  TfAttnDesc d{};
+  d.dtype = dtype_code(Q);
+  const Lead lq = lead_dims(Q, "Q"), lk = lead_dims(K, "K"), lv = lead_dims(V, "V"), lo = lead_dims(O, "O");
+  TORCH_CHECK(lq.batch == lk.batch && lq.batch == lv.batch && lq.batch == lo.batch && lq.heads == lk.heads &&
+                  lq.heads == lv.heads && lq.heads == lo.heads,
+              "leading (batch, head) dimensions of Q, K, V and O must match");
+  d.batch = (int32_t)lq.batch;
+  d.heads = (int32_t)lq.heads;
+  d.len_q = (int32_t)Q.size(-2);
+  d.head_dim = (int32_t)Q.size(-1);
+  d.len_kv = (int32_t)K.size(-2);
+  d.head_dim_v = (int32_t)O.size(-1);
+  TORCH_CHECK(K.size(-1) == d.head_dim && O.size(-2) == d.len_q, "expected Q [.., Lq, D], K [.., Lk, D], O [.., Lq, Dv]");
+  TORCH_CHECK(V.size(-2) == d.head_dim_v && V.size(-1) == d.len_kv, "V must be V^T, [..., Dv, Lk]");
+  TORCH_CHECK(Q.stride(-1) == 1 && O.stride(-1) == 1 && K.stride(-1) == 1 && V.stride(-2) == 1,
+              "rows of Q, K, O must be contiguous and V^T must be a transposed view of a value stored [..., Lk, Dv]");
+  TORCH_CHECK(LSE.scalar_type() == at::kFloat && LSE.is_contiguous() && LSE.numel() == (int64_t)d.batch * d.heads * d.len_q,
+              "LSE must be a contiguous fp32 tensor with batch*heads*Lq elements");
+  d.q_stride_b = lq.stride_b;
+  d.q_stride_h = lq.stride_h;
+  d.q_stride_l = Q.stride(-2);
+  d.k_stride_b = lk.stride_b;
+  d.k_stride_h = lk.stride_h;
+  d.k_stride_l = K.stride(-2);
+  d.k_stride_d = 1;
+  d.v_stride_b = lv.stride_b;
+  d.v_stride_h = lv.stride_h;
+  d.v_stride_l = V.stride(-1);
+  d.v_stride_d = 1;
+  d.o_stride_b = lo.stride_b;
+  d.o_stride_h = lo.stride_h;
+  d.o_stride_l = O.stride(-2);
+  d.softmax_scale = (float)softmax_scale;
+  d.causal = causal ? 1 : 0;
+  const c10::cuda::CUDAGuard guard(Q.device());
+  check_earlier_launches();
+  const uint64_t need = tf_attn_bwd_workspace_bytes(&d);
+  at::Tensor ws = at::empty({(int64_t)((need + 3) / 4)}, Q.options().dtype(at::kFloat));
+  check_status(tf_attn_bwd(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), dO.data_ptr(), LSE.data_ptr<float>(),
+                           dQ.data_ptr(), dK.data_ptr(), dV.data_ptr(), &d, ws.data_ptr(), (uint64_t)ws.numel() * 4,
+                           at::cuda::getCurrentCUDAStream().stream()));
+}
+
 TfDecodeDesc decode_desc(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, int64_t kv_chunk,
                          int64_t num_splits, double softmax_scale) {
   TORCH_CHECK(Q.is_cuda() && K.is_cuda() && V.is_cuda(), "Q, K and V must be CUDA tensors");
@@ -361,6 +423,11 @@ TF_REGISTER_OP(flash_attention_lse,
                "flash_attention_lse(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, Tensor(b!) LSE, "
                "int tile_length_q, int tile_length_kv, float softmax_scale, bool causal) -> ()",
                &flash_attention_lse);
+
+TF_REGISTER_OP(flash_attention_bwd,
+               "flash_attention_bwd(Tensor Q, Tensor K, Tensor V, Tensor O, Tensor dO, Tensor LSE, "
+               "Tensor(a!) dQ, Tensor(b!) dK, Tensor(c!) dV, float softmax_scale, bool causal) -> ()",
+               &flash_attention_bwd);
 
 TF_REGISTER_OP(flash_decoding,
                "flash_decoding(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, Tensor(b!) LSE, "

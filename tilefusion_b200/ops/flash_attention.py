@@ -21,7 +21,7 @@ import torch
 
 from .._torch_ops import ensure_loaded
 
-__all__ = ["FlashAttention", "flash_attention"]
+__all__ = ["FlashAttention", "flash_attention", "flash_attention_bwd", "flash_attention_autograd"]
 
 
 class FlashAttention:
@@ -114,3 +114,62 @@ def flash_attention(
         tile_length_q, tile_length_kv, tile_hidden_qk, tile_hidden_v, softmax_scale, causal
     )
     return attn(query, key, value)
+
+
+def flash_attention_bwd(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    output: torch.Tensor,
+    grad_output: torch.Tensor,
+    lse: torch.Tensor,
+    softmax_scale: float,
+    causal: bool,
+):
+    """Gradients of :func:`flash_attention` (TileFusion has no backward pass; this
+    extends its operator with one, in the same argument convention).
+
+    ``query [..., Lq, D]``, ``key [..., D, Lk]``, ``value [..., Lk, Dv]``, ``output`` and
+    ``grad_output [..., Lq, Dv]``, ``lse [..., Lq]`` as returned by
+    ``FlashAttention(...)(q, k, v, return_lse=True)``.  Returns ``(dq, dk, dv)`` shaped
+    like ``query``, ``key`` and ``value``.  ``D == Dv`` in {64, 128}.
+    """
+    ensure_loaded()
+    q = query if query.stride(-1) == 1 else query.contiguous()
+    k_op = key.transpose(-1, -2)                       # [..., Lk, D]
+    if k_op.stride(-1) != 1:
+        k_op = k_op.contiguous()
+    v_nat = value if value.stride(-1) == 1 else value.contiguous()
+    o = output if output.stride(-1) == 1 else output.contiguous()
+    d_o = grad_output
+    if d_o.stride() != o.stride():
+        d_o = torch.empty_strided(o.shape, o.stride(), dtype=o.dtype, device=o.device).copy_(grad_output)
+    dq = torch.empty_strided(q.shape, q.stride(), dtype=q.dtype, device=q.device)
+    dk = torch.empty_strided(k_op.shape, k_op.stride(), dtype=q.dtype, device=q.device)
+    dv = torch.empty_strided(v_nat.shape, v_nat.stride(), dtype=q.dtype, device=q.device)
+    torch.ops.tilefusion.flash_attention_bwd(
+        q, k_op, v_nat.transpose(-1, -2), o, d_o, lse.contiguous(),
+        dq, dk, dv.transpose(-1, -2), softmax_scale, causal,
+    )
+    return dq, dk.transpose(-1, -2), dv
+
+
+class _FlashAttentionFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, query, key, value, softmax_scale, causal):
+        out, lse = FlashAttention(0, 0, 0, 0, softmax_scale, causal)(query, key, value, return_lse=True)
+        ctx.save_for_backward(query, key, value, out, lse)
+        ctx.softmax_scale, ctx.causal = softmax_scale, causal
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        query, key, value, out, lse = ctx.saved_tensors
+        dq, dk, dv = flash_attention_bwd(query, key, value, out, grad_output, lse, ctx.softmax_scale, ctx.causal)
+        return dq, dk, dv, None, None
+
+
+def flash_attention_autograd(query, key, value, softmax_scale: float, causal: bool = False) -> torch.Tensor:
+    """:func:`flash_attention` as a differentiable function (``key`` as ``[..., D, Lk]``):
+    the forward keeps the log-sum-exp rows and ``.backward()`` runs the CUDA backward."""
+    return _FlashAttentionFunction.apply(query, key, value, softmax_scale, causal)
