@@ -688,6 +688,11 @@ int launch_sharded_decode(const void* q, const void* k, const void* v, void* o, 
                           const TfDecodeDesc* d, const ShardStep& st, cudaStream_t stream) {
   TfDecodePlan plan;
   if (int rc = plan_and_check_decode(q, k, v, st.workspace, st.workspace_bytes, d, &plan)) return rc;
+  // (the item flags of the fused tail follow the partial rows in the workspace)
+  const uint64_t ws_need = plan.workspace_bytes + (uint64_t)d->batch * d->heads * plan.num_splits * sizeof(unsigned);
+  if (st.workspace_bytes < ws_need)
+    return fail(TF_ERR_WORKSPACE, "workspace holds %llu bytes but %llu are needed", (unsigned long long)st.workspace_bytes,
+                (unsigned long long)ws_need);
   const bool p2p = st.peer_table != nullptr;
   if (p2p && o == nullptr) return fail(TF_ERR_BAD_ARG, "o is null");
   if (int rc = ensure_device_ready()) return rc;
@@ -701,7 +706,7 @@ int launch_sharded_decode(const void* q, const void* k, const void* v, void* o, 
   if (!is_grouped(d)) {
     // one launch: split, merge, exchange, final combine
     DecodeFuseArgs f{};
-    f.row_arrivals = st.row_arrivals;
+    f.item_flags = reinterpret_cast<unsigned*>(static_cast<char*>(st.workspace) + plan.workspace_bytes);
     f.rows_done = st.rows_done;
     f.rows = rows;
     f.peer_bases = st.peer_table;

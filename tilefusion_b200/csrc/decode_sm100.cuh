@@ -26,18 +26,21 @@
 // all-gather).
 //
 // KV sharded across GPUs: with DecodeFuseArgs set, decode_split_kernel carries
-// the exchange itself.  A tenth warp (the "merger") of every CTA counts the
-// CTA's finished items into a per-(b, h) arrival counter; the merger that
-// counts a row's last split merges that row's partials and stores the merged
-// (O, m, l) row straight into the gather area of every rank through
-// peer-mapped pointers; the one that completes the rank's last row raises this
-// rank's flag on every peer; and the CTAs then wait (bounded) for all ranks'
-// flags and write the final O / LSE for their rows -- split, all-gather and
-// combine in one launch.  The consumers only signal "item written" on an
-// mbarrier and go on streaming: the device-scope fence and the atomic round
-// trip an arrival costs (tens of microseconds per item when paid by the
-// consumers of a saturated SM) are the merger's, and it batches them.  Only
-// plain peer stores and system-scope release/acquire touch peer memory.
+// the exchange itself.  A tenth warp (the "merger") of every CTA publishes the
+// CTA's finished items: one flag word per item receives the step number, after
+// a device-scope fence that covers every item signalled so far.  The CTA that
+// runs the LAST split of a (b, h) owns that row's merge: its merger polls the
+// row's flag words, merges the partials once all carry the step number, and
+// stores the merged (O, m, l) row straight into the gather area of every rank
+// through peer-mapped pointers; the merger that completes the rank's last row
+// raises this rank's flag on every peer; and the CTAs then wait (bounded) for
+// all ranks' flags and write the final O / LSE for their rows -- split,
+// all-gather and combine in one launch.  The consumers only signal "item
+// written" on an mbarrier and go on streaming.  (Counting arrivals per row with
+// atomics instead costs tens of microseconds per item: the CTAs of a persistent
+// grid work on the same one or two rows at any moment, so all of them hit the
+// same counter at once.)  Only plain peer stores and system-scope
+// release/acquire touch peer memory.
 #pragma once
 
 #include <type_traits>
@@ -55,7 +58,8 @@ constexpr int kDecMaxChunk = 1024;        // keys; bounds the score buffers
 // Fused merge / exchange / final combine of a KV-sharded decode step (all
 // fields zero: the split pass only writes its partial rows).
 struct DecodeFuseArgs {
-  unsigned* row_arrivals;     // [rows], zero between steps: splits of a (b,h) finished so far
+  unsigned* item_flags;       // [items]: item i's partial row is in global memory once its word == step
+                              // (words only grow from step to step; null = no fused tail)
   unsigned* rows_done;        // one word, zero between steps: merged rows of this rank
   int rows;                   // batch * heads
   // Destination of the merged rows: every peer's gather area (peer_bases[p] +
@@ -115,7 +119,9 @@ struct DecodeSmem {
   static constexpr int kBytes = kOffAbort + 16 + 128;                   // + alignment slack
 };
 
-enum DecodeWaitCode { kWaitDecEmpty = 201, kWaitDecFullK = 202, kWaitDecFullV = 203, kWaitDecDone = 204, kWaitDecFree = 205 };
+enum DecodeWaitCode {
+  kWaitDecEmpty = 201, kWaitDecFullK = 202, kWaitDecFullV = 203, kWaitDecDone = 204, kWaitDecFree = 205, kWaitDecRow = 206
+};
 enum CombineWaitCode { kWaitGatherFlag = 401 };
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
@@ -172,7 +178,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
   const uint32_t bar_empty = smem_base + S::kOffBar + kStages * 8;
   const uint32_t bar_done = smem_base + S::kOffDone;                      // [kDecDoneSlots] item n is in global memory
   const uint32_t bar_free = smem_base + S::kOffDone + kDecDoneSlots * 8;  // [kDecDoneSlots] the merger has taken item n
-  const bool fused = args.fuse.row_arrivals != nullptr;
+  const bool fused = args.fuse.item_flags != nullptr;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -198,86 +204,129 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
 
   if (warp == kDecConsumerThreads / 32 + 1) {
     // -------------------------------------------------------------- merger --
-    // Counts this CTA's finished items into the per-row arrival counters, merges
-    // the rows it completes and sends them out.  Items are taken in batches: one
-    // device-scope fence covers every item the consumers have signalled so far.
+    // Publishes this CTA's finished items (flag word = step), merges the rows
+    // whose last split this CTA runs, and sends them out.
     if (fused) {
       const DecodeFuseArgs& f = args.fuse;
       constexpr int kVec = D / 32;                     // output dims per lane
+      constexpr int kMaxPending = 8;
+      int pending[kMaxPending];                        // rows this CTA has to merge, oldest first
+      int n_pending = 0;
+      unsigned long long pending_since = 0;
       bool ok = true;
-      uint32_t n = 0;                                  // items of this CTA taken so far
-      for (int item = blockIdx.x; ok && item < args.items;) {
-        // the next item, then every further one that is already written
-        ok = mbar_wait_warp(bar_done + (n % kDecDoneSlots) * 8, (n / kDecDoneSlots) & 1, abort_flag, kWaitDecDone);
-        if (!ok) break;
+      uint32_t n = 0;                                  // items of this CTA published so far
+      int item = blockIdx.x;
+
+      // Publishes every item the consumers have signalled (at least one if `must`).
+      auto publish = [&](bool must) -> bool {
+        if (item >= args.items || n_pending >= kMaxPending) return true;
+        if (must) {
+          if (!mbar_wait_warp(bar_done + (n % kDecDoneSlots) * 8, (n / kDecDoneSlots) & 1, abort_flag, kWaitDecDone))
+            return false;
+        } else if (!__all_sync(0xffffffffu, mbar_try_wait(bar_done + (n % kDecDoneSlots) * 8, (n / kDecDoneSlots) & 1))) {
+          return true;
+        }
         int batch = 1;
-        while (batch < kDecDoneSlots && item + batch * (int)gridDim.x < args.items &&
+        while (batch < kDecDoneSlots && item + batch * (int)gridDim.x < args.items && n_pending + batch < kMaxPending &&
                __all_sync(0xffffffffu, mbar_try_wait(bar_done + ((n + batch) % kDecDoneSlots) * 8,
                                                      ((n + batch) / kDecDoneSlots) & 1)))
           ++batch;
         if (lane == 0)
           for (int i = 0; i < batch; ++i) mbar_arrive(bar_free + ((n + i) % kDecDoneSlots) * 8);
-        __threadfence();                               // the consumers' partial rows, before they are counted
+        __threadfence();                               // the consumers' partial rows, before their flags
         for (int i = 0; i < batch; ++i, item += gridDim.x) {
+          if (lane == 0) *reinterpret_cast<volatile unsigned*>(f.item_flags + item) = f.step;
           const int bh = item / args.num_splits;
-          unsigned last = 0;
-          if (lane == 0) last = (atomicAdd(f.row_arrivals + bh, 1u) == (unsigned)args.num_splits - 1u) ? 1u : 0u;
-          if (__shfl_sync(0xffffffffu, last, 0) == 0) continue;
-          // ---- this arrival completed row bh: merge its splits (written by other SMs: read past L1) ----
-          __threadfence();
-          const float* ml = args.part_ml + (long long)bh * args.num_splits * 2;
-          const float* po = args.part_o + (long long)bh * args.num_splits * D + lane * kVec;
-          float m = -INFINITY;
-          for (int p = lane; p < args.num_splits; p += 32) m = fmaxf(m, __ldcg(ml + 2 * p));
-#pragma unroll
-          for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-          float acc_o[kVec], l = 0.f;
-#pragma unroll
-          for (int e = 0; e < kVec; ++e) acc_o[e] = 0.f;
-#pragma unroll 4
-          for (int p = 0; p < args.num_splits; ++p) {
-            const float2 mlp = __ldcg(reinterpret_cast<const float2*>(ml + 2 * p));
-            const float w = (mlp.x == -INFINITY) ? 0.f : fast_exp2(mlp.x - m);
-            l = fmaf(mlp.y, w, l);
-            if constexpr (kVec == 4) {
-              const float4 x = __ldcg(reinterpret_cast<const float4*>(po + (long long)p * D));
-              acc_o[0] = fmaf(x.x, w, acc_o[0]);
-              acc_o[1] = fmaf(x.y, w, acc_o[1]);
-              acc_o[2] = fmaf(x.z, w, acc_o[2]);
-              acc_o[3] = fmaf(x.w, w, acc_o[3]);
-            } else {
-              const float2 x = __ldcg(reinterpret_cast<const float2*>(po + (long long)p * D));
-              acc_o[0] = fmaf(x.x, w, acc_o[0]);
-              acc_o[1] = fmaf(x.y, w, acc_o[1]);
-            }
-          }
-          const int n_dst = f.peer_bases != nullptr ? f.n_peers : 1;
-          for (int p = 0; p < n_dst; ++p) {
-            float* base = f.peer_bases != nullptr ? f.peer_bases[p] + f.slot_offset : f.out_slot;
-            float* dst = base + (long long)bh * D + lane * kVec;
-            if constexpr (kVec == 4) {
-              *reinterpret_cast<float4*>(dst) = make_float4(acc_o[0], acc_o[1], acc_o[2], acc_o[3]);
-            } else {
-              *reinterpret_cast<float2*>(dst) = make_float2(acc_o[0], acc_o[1]);
-            }
-            if (lane == 0)
-              *reinterpret_cast<float2*>(base + (long long)f.rows * D + (long long)bh * 2) = make_float2(m, l);
-          }
-          __threadfence_system();                      // my peer stores are performed before the row is counted
-          __syncwarp();
-          if (lane == 0) {
-            f.row_arrivals[bh] = 0;                    // re-armed for the next step
-            if (atomicAdd(f.rows_done, 1u) == (unsigned)f.rows - 1u) {
-              // the rank's last row: re-arm the counter and raise this rank's flag everywhere
-              *f.rows_done = 0;
-              __threadfence_system();
-              if (f.peer_bases != nullptr)
-                for (int p = 0; p < f.n_peers; ++p)
-                  st_release_sys(reinterpret_cast<unsigned*>(f.peer_bases[p] + f.flag_offset) + f.my_rank, f.step);
-            }
+          if (item - bh * args.num_splits == args.num_splits - 1) {      // the row's last split: the merge is ours
+            if (n_pending == 0) pending_since = global_timer_ns();
+            pending[n_pending++] = bh;
           }
         }
         n += batch;
+        return true;
+      };
+
+      while (ok && (item < args.items || n_pending > 0)) {
+        ok = publish(n_pending == 0);
+        if (!ok || n_pending == 0) continue;
+        // ---- is the oldest pending row complete? (flags written by other SMs: read past L1) ----
+        const int bh = pending[0];
+        const unsigned* flags = f.item_flags + (long long)bh * args.num_splits;
+        bool all_in = true;
+        for (int p = lane; p < args.num_splits; p += 32) all_in = all_in && (__ldcg(flags + p) == f.step);
+        if (!__all_sync(0xffffffffu, all_in)) {
+          if (global_timer_ns() - pending_since > wait_limit_ns()) {
+            if (lane == 0) {
+              *abort_flag = kWaitDecRow;
+              report_wait_timeout(kWaitDecRow);
+            }
+            ok = false;
+          }
+          if (n_pending == kMaxPending || item >= args.items) __nanosleep(200);
+          continue;
+        }
+        __threadfence();                               // (acquire side: the partial rows behind the flags)
+        // ---- merge the splits of row bh ----
+        const float* ml = args.part_ml + (long long)bh * args.num_splits * 2;
+        const float* po = args.part_o + (long long)bh * args.num_splits * D + lane * kVec;
+        float m = -INFINITY;
+        for (int p = lane; p < args.num_splits; p += 32) m = fmaxf(m, __ldcg(ml + 2 * p));
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        float acc_o[kVec], l = 0.f;
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) acc_o[e] = 0.f;
+        for (int p0 = 0; p0 < args.num_splits; p0 += 8) {
+          // eight splits at a time: their loads are in flight together
+          float2 mlp[8];
+          float x[8][kVec];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int p = min(p0 + u, args.num_splits - 1);
+            mlp[u] = __ldcg(reinterpret_cast<const float2*>(ml + 2 * p));
+            if constexpr (kVec == 4) {
+              const float4 t = __ldcg(reinterpret_cast<const float4*>(po + (long long)p * D));
+              x[u][0] = t.x; x[u][1] = t.y; x[u][2] = t.z; x[u][3] = t.w;
+            } else {
+              const float2 t = __ldcg(reinterpret_cast<const float2*>(po + (long long)p * D));
+              x[u][0] = t.x; x[u][1] = t.y;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const float w = (p0 + u >= args.num_splits || mlp[u].x == -INFINITY) ? 0.f : fast_exp2(mlp[u].x - m);
+            l = fmaf(mlp[u].y, w, l);
+#pragma unroll
+            for (int e = 0; e < kVec; ++e) acc_o[e] = fmaf(x[u][e], w, acc_o[e]);
+          }
+          if ((p0 & 63) == 56) ok = ok && publish(false);      // keep the consumers' slots moving during a long merge
+        }
+        const int n_dst = f.peer_bases != nullptr ? f.n_peers : 1;
+        for (int p = 0; p < n_dst; ++p) {
+          float* base = f.peer_bases != nullptr ? f.peer_bases[p] + f.slot_offset : f.out_slot;
+          float* dst = base + (long long)bh * D + lane * kVec;
+          if constexpr (kVec == 4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(acc_o[0], acc_o[1], acc_o[2], acc_o[3]);
+          } else {
+            *reinterpret_cast<float2*>(dst) = make_float2(acc_o[0], acc_o[1]);
+          }
+          if (lane == 0)
+            *reinterpret_cast<float2*>(base + (long long)f.rows * D + (long long)bh * 2) = make_float2(m, l);
+        }
+        __threadfence_system();                        // my peer stores are performed before the row is counted
+        __syncwarp();
+        if (lane == 0 && atomicAdd(f.rows_done, 1u) == (unsigned)f.rows - 1u) {
+          // the rank's last row: re-arm the counter and raise this rank's flag everywhere
+          *f.rows_done = 0;
+          __threadfence_system();
+          if (f.peer_bases != nullptr)
+            for (int p = 0; p < f.n_peers; ++p)
+              st_release_sys(reinterpret_cast<unsigned*>(f.peer_bases[p] + f.flag_offset) + f.my_rank, f.step);
+        }
+        // pop the row
+        for (int i = 1; i < n_pending; ++i) pending[i - 1] = pending[i];
+        --n_pending;
+        pending_since = global_timer_ns();
       }
     }
   } else if (warp == kDecConsumerThreads / 32) {

@@ -20,9 +20,9 @@ int ensure_device_ready();
 
 // One step of a KV-sharded decode.  All buffers belong to the TfShardCtx.
 struct ShardStep {
-  void* workspace;             // split-KV partial rows of this rank
-  uint64_t workspace_bytes;
-  unsigned* row_arrivals;      // [batch*heads], zero between steps
+  void* workspace;             // split-KV partial rows of this rank, then one flag word per (b, h, split):
+  uint64_t workspace_bytes;    //   plan.workspace_bytes + batch*heads*num_splits*4 bytes; flag words start
+                               //   at zero and hold the number of the last step that wrote their row
   unsigned* rows_done;         // one word, zero between steps
   float* const* peer_table;    // device array [n_ranks] of gather-buffer bases as mapped into this
                                // process; null = merged rows go to this rank's slot only (NCCL transport)

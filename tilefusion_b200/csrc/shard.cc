@@ -114,7 +114,8 @@ struct TfShardCtx {
   void* peer_mapping[kMaxRanks] = {}; // IPC mappings opened by this process (to close)
   void* workspace = nullptr;          // split-KV partial rows; grows on demand
   uint64_t workspace_bytes = 0;
-  unsigned* counters = nullptr;       // [rows] arrivals per (b,h), then the merged-row count
+  int splits_of_workspace = 0;        // split count the flag words in the workspace were laid out for
+  unsigned* counters = nullptr;       // the merged-row count of the step in flight
   unsigned step = 0;
   std::string note;                   // why p2p was not used, if it was asked for
 };
@@ -282,8 +283,8 @@ int tf_shard_create(int32_t rank, int32_t world, const void* nccl_id, int32_t tr
   const size_t buffer_bytes = (size_t)(c->flag_offset + kFlagWords) * sizeof(float);
   TF_CREATE_CUDA(cudaMalloc(&c->buffer, buffer_bytes));
   TF_CREATE_CUDA(cudaMemset(c->buffer, 0, buffer_bytes));
-  TF_CREATE_CUDA(cudaMalloc(&c->counters, (size_t)(rows + 1) * sizeof(unsigned)));
-  TF_CREATE_CUDA(cudaMemset(c->counters, 0, (size_t)(rows + 1) * sizeof(unsigned)));
+  TF_CREATE_CUDA(cudaMalloc(&c->counters, 64));
+  TF_CREATE_CUDA(cudaMemset(c->counters, 0, 64));
   // flags and counters are zero on this rank before any peer can learn the buffer's address
   TF_CREATE_CUDA(cudaDeviceSynchronize());
 
@@ -347,24 +348,30 @@ int tf_decode_sharded(TfShardCtx* c, const void* q, const void* k_local, const v
   TfDecodePlan plan;
   if (int rc = tf_decode_plan(desc, &plan)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (plan.workspace_bytes > c->workspace_bytes) {
-    // first call, or a longer shard than any before: the only allocation a step can make
-    if (c->workspace != nullptr) {
+  // partial rows, then one flag word per (b, h, split) for the fused tail
+  const uint64_t ws_need = plan.workspace_bytes + (uint64_t)c->batch * c->heads * plan.num_splits * sizeof(unsigned);
+  if (ws_need > c->workspace_bytes || plan.num_splits != c->splits_of_workspace) {
+    // first call, or a differently split shard than the last one: the only allocation a
+    // step can make.  The flag words must start below every step number still to come.
+    if (c->workspace != nullptr && ws_need > c->workspace_bytes) {
       TF_SHARD_CUDA(cudaStreamSynchronize(s));
       TF_SHARD_CUDA(cudaFree(c->workspace));
       c->workspace = nullptr;
       c->workspace_bytes = 0;
     }
-    TF_SHARD_CUDA(cudaMalloc(&c->workspace, plan.workspace_bytes));
-    c->workspace_bytes = plan.workspace_bytes;
+    if (c->workspace == nullptr) {
+      TF_SHARD_CUDA(cudaMalloc(&c->workspace, ws_need));
+      c->workspace_bytes = ws_need;
+    }
+    TF_SHARD_CUDA(cudaMemsetAsync(c->workspace, 0, c->workspace_bytes, s));
+    c->splits_of_workspace = plan.num_splits;
   }
   c->step += 1;
   const long long rows = (long long)c->batch * c->heads;
   tfb::ShardStep st;
   st.workspace = c->workspace;
   st.workspace_bytes = c->workspace_bytes;
-  st.row_arrivals = c->counters;
-  st.rows_done = c->counters + rows;
+  st.rows_done = c->counters;
   st.peer_table = c->transport == TF_TRANSPORT_P2P ? c->peer_table_dev : nullptr;
   st.local_base = c->buffer;
   st.n_ranks = c->world;
