@@ -24,10 +24,15 @@ pytestmark = pytest.mark.gpu
 
 def _check_grad(name, got, ref, dtype):
     assert torch.isfinite(got.float()).all(), f"{name}: kernel left NaN/Inf"
+    assert orc.max_abs(got.cpu(), ref) <= 2e-2 * max(1.0, ref.abs().max().item()), name
+    if ref.float().pow(2).mean().sqrt().item() < 1e-4:
+        # a gradient that is exactly zero (one key: softmax is constant) has no relative error;
+        # what the kernel returns comes from the rounding of O and must stay at that level
+        assert got.float().abs().max().item() <= 2e-3, name
+        return
     bound = 2e-3 if dtype == torch.float16 else 2.0 * orc.rel_l2_bound(ref, dtype)
     rel = orc.rel_l2(got.cpu(), ref)
     assert rel <= bound, f"{name}: rel-L2 {rel:.3e} > {bound:.3e}"
-    assert orc.max_abs(got.cpu(), ref) <= 2e-2 * max(1.0, ref.abs().max().item()), name
 
 
 def _run(b, h, lq, lk, d, causal, dtype, seed=3, sigma=1.0):

@@ -416,10 +416,11 @@ def test_unsupported_inputs_report_errors():
     from cabi_helpers import attn_fwd
     from tilefusion_b200._cabi import TileFusionError, TF_ERR_UNSUPPORTED
 
-    q = torch.zeros(1, 1, 16, 96, dtype=torch.float16, device="cuda")
-    with pytest.raises(TileFusionError) as e:
-        attn_fwd(q, q, q, 1.0)
-    assert e.value.code == TF_ERR_UNSUPPORTED and "head_dim" in str(e.value)
+    for width in (100, 264):            # not a multiple of 8; wider than the widest kernel
+        q = torch.zeros(1, 1, 16, width, dtype=torch.float16, device="cuda")
+        with pytest.raises(TileFusionError) as e:
+            attn_fwd(q, q, q, 1.0)
+        assert e.value.code == TF_ERR_UNSUPPORTED and "head_dim" in str(e.value)
 
 
 def test_host_pipeline_matches_direct_calls():
