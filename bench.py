@@ -81,6 +81,8 @@ WORKLOADS["decode_gqa"] = dict(WORKLOADS["decode_c3"], B=64, Hkv=8)
 WORKLOADS["prefill_profile"] = dict(WORKLOADS["prefill_c2"], B=4)
 WORKLOADS["decode_profile"] = dict(WORKLOADS["decode_c3"], B=4)
 WORKLOADS["decode_gqa_profile"] = dict(WORKLOADS["decode_gqa"], B=16)
+# A 1-GiB case of the sharded decode step (split, merge, exchange and combine in one launch) for captures.
+WORKLOADS["decode_c4_profile"] = dict(WORKLOADS["decode_c4"], L=16384)
 # One rank's share of decode_c4 when the KV length is sharded over 8 GPUs.
 WORKLOADS["decode_c4_shard8"] = dict(WORKLOADS["decode_c4"], L=131072 // 8, scaling="weak")
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)   # earlier measurement on this pool
@@ -341,7 +343,7 @@ MAX_REPEATS = 25
 IDLE_GAP_S = 0.02
 
 
-def time_steps(fn, steps, warmup, device, world, max_repeats=MAX_REPEATS):
+def time_steps(fn, steps, warmup, device, world, max_repeats=None):
     """W warm-up steps, then regions of exactly `steps` steps, each bracketed by
     barrier + synchronize on both sides and timed with CUDA events on the current
     stream, max over ranks.  Returns (median seconds per region, info)."""
@@ -353,6 +355,7 @@ def time_steps(fn, steps, warmup, device, world, max_repeats=MAX_REPEATS):
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    max_repeats = MAX_REPEATS if max_repeats is None else max_repeats
     for _ in range(warmup):
         fn()
     sampler = ClockSampler(device.index if device.index is not None else 0)
@@ -740,6 +743,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.profile:
         args.no_secondary = True
+        global MAX_REPEATS
+        MAX_REPEATS = 1          # one timed region: a capture should see few launches
     w = WORKLOADS[args.workload]
 
     if args.impl == "reference":
