@@ -548,6 +548,55 @@ def run_prefill(args, w, name, device, rank, world, causal=False, steps=None, wa
     return res
 
 
+def run_backward(args, w, device, rank, world, steps, warmup):
+    """Backward of the prefill workload `w` (dQ, dK, dV through tf_attn_bwd: three launches per
+    step); FLOPs counted as 2.5 x the forward (five tile products against two)."""
+    import ctypes as C
+
+    from tilefusion_b200 import _cabi
+
+    lib = _cabi.lib()
+    scale = 1.0 / math.sqrt(w["D"])
+    stream = torch.cuda.current_stream(device).cuda_stream
+    q, k, v = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), device)
+    g = torch.Generator(device=device).manual_seed(w["seed"] + 77 + 1000 * rank)
+    d_o = (torch.randn(q.shape, generator=g, device=device) * w["sigma"]).to(q.dtype)
+    o = torch.empty_like(q)
+    lse = torch.empty(w["B"], w["H"], w["L"], dtype=torch.float32, device=device)
+    d = attn_desc_for(q, k, v, o, w["dtype"], scale, False)
+    _cabi.check(lib.tf_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), C.byref(d), stream))
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ws = torch.empty(lib.tf_attn_bwd_workspace_bytes(C.byref(d)) // 4, dtype=torch.float32, device=device)
+    ptrs = [t.data_ptr() for t in (q, k, v, o, d_o, lse, dq, dk, dv, ws)]
+
+    def step():
+        rc = lib.tf_attn_bwd(*ptrs[:9], C.byref(d), ptrs[9], ws.numel() * 4, stream)
+        if rc != 0:
+            _cabi.check(rc)
+
+    secs, info = time_steps(step, steps, warmup, device, world)
+    flops = 2.5 * prefill_flops(w["B"] * world, w["H"], w["L"], w["L"], w["D"])
+    pk = peaks()
+    ach = flops / world * steps / secs / 1e12
+    res = dict(value=flops * steps / secs / 1e12, unit="TFLOP/s", secs=secs, info=info, launches=3 * steps,
+               roofline={"bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": ach / pk["bf16_tflops"], "traffic": None, "traffic_source": "not captured",
+                         "kernel": "attn_bwd_kernel (dK/dV and dQ) + attn_bwd_delta_kernel",
+                         "flops_counted": "10*B*H*Lq*Lk*D (2.5 x forward); the kernels execute 14 (S and dP are "
+                                          "recomputed by the dQ kernel)",
+                         "peak_source": pk["source"] + " (burst cuBLAS bf16)"})
+    # parity of one head: gradient of the fp32 expression by torch.autograd on the device
+    qh, kh, vh = (t[0, 0].float().detach().requires_grad_(True) for t in (q, k, v))
+    ref, _ = gpu_attention_fp32(qh, kh, vh, scale, False)
+    ref.backward(d_o[0, 0].float())
+    from oracle import attention_oracle as orc
+
+    res["parity"] = {name: orc.rel_l2(got[0, 0].cpu(), want.grad.cpu())
+                     for name, got, want in (("dq_rel_l2", dq, qh), ("dk_rel_l2", dk, kh), ("dv_rel_l2", dv, vh))}
+    res["parity"]["checked"] = "one (batch, head): gradients of softmax(QK^T s)V in fp32 by torch.autograd on the device"
+    return res
+
+
 def sharded_parity(q, k_local, v_local, o, lse, scale, device, world):
     """Parity of a KV-sharded decode step without ever holding the whole sequence in
     one place: every rank evaluates the fp32 expression on its own shard for two
@@ -808,6 +857,9 @@ def main():
         cz = run_prefill(args, w, "prefill_c2", device, rank, world, causal=True, with_e2e=False)
         line["causal"] = secondary_object("prefill_c2+causal", cz, args.steps, world)
         line["causal"]["flops_counted"] = "unmasked (query, key) pairs only"
+        torch.cuda.empty_cache()
+        bw = run_backward(args, w, device, rank, world, max(5, min(args.steps, 20)), 3)
+        line["backward"] = secondary_object("prefill_c2 backward", bw, max(5, min(args.steps, 20)), world)
 
     if rank == 0 and world == 1 and not args.no_secondary:
         line["cpu_baseline"] = cpu_baseline(w)
