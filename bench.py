@@ -85,6 +85,9 @@ WORKLOADS["decode_gqa_profile"] = dict(WORKLOADS["decode_gqa"], B=16)
 WORKLOADS["decode_c4_profile"] = dict(WORKLOADS["decode_c4"], L=16384)
 # One rank's share of decode_c4 when the KV length is sharded over 8 GPUs.
 WORKLOADS["decode_c4_shard8"] = dict(WORKLOADS["decode_c4"], L=131072 // 8, scaling="weak")
+# fused_two_gemms, D = (A B^T) C^T: the reference's own test case and one GEMM-sized case.
+WORKLOADS["two_gemms_ref"] = dict(kind="two_gemms", dtype="fp16", M=256, N=128, K=64, P=64, scaling="weak")
+WORKLOADS["two_gemms"] = dict(kind="two_gemms", dtype="fp16", M=262144, N=8192, K=128, P=128, scaling="weak")
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)   # earlier measurement on this pool
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel
@@ -323,10 +326,15 @@ def run_reference_arm(args, w, name):
 
 
 def metric_name(w):
-    return "prefill_tflops" if w["kind"] == "prefill" else "decode_hbm_gbs"
+    return {"prefill": "prefill_tflops", "decode": "decode_hbm_gbs", "two_gemms": "fused_two_gemms_tflops"}[w["kind"]]
 
 
 def workload_config(w, name, n_gpus, causal=False):
+    if w["kind"] == "two_gemms":
+        return {"workload": name, "m": w["M"], "n": w["N"], "k": w["K"], "p": w["P"],
+                "l2": ("A and D larger than L2 (64 MB each); no flush between steps" if w["M"] * w["K"] * 2 >= 64 << 20
+                       else "plumbing case: everything is L2-resident, launch-latency bound"),
+                "timing": "median of repeated regions of exactly `steps` steps, idle gap between regions"}
     return {"workload": name + ("+causal" if causal else ""), "batch_per_step": w["B"] * (n_gpus if w["scaling"] == "weak" else 1),
             "heads": w["H"], "len_q": w["L"] if w["kind"] == "prefill" else 1, "len_kv": w["L"],
             "head_dim": w["D"], "causal": bool(causal), "softmax_scale": "1/sqrt(D)",
@@ -760,6 +768,45 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
     return res
 
 
+def run_two_gemms(args, w, device, rank, world):
+    """fused_two_gemms through tf_fused_two_gemms: A [M,K], B [N,K], C [P,N] -> D [M,P]."""
+    from tilefusion_b200 import _cabi
+
+    lib = _cabi.lib()
+    dt = torch_dtype(w["dtype"])
+    g = torch.Generator(device=device).manual_seed(5 + rank)
+    a = (torch.randn(w["M"], w["K"], generator=g, device=device)).to(dt)
+    b = (torch.randn(w["N"], w["K"], generator=g, device=device) * 0.125).to(dt)
+    c = (torch.randn(w["P"], w["N"], generator=g, device=device) * 0.125).to(dt)
+    d = torch.empty(w["M"], w["P"], dtype=dt, device=device)
+    stream = torch.cuda.current_stream(device).cuda_stream
+    code = _cabi.TF_F16 if w["dtype"] == "fp16" else _cabi.TF_BF16
+    argv = (a.data_ptr(), b.data_ptr(), c.data_ptr(), d.data_ptr(), w["M"], w["N"], w["K"], w["P"], code,
+            a.stride(0), b.stride(0), c.stride(0), d.stride(0), stream)
+
+    def step():
+        rc = lib.tf_fused_two_gemms(*argv)
+        if rc != 0:
+            _cabi.check(rc)
+
+    secs, info = time_steps(step, args.steps, args.warmup, device, world)
+    flops = 2.0 * w["M"] * w["N"] * (w["K"] + w["P"])
+    pk = peaks()
+    ach = flops * args.steps / secs / 1e12
+    from oracle import attention_oracle as orc
+
+    rows = slice(0, min(w["M"], 256))
+    ref = ((a[rows].float() @ b.float().t()).to(dt).float() @ c.float().t()).cpu()
+    res = dict(value=ach * world, unit="TFLOP/s", secs=secs, info=info, launches=args.steps,
+               roofline={"bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": ach / pk["bf16_tflops"], "traffic": None, "traffic_source": "not captured",
+                         "kernel": "attn_fwd_kernel<T, D, true> (one CTA per 128 rows of A: M/128 CTAs)",
+                         "peak_source": pk["source"] + " (burst cuBLAS bf16)"},
+               parity={"rel_l2": orc.rel_l2(d[rows].cpu(), ref), "max_abs": orc.max_abs(d[rows].cpu(), ref),
+                       "checked": "first 256 rows vs (A B^T rounded to 16 bits) C^T in fp32 (torch, on the device)"})
+    return res
+
+
 def secondary_object(wname, res, steps, world):
     """Compact form of a secondary workload's result for the default line."""
     obj = {"workload": wname, "value": res["value"], "unit": res["unit"], "value_per_gpu": res["value"] / world,
@@ -815,6 +862,8 @@ def main():
 
     if w["kind"] == "prefill":
         res = run_prefill(args, w, args.workload, device, rank, world, causal=args.causal)
+    elif w["kind"] == "two_gemms":
+        res = run_two_gemms(args, w, device, rank, world)
     else:
         res = run_decode(args, w, args.workload, device, rank, world)
 
