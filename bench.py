@@ -430,7 +430,7 @@ def gpu_attention_fp32(q, k, v, scale, causal):
     return torch.exp(s - lse[:, None]) @ v.float(), lse
 
 
-def prefill_roofline(w, local_flops, per_launch_s, units, loaded_s, reasons):
+def prefill_roofline(w, local_flops, per_launch_s, units, loaded_s, reasons, causal=False):
     pk = peaks()
     # A kernel timed alone in a short region is held against the burst cuBLAS figure;
     # when the timed region is long enough to run into the power cap (seconds-long
@@ -438,7 +438,7 @@ def prefill_roofline(w, local_flops, per_launch_s, units, loaded_s, reasons):
     sustained = ("sw_power_cap" in reasons or loaded_s > 0.5) and pk.get("bf16_tflops_sustained", 0) > 0
     peak_tf = pk["bf16_tflops_sustained"] if sustained else pk["bf16_tflops"]
     ach = local_flops / per_launch_s / 1e12
-    traffic, note = ncu_traffic(w, units)
+    traffic, note = (None, "not captured with the causal mask") if causal else ncu_traffic(w, units)
     return {"bound": "tensor", "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
             "traffic": traffic, "traffic_source": note, "kernel": "attn_fwd_pair_kernel",
             "algorithmic_bytes": 4.0 * units * w["L"] * w["D"] * 2,
@@ -500,7 +500,7 @@ def run_prefill(args, w, name, device, rank, world, causal=False, steps=None, wa
     per_launch_s = secs / steps
     local_flops = prefill_flops(1, local_heads, w["L"], w["L"], w["D"], causal)
     roof = prefill_roofline(w, local_flops, per_launch_s, local_heads, secs * info["repeats"],
-                            info["clocks"]["reasons"])
+                            info["clocks"]["reasons"], causal)
     res = dict(value=value, unit="TFLOP/s", secs=secs, info=info, roofline=roof, launches=steps)
     if args.profile:
         return res
