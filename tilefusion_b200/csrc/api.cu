@@ -408,9 +408,9 @@ int launch_attn_bwd(const void* q, const void* k, const void* v, const void* o, 
   }
   const int n_q_tiles = (d->len_q + tfb::kAttnTile - 1) / tfb::kAttnTile;
   const int n_kv_tiles = (d->len_kv + tfb::kAttnTile - 1) / tfb::kAttnTile;
-  dkv<<<dim3(n_kv_tiles, d->heads, d->batch), tfb::kAttnThreads, Smem::kBytes, stream>>>(mq, mk, mv, mdo, a);
+  dkv<<<dim3(n_kv_tiles, d->heads, d->batch), tfb::kBwdThreads, Smem::kBytes, stream>>>(mq, mk, mv, mdo, a);
   TF_CUDA_TRY(cudaGetLastError());
-  dqk<<<dim3(n_q_tiles, d->heads, d->batch), tfb::kAttnThreads, Smem::kBytes, stream>>>(mq, mk, mv, mdo, a);
+  dqk<<<dim3(n_q_tiles, d->heads, d->batch), tfb::kBwdThreads, Smem::kBytes, stream>>>(mq, mk, mv, mdo, a);
   TF_CUDA_TRY(cudaGetLastError());
   return TF_OK;
 }

@@ -23,7 +23,10 @@
 //                           operands of the second, so nothing is transposed;
 //   attn_bwd_dq_kernel      one CTA per 128-query tile, loops over the key tiles:
 //                           S = Q K^T, dP = dO V^T, dS over dP, dQ += dS K.
-// TMEM: S|dP|dV|dK = 128+128+D+D columns (dK/dV kernel), S|dP|dQ (dQ kernel).
+// A streamed tile is worked in two halves of 64 rows that alternate between two
+// TMEM buffers, so the element-wise stage of one half runs under the MMAs of its
+// neighbours.  TMEM: two buffers of (S | dP) = 2 x (64 + 64) columns, then dV | dK
+// (D + D columns; dK/dV kernel) or dQ (dQ kernel).
 // P and dS are rounded to the 16-bit input type before the second MMAs, all
 // accumulation is fp32.  The two kernels recompute S and dP independently (7
 // tile products per tile pair instead of 5), which keeps dQ free of atomics and
@@ -102,8 +105,8 @@ struct AttnBwdSmem {
   static constexpr int kOffStream = 2 * kTileBytes;
   static constexpr int kOffRows = 6 * kTileBytes;               // lse2 / delta of the streamed tile: [2][2][128] fp32
   static constexpr int kOffBar = kOffRows + 2 * 2 * kAttnTile * 4;
-  static constexpr int kOffTmemSlot = kOffBar + 64;
-  static constexpr int kOffAbort = kOffBar + 68;
+  static constexpr int kOffTmemSlot = kOffBar + 80;
+  static constexpr int kOffAbort = kOffBar + 84;
   static constexpr int kBytes = kOffBar + 128 + 1024;
 };
 
@@ -111,8 +114,14 @@ enum AttnBwdWaitCode {
   kBWaitFixed = 501, kBWaitStream = 502, kBWaitS = 503, kBWaitP = 504, kBWaitSlot = 505, kBWaitEpi = 506
 };
 
+// Element-wise warps: 4 (one thread per row of the fixed tile) or 8 (two threads per row, 32 of the 64
+// streamed columns of a half tile each).  Eight measured no faster (520 against 534 TFLOP/s on the fp16
+// prefill config): the kernels wait for their streamed tiles, not for this stage.
+constexpr int kBwdComputeWarps = 4;
+constexpr int kBwdThreads = (kBwdComputeWarps + 1) * 32;  // + the TMA / MMA issuer warp
+
 __device__ __forceinline__ void bwd_rows_sync() {
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(kBwdComputeWarps * 32) : "memory");
 }
 
 // Shared by the two kernels: which tensor plays which role is the only difference.
@@ -121,14 +130,16 @@ __device__ __forceinline__ void bwd_rows_sync() {
 //   kDkv = false: fixed = (Q, dO) of query tile `tile`; streamed = (K, V) of key tiles
 //                 lanes = queries; output dQ
 template <typename T, int D, bool kDkv>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const AttnBwdArgs args) {
   using S = AttnBwdSmem<D>;
   constexpr int kIsBf16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   constexpr int kTmemCols = 512;
-  constexpr int kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 256 + D;
+  // Two buffers of (S | dP) for 64 streamed rows each: buffer b has S in columns [128 b, 128 b + 64) and
+  // dP in [128 b + 64, 128 b + 128); the accumulators follow.
+  constexpr int kColAcc0 = 256, kColAcc1 = 256 + D;
   constexpr int kBlocks = D / 64;
 
   extern __shared__ uint8_t smem_raw[];
@@ -141,9 +152,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   float* s_rows = reinterpret_cast<float*>(smem_gen + S::kOffRows);   // [slot][lse2 | delta][128]
   const uint32_t bar_fix = smem_base + S::kOffBar + 0;
   const uint32_t bar_str = smem_base + S::kOffBar + 8;     // [2]
-  const uint32_t bar_s = smem_base + S::kOffBar + 24;
-  const uint32_t bar_p = smem_base + S::kOffBar + 32;
-  const uint32_t bar_o = smem_base + S::kOffBar + 40;      // [2]
+  const uint32_t bar_s = smem_base + S::kOffBar + 24;      // [2]  first MMA pair of a half tile is complete (per TMEM buffer)
+  const uint32_t bar_p = smem_base + S::kOffBar + 40;      // [2]  P / dS of a half tile are in place (per TMEM buffer)
+  const uint32_t bar_o = smem_base + S::kOffBar + 56;      // [2]  second MMA pairs of a streamed tile are complete (per slot)
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kOffTmemSlot);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
 
@@ -170,13 +181,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar_str, 1);
     mbar_init(bar_str + 8, 1);
     mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
+    mbar_init(bar_s + 8, 1);
+    mbar_init(bar_p, kBwdComputeWarps * 32);
+    mbar_init(bar_p + 8, kBwdComputeWarps * 32);
     mbar_init(bar_o, 1);
     mbar_init(bar_o + 8, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 4) {
+  if (warp == kBwdComputeWarps) {
     tmem_alloc<kTmemCols>(smem_u32(const_cast<uint32_t*>(tmem_slot)));
     tmem_relinquish();
   }
@@ -185,7 +198,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == kBwdComputeWarps) {
     if (lane == 0 && n > 0) {
       // ------------------------------------------------ TMA + MMA issuer ----
       tma_prefetch_desc(&map_q);
@@ -216,7 +229,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       auto desc_rows = [&](uint32_t tile_smem, int k) {
         return make_smem_desc(tile_smem + k * 2048, S::kBlockBytes, 1024);
       };
-      const uint32_t idesc_sd = make_idesc(128, 128, kIsBf16, 0, 0);
+      const uint32_t idesc_sd = make_idesc(128, 64, kIsBf16, 0, 0);
       const uint32_t idesc_acc = make_idesc(128, D, kIsBf16, 0, 1);
 
       mbar_arrive_expect_tx(bar_fix, 2 * S::kTileBytes);
@@ -225,47 +238,66 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       load_stream(0);
       if (n > 1) load_stream(1);
 
+      // A streamed tile is worked in two halves of 64 rows (u = 2 it + half), alternating between
+      // the two TMEM buffers, so that the element-wise stage of one half runs under the MMAs of its
+      // neighbours.  Issue order:  P1(0) P1(1) | P2(0) P1(2) | P2(1) P1(3) | ...
+      //   P1(u): lanes x 64 streamed rows, contraction over D, into buffer u & 1
+      //          dkv: S^T = K Q^T, dP^T = V dO^T        dq: S = Q K^T, dP = dO V^T
+      //   P2(u): A from tensor memory (16-bit P / dS of buffer u & 1: rows 0..31 of the half in columns
+      //          0..15 of S resp. dP, rows 32..63 in columns 32..47), contraction over the 64 rows
+      //          dkv: dV += P^T dO, dK += dS^T Q        dq: dQ += dS K
+      // The tensor pipe executes in issue order, so P1(u + 2) overwrites buffer u & 1 only after P2(u)
+      // has read it.
+      const int n_half = 2 * n;
       bool ok = mbar_wait(bar_fix, 0, abort_flag, kBWaitFixed);
-      for (int it = 0; ok && it < n; ++it) {
-        const int slot = it & 1;
-        ok = mbar_wait(bar_str + slot * 8, (it >> 1) & 1, abort_flag, kBWaitStream);
-        if (!ok) break;
-        tc_fence_after();
-        // first pair: lanes x streamed rows, contraction over D
-        //   dkv: S^T = K Q^T, dP^T = V dO^T        dq: S = Q K^T, dP = dO V^T
+      auto issue_p1 = [&](int u) -> bool {
+        const int it = u >> 1, hh = u & 1, slot = it & 1, b = u & 1;
+        if (hh == 0) {
+          if (!mbar_wait(bar_str + slot * 8, (it >> 1) & 1, abort_flag, kBWaitStream)) return false;
+          tc_fence_after();
+        }
+        const uint32_t rows = hh * 64 * 128;            // 64 rows of 128 B inside every 64-column block
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_ss(tmem_base + kColS, desc_kmajor(sFix0, k), desc_kmajor(sStr0(slot), k), idesc_sd, k > 0);
+          umma_ss(tmem_base + b * 128, desc_kmajor(sFix0, k), desc_kmajor(sStr0(slot) + rows, k), idesc_sd, k > 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_ss(tmem_base + kColDP, desc_kmajor(sFix1, k), desc_kmajor(sStr1(slot), k), idesc_sd, k > 0);
-        umma_commit(bar_s);
-        // the other slot is free once the second pair of the previous iteration has read it
-        if (it >= 1 && it + 1 < n) {
+          umma_ss(tmem_base + b * 128 + 64, desc_kmajor(sFix1, k), desc_kmajor(sStr1(slot) + rows, k), idesc_sd, k > 0);
+        umma_commit(bar_s + b * 8);
+        return true;
+      };
+      if (ok) ok = issue_p1(0);
+      for (int u = 0; ok && u < n_half; ++u) {
+        const int it = u >> 1, hh = u & 1, slot = it & 1, b = u & 1;
+        if (u + 1 < n_half) {
+          ok = issue_p1(u + 1);
+          if (!ok) break;
+        }
+        // the other slot is free once the second pairs of the previous tile have read it
+        if (hh == 0 && it >= 1 && it + 1 < n) {
           ok = mbar_wait(bar_o + (slot ^ 1) * 8, ((it - 1) >> 1) & 1, abort_flag, kBWaitSlot);
           if (!ok) break;
           load_stream(it + 1);
         }
-        ok = mbar_wait(bar_p, it & 1, abort_flag, kBWaitP);
+        ok = mbar_wait(bar_p + b * 8, (u >> 1) & 1, abort_flag, kBWaitP);
         if (!ok) break;
         tc_fence_after();
-        // second pair: A from tensor memory (16-bit, 2 values per column), contraction over the streamed rows
         if (kDkv) {
 #pragma unroll
-          for (int k = 0; k < kAttnTile / 16; ++k)      // dV += P^T dO
-            umma_ts(tmem_base + kColAcc0, tmem_base + kColS + k * 8, desc_rows(sStr1(slot), k), idesc_acc,
-                    (it > 0) || (k > 0));
+          for (int k = 0; k < 4; ++k)      // dV += P^T dO
+            umma_ts(tmem_base + kColAcc0, tmem_base + b * 128 + (k >> 1) * 32 + (k & 1) * 8, desc_rows(sStr1(slot), hh * 4 + k), idesc_acc,
+                    (u > 0) || (k > 0));
 #pragma unroll
-          for (int k = 0; k < kAttnTile / 16; ++k)      // dK += dS^T Q
-            umma_ts(tmem_base + kColAcc1, tmem_base + kColDP + k * 8, desc_rows(sStr0(slot), k), idesc_acc,
-                    (it > 0) || (k > 0));
+          for (int k = 0; k < 4; ++k)      // dK += dS^T Q
+            umma_ts(tmem_base + kColAcc1, tmem_base + b * 128 + 64 + (k >> 1) * 32 + (k & 1) * 8, desc_rows(sStr0(slot), hh * 4 + k), idesc_acc,
+                    (u > 0) || (k > 0));
         } else {
 #pragma unroll
-          for (int k = 0; k < kAttnTile / 16; ++k)      // dQ += dS K
-            umma_ts(tmem_base + kColAcc0, tmem_base + kColDP + k * 8, desc_rows(sStr0(slot), k), idesc_acc,
-                    (it > 0) || (k > 0));
+          for (int k = 0; k < 4; ++k)      // dQ += dS K
+            umma_ts(tmem_base + kColAcc0, tmem_base + b * 128 + 64 + (k >> 1) * 32 + (k & 1) * 8, desc_rows(sStr0(slot), hh * 4 + k), idesc_acc,
+                    (u > 0) || (k > 0));
         }
-        umma_commit(bar_o + slot * 8);
+        if (hh == 1) umma_commit(bar_o + slot * 8);
       }
       if (!ok) {
         // let copies still in flight land before the CTA gives up its shared memory
@@ -276,8 +308,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   } else {
     // ------------------------------------------------- element-wise warps ---
-    const int row = warp * 32 + lane;                       // lane of tensor memory == row of the fixed tile
-    const uint32_t t_lane = tmem_base + (uint32_t(warp * 32) << 16);
+    // Warp w works on TMEM lane quarter w & 3; with eight warps, on 32-column chunk w >> 2 of every
+    // half tile (and every other chunk of the epilogue), with four on both chunks.
+    constexpr int kChunkStep = kBwdComputeWarps / 4;
+    const int quarter = warp & 3, chunk = warp >> 2;
+    const int row = quarter * 32 + lane;                    // lane of tensor memory == row of the fixed tile
+    const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
     const int fixed_idx = t0 + row;                         // key index (dkv) / query index (dq)
     const long long row_base = (long long)batch * args.row_stride_b + (long long)head * args.row_stride_h;
     bool ok = true;
@@ -298,53 +334,60 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // lse2 / delta of the streamed queries: one value per thread, shared through shared memory
         const int qi = s0 + row;
         const bool valid = qi < args.len_q;
-        rows_lse2[row] = valid ? args.lse[row_base + qi] * 1.4426950408889634f : INFINITY;   // P = 0 beyond len_q
-        rows_delta[row] = valid ? args.delta[row_base + qi] : 0.f;
+        if (kChunkStep == 1 || chunk == 0)
+          rows_lse2[row] = valid ? args.lse[row_base + qi] * 1.4426950408889634f : INFINITY;   // P = 0 beyond len_q
+        if (kChunkStep == 1 || chunk == 1) rows_delta[row] = valid ? args.delta[row_base + qi] : 0.f;
         bwd_rows_sync();
       }
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_s, it & 1, abort_flag, kBWaitS));
-      if (!ok) break;
-      tc_fence_after();
-
+      for (int hh = 0; hh < 2; ++hh) {
+        const int u = 2 * it + hh, b = u & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_s + b * 8, (u >> 1) & 1, abort_flag, kBWaitS));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t col_s = b * 128, col_dp = b * 128 + 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32], dp[32];
-        tmem_ld32(t_lane + kColS + c * 32, sr);
-        tmem_ld32(t_lane + kColDP + c * 32, dp);
-        tmem_wait_ld();
-        uint32_t pk[16], dk[16];
+        for (int c = chunk; c < 2; c += kChunkStep) {
+          uint32_t sr[32], dp[32];
+          tmem_ld32(t_lane + col_s + c * 32, sr);
+          tmem_ld32(t_lane + col_dp + c * 32, dp);
+          tmem_wait_ld();
+          uint32_t pk[16], dk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p[2], ds[2];
+          for (int i = 0; i < 32; i += 2) {
+            float p[2], ds[2];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = s0 + c * 32 + i + e;            // streamed index of this element
-            float lse2, delta;
-            bool masked;
-            if (kDkv) {
-              lse2 = rows_lse2[c * 32 + i + e];
-              delta = rows_delta[c * 32 + i + e];
-              masked = args.causal && fixed_idx > col;      // key beyond the query
-            } else {
-              lse2 = my_lse2;
-              delta = my_delta;
-              masked = col >= args.len_kv || (args.causal && col > fixed_idx);
+            for (int e = 0; e < 2; ++e) {
+              const int local = hh * 64 + c * 32 + i + e;     // row of the streamed tile
+              const int col = s0 + local;                     // its global index
+              float lse2, delta;
+              bool masked;
+              if (kDkv) {
+                lse2 = rows_lse2[local];
+                delta = rows_delta[local];
+                masked = args.causal && fixed_idx > col;      // key beyond the query
+              } else {
+                lse2 = my_lse2;
+                delta = my_delta;
+                masked = col >= args.len_kv || (args.causal && col > fixed_idx);
+              }
+              const float pe = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(sr[i + e]), args.scale_log2, -lse2));
+              p[e] = pe;
+              ds[e] = pe * (__uint_as_float(dp[i + e]) - delta) * args.scale;
             }
-            const float pe = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(sr[i + e]), args.scale_log2, -lse2));
-            p[e] = pe;
-            ds[e] = pe * (__uint_as_float(dp[i + e]) - delta) * args.scale;
+            pk[i >> 1] = pack2<T>(p[0], p[1]);
+            dk[i >> 1] = pack2<T>(ds[0], ds[1]);
           }
-          pk[i >> 1] = pack2<T>(p[0], p[1]);
-          dk[i >> 1] = pack2<T>(ds[0], ds[1]);
+          // 16-bit P over S and dS over dP, each thread over the start of the 32 fp32 columns it
+          // has just read (so the row's other thread is never disturbed): chunk c lands in
+          // columns [32c, 32c + 16) of the buffer.
+          if (kDkv) tmem_st16(t_lane + col_s + c * 32, pk);
+          tmem_st16(t_lane + col_dp + c * 32, dk);
         }
-        // 16-bit P over the start of S, dS over the start of dP (the fp32 columns
-        // they replace have been read: chunk c lands in columns [16c, 16c + 16))
-        if (kDkv) tmem_st16(t_lane + kColS + c * 16, pk);
-        tmem_st16(t_lane + kColDP + c * 16, dk);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p + b * 8);
       }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar_p);
+      if (!ok) break;
     }
 
     // ------------------------------------------------------------ epilogue --
@@ -357,6 +400,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         T* out = reinterpret_cast<T*>(base) + (long long)batch * sb + (long long)head * sh + (long long)fixed_idx * sl;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
+          if (kChunkStep == 2 && (c & 1) != chunk) continue;      // two threads per row take alternate chunks
           uint32_t acc[32];
           if (n > 0) {
             tmem_ld32(t_lane + col0 + c * 32, acc);
@@ -391,7 +435,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   // ---------------------------------------------------------------- teardown --
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kBwdComputeWarps) {
     __syncwarp();
     tmem_dealloc<kTmemCols>(tmem_base);
   }
