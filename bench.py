@@ -80,6 +80,9 @@ WORKLOADS["decode_gqa"] = dict(WORKLOADS["decode_c3"], B=64, Hkv=8)
 # exceed the 126 MB L2, but only a few hundred MB are held on the device.
 WORKLOADS["prefill_profile"] = dict(WORKLOADS["prefill_c2"], B=4)
 WORKLOADS["decode_profile"] = dict(WORKLOADS["decode_c3"], B=4)
+# the short-decode config over an 8-bit (e4m3) K/V cache: half the bytes per key
+WORKLOADS["decode_c3_fp8"] = dict(WORKLOADS["decode_c3"], kv="e4m3")
+WORKLOADS["decode_fp8_profile"] = dict(WORKLOADS["decode_c3_fp8"], B=8)
 WORKLOADS["decode_gqa_profile"] = dict(WORKLOADS["decode_gqa"], B=16)
 # A 1-GiB case of the sharded decode step (split, merge, exchange and combine in one launch) for captures.
 WORKLOADS["decode_c4_profile"] = dict(WORKLOADS["decode_c4"], L=16384)
@@ -119,7 +122,7 @@ def ncu_traffic(w, units_in_launch):
     if not table.exists():
         return None, "no capture recorded"
     kernel = "attn_fwd_pair_kernel" if (w["kind"] == "prefill" or "Hkv" in w) else "decode_split_kernel"
-    case = f"{w['kind']}{'_gqa' if 'Hkv' in w else ''}_L{w['L']}_D{w['D']}"
+    case = f"{w['kind']}{'_gqa' if 'Hkv' in w else ''}{'_' + w['kv'] if 'kv' in w else ''}_L{w['L']}_D{w['D']}"
     entry = json.loads(table.read_text()).get(kernel, {}).get(case)
     if entry is None:
         return None, f"no capture of {kernel} for {case}"
@@ -147,8 +150,8 @@ def prefill_flops(b, h, lq, lk, d, causal=False):
     return 4.0 * b * h * pairs * d
 
 
-def decode_bytes(b, h, lk, d):
-    return 2.0 * b * h * lk * d * 2
+def decode_bytes(b, h, lk, d, elem_bytes=2):
+    return 2.0 * b * h * lk * d * elem_bytes
 
 
 # ------------------------------------------------------------------ clocks ---
@@ -714,6 +717,17 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
     o = torch.empty_like(q)
     lse = torch.empty(w["B"], w["H"], 1, dtype=torch.float32, device=device)
     d = _cabi.TfDecodeDesc()
+    kv_bytes = 2
+    if "kv" in w:
+        # 8-bit cache: the 16-bit draws are quantised on the device (factor 1: the values fit the format)
+        import tilefusion_b200 as tilefusion
+
+        fp8_dtype = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}[w["kv"]]
+        k = tilefusion.ops.fp8_quantize(k, fp8_dtype)
+        v = tilefusion.ops.fp8_quantize(v, fp8_dtype)
+        d.kv_dtype = {"e4m3": _cabi.TF_FP8_E4M3, "e5m2": _cabi.TF_FP8_E5M2}[w["kv"]]
+        kv_bytes = 1
+        torch.cuda.empty_cache()
     d.dtype = _cabi.TF_F16 if w["dtype"] == "fp16" else _cabi.TF_BF16
     d.batch, d.heads, d.len_kv, d.head_dim = w["B"], w["H"], w["L"], w["D"]
     d.kv_chunk, d.num_splits, d.softmax_scale = 512, 0, scale
@@ -734,8 +748,8 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
         if rc != 0:
             _cabi.check(rc)
 
-    total_units = decode_bytes(w["B"] * world, hkv, w["L"], w["D"])
-    local_units = decode_bytes(w["B"], hkv, w["L"], w["D"])
+    total_units = decode_bytes(w["B"] * world, hkv, w["L"], w["D"], kv_bytes)
+    local_units = decode_bytes(w["B"], hkv, w["L"], w["D"], kv_bytes)
     secs, info = time_steps(step, steps, warmup, device, world)
     res = dict(value=total_units * steps / secs / 1e9, unit="GB/s", secs=secs, info=info,
                roofline=decode_roofline(w, local_units, secs, steps, w["B"] * hkv, False), launches=2 * steps)
@@ -763,7 +777,7 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
 
     e2e_secs, _ = time_steps(e2e_step, e2e_steps, 2, device, world, max_repeats=1)
     res["e2e"] = {"value": total_units * e2e_steps / e2e_secs / 1e9, "unit": "GB/s",
-                  "h2d_bytes_per_step": (q.numel() + 2 * k.numel()) * 2,
+                  "h2d_bytes_per_step": q.numel() * 2 + 2 * k.numel() * kv_bytes,
                   "d2h_bytes_per_step": o.numel() * 2, "steps": e2e_steps}
     return res
 
@@ -892,6 +906,13 @@ def main():
         sec_steps = max(10, min(args.steps, 50))
         dres = run_decode(args, WORKLOADS["decode_c3"], "decode_c3", device, rank, world, steps=sec_steps, warmup=3)
         line["decode"] = secondary_object("decode_c3", dres, sec_steps, world)
+        del dres
+        torch.cuda.empty_cache()
+        d8 = run_decode(args, WORKLOADS["decode_c3_fp8"], "decode_c3_fp8", device, rank, world, steps=sec_steps, warmup=3)
+        line["decode_fp8"] = secondary_object("decode_c3_fp8", d8, sec_steps, world)
+        line["decode_fp8"]["kv_cache"] = "e4m3, one byte per element; GB/s counts the 8-bit bytes"
+        line["decode_fp8"]["speedup_vs_16bit_cache"] = line["decode"]["ms_per_step"] / line["decode_fp8"]["ms_per_step"]
+        del d8
         torch.cuda.empty_cache()
         c4 = run_decode(args, WORKLOADS["decode_c4"], "decode_c4", device, rank, world, steps=sec_steps, warmup=3)
         line["decode_c4"] = secondary_object("decode_c4", c4, sec_steps, world)

@@ -33,7 +33,15 @@ typedef enum TfStatus {
   TF_ERR_WORKSPACE = -5      /* caller's workspace is too small               */
 } TfStatus;
 
-typedef enum TfDType { TF_F16 = 0, TF_BF16 = 1 } TfDType;
+typedef enum TfDType {
+  TF_F16 = 0,
+  TF_BF16 = 1,
+  /* 8-bit storage types (OCP 8-bit floating point: e4m3 without infinities,
+   * e5m2 IEEE-like), the ones TileFusion declares in include/types/base.hpp:13-39.
+   * Accepted only where a descriptor says so (TfDecodeDesc.kv_dtype).          */
+  TF_FP8_E4M3 = 2,
+  TF_FP8_E5M2 = 3
+} TfDType;
 
 /*
  * Prefill attention problem: O = softmax(Q K^T * scale [+ causal]) V, fp32
@@ -113,6 +121,13 @@ typedef struct TfDecodeDesc {
                            addressed by (k/v_stride_page, k/v_stride_h) and
                            k/v_stride_b are ignored.  Rows of a sequence's last
                            page beyond len_kv must hold finite values.        */
+  int32_t kv_dtype;     /* stored element of K and V: 0 or == dtype: the query's
+                           type; TF_FP8_E4M3 / TF_FP8_E5M2: one byte per element
+                           (K/V strides then count bytes and are multiples of
+                           16; heads_kv == heads).  Q, O stay `dtype`; all
+                           arithmetic is fp32.                                 */
+  float k_scale;        /* dequantisation factors of an 8-bit cache: key =     */
+  float v_scale;        /* k_scale * stored, value = v_scale * stored; 0 = 1   */
 } TfDecodeDesc;
 
 /* What the registry chose for a decode problem (tf_decode_plan). */
@@ -442,6 +457,26 @@ TF_EXPORT int tf_device_status_peek(int32_t* code_out);
  * effect on each device with the next launch made through this library.
  */
 TF_EXPORT int tf_set_wait_limit_ms(uint32_t milliseconds);
+
+/* ---- 8-bit storage -------------------------------------------------------- */
+
+/*
+ * Bulk conversion of `n` contiguous elements between a 16-bit tensor (TF_F16 /
+ * TF_BF16) and 8-bit storage (TF_FP8_E4M3 / TF_FP8_E5M2); both pointers 16-byte
+ * aligned, any n >= 0.  The bulk form of TileFusion's per-value from_float /
+ * to_float (include/types/base.hpp:70-107, the CUDA __nv_fp8 constructors):
+ *   quantize  : dst[i] = fp8(float(src[i]) * factor), round to nearest even,
+ *               values beyond the largest finite one saturate to it;
+ *   dequantize: dst[i] = 16-bit(float(src[i]) * factor), round to nearest even.
+ * A K/V cache written with factor f is read by tf_decode* with k_scale /
+ * v_scale = 1 / f.  One HBM-bound kernel each (3 bytes per element).
+ */
+TF_EXPORT int tf_fp8_quantize(const void* src, void* dst, int64_t n,
+                              int32_t src_dtype, int32_t fp8_dtype, float factor,
+                              void* stream);
+TF_EXPORT int tf_fp8_dequantize(const void* src, void* dst, int64_t n,
+                                int32_t fp8_dtype, int32_t dst_dtype, float factor,
+                                void* stream);
 
 /* Library ABI version (bumped when a struct above changes). */
 TF_EXPORT int tf_abi_version(void);

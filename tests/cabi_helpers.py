@@ -70,10 +70,15 @@ def attn_bwd(q, k, v, o, d_o, lse, scale, causal=False):
     return dq, dk, dv
 
 
-def decode_desc(q, k, v, o=None, scale=None, kv_chunk=512, num_splits=0) -> _cabi.TfDecodeDesc:
-    """q [B,H,1,D], k/v [B,H,Lk,D]."""
+_FP8_CODES = {torch.float8_e4m3fn: _cabi.TF_FP8_E4M3, torch.float8_e5m2: _cabi.TF_FP8_E5M2}
+
+
+def decode_desc(q, k, v, o=None, scale=None, kv_chunk=512, num_splits=0, k_scale=0.0, v_scale=0.0) -> _cabi.TfDecodeDesc:
+    """q [B,H,1,D], k/v [B,H,Lk,D] (q's dtype, or float8 with dequantisation factors)."""
     d = _cabi.TfDecodeDesc()
     d.dtype = _dtype_code(q)
+    d.kv_dtype = _FP8_CODES.get(k.dtype, 0)
+    d.k_scale, d.v_scale = k_scale, v_scale
     d.batch, d.heads = q.size(0), q.size(1)
     d.heads_kv = k.size(1)
     d.len_kv = k.size(2)
@@ -94,12 +99,12 @@ def decode_plan(d: _cabi.TfDecodeDesc) -> _cabi.TfDecodePlan:
     return plan
 
 
-def decode(q, k, v, scale=None, kv_chunk=512, num_splits=0):
+def decode(q, k, v, scale=None, kv_chunk=512, num_splits=0, k_scale=0.0, v_scale=0.0):
     lib = _cabi.lib()
     b, h, _, dim = q.shape
     o = torch.full((b, h, 1, dim), float("nan"), dtype=q.dtype, device=q.device)
     lse = torch.full((b, h, 1), float("nan"), dtype=torch.float32, device=q.device)
-    d = decode_desc(q, k, v, o, scale, kv_chunk, num_splits)
+    d = decode_desc(q, k, v, o, scale, kv_chunk, num_splits, k_scale, v_scale)
     plan = decode_plan(d)
     ws = torch.full((max(1, plan.workspace_bytes // 4),), float("nan"), dtype=torch.float32, device=q.device)
     rc = lib.tf_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
@@ -108,11 +113,11 @@ def decode(q, k, v, scale=None, kv_chunk=512, num_splits=0):
     return o, lse
 
 
-def decode_split(q, k, v, scale=None, kv_chunk=512, num_splits=0):
+def decode_split(q, k, v, scale=None, kv_chunk=512, num_splits=0, k_scale=0.0, v_scale=0.0):
     """Returns (part_o [B,H,S,D], part_ml [B,H,S,2], plan)."""
     lib = _cabi.lib()
     b, h, _, dim = q.shape
-    d = decode_desc(q, k, v, None, scale, kv_chunk, num_splits)
+    d = decode_desc(q, k, v, None, scale, kv_chunk, num_splits, k_scale, v_scale)
     plan = decode_plan(d)
     ws = torch.full((plan.workspace_bytes // 4,), float("nan"), dtype=torch.float32, device=q.device)
     rc = lib.tf_decode_split(q.data_ptr(), k.data_ptr(), v.data_ptr(), ws.data_ptr(), ws.numel() * 4,
@@ -144,6 +149,18 @@ def decode_gathered(slots, batch, heads, dim, dtype):
                                 o.stride(0), o.stride(1), lse.data_ptr(), _stream())
     _cabi.check(rc)
     return o, lse
+
+
+def fp8_convert(src, dst, factor=1.0):
+    """tf_fp8_quantize (dst float8) or tf_fp8_dequantize (src float8) over flat tensors."""
+    lib = _cabi.lib()
+    if dst.dtype in _FP8_CODES:
+        rc = lib.tf_fp8_quantize(src.data_ptr(), dst.data_ptr(), src.numel(), _dtype_code(src), _FP8_CODES[dst.dtype],
+                                 factor, _stream())
+    else:
+        rc = lib.tf_fp8_dequantize(src.data_ptr(), dst.data_ptr(), src.numel(), _FP8_CODES[src.dtype], _dtype_code(dst),
+                                   factor, _stream())
+    _cabi.check(rc)
 
 
 def device_status() -> int:

@@ -89,7 +89,7 @@ static int run_case(int lq, int lk, int d, int decode) {
 }
 
 int main(void) {
-  if (tf_abi_version() != 4) { printf("unexpected ABI version %d\n", tf_abi_version()); return 4; }
+  if (tf_abi_version() != 5) { printf("unexpected ABI version %d\n", tf_abi_version()); return 4; }
   int bad = 0;
   bad |= run_case(200, 300, 128, 0);
   bad |= run_case(64, 128, 64, 0);

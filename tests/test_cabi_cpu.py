@@ -22,13 +22,13 @@ def test_library_exports_every_declared_symbol(native_lib):
     assert sorted(declared) == sorted(_cabi.EXPORTED)
     for name in declared:
         assert hasattr(native_lib, name), f"{name} is declared but not exported"
-    assert native_lib.tf_abi_version() == 4
+    assert native_lib.tf_abi_version() == 5
 
 
 def test_struct_layouts_match_header():
     # field order and types are mirrored by hand; sizes catch a drift
     assert C.sizeof(_cabi.TfAttnDesc) == 12 * 4 + 14 * 8
-    assert C.sizeof(_cabi.TfDecodeDesc) == 8 * 4 + 8 * 8 + 2 * 4 + 8 + 2 * 4 + 2 * 8
+    assert C.sizeof(_cabi.TfDecodeDesc) == 8 * 4 + 8 * 8 + 2 * 4 + 8 + 2 * 4 + 2 * 8 + 3 * 4 + 4   # (+ tail padding)
     assert C.sizeof(_cabi.TfDecodePlan) == 6 * 4 + 8
     assert C.sizeof(_cabi.TfAttnPlan) == 7 * 4 + 4 + 8
     for struct, cname in [(_cabi.TfAttnDesc, "TfAttnDesc"), (_cabi.TfDecodeDesc, "TfDecodeDesc"),
@@ -178,6 +178,40 @@ def test_decode_plan_honours_requested_splits(native_lib):
     assert (plan.num_splits, plan.chunks_per_split) == (3, 3)
     assert native_lib.tf_decode_plan(C.byref(_decode_desc(4, 8, 4096, splits=100)), C.byref(plan)) == 0
     assert (plan.num_splits, plan.chunks_per_split) == (8, 1)
+
+
+def test_decode_plan_for_an_8bit_cache(native_lib):
+    plan = _cabi.TfDecodePlan()
+    d = _decode_desc(4, 32, 16384)
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == 0 and plan.stages == 3
+    for code in (_cabi.TF_FP8_E4M3, _cabi.TF_FP8_E5M2):
+        d.kv_dtype = code
+        assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == 0
+        assert plan.stages == 5 and plan.workspace_bytes == 4 * 32 * plan.num_splits * 130 * 4
+    d.heads_kv = 8
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_UNSUPPORTED
+    assert "grouped-query" in native_lib.tf_last_error().decode()
+    d.heads_kv = 0
+    d.k_stride_h += 8
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_UNSUPPORTED
+    assert "multiples of 16" in native_lib.tf_last_error().decode()
+    d.k_stride_h -= 8
+    d.v_scale = float("inf")
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_BAD_ARG
+    d.v_scale, d.kv_dtype = 0.0, 9
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_UNSUPPORTED
+    assert "kv_dtype" in native_lib.tf_last_error().decode()
+
+
+def test_fp8_conversion_argument_checks_need_no_device(native_lib):
+    q, dq = native_lib.tf_fp8_quantize, native_lib.tf_fp8_dequantize
+    assert q(None, None, 0, _cabi.TF_F16, _cabi.TF_FP8_E4M3, 1.0, None) == 0            # nothing to do
+    assert q(None, None, 16, _cabi.TF_F16, _cabi.TF_FP8_E4M3, 1.0, None) == _cabi.TF_ERR_BAD_ARG
+    assert q(None, None, -1, _cabi.TF_F16, _cabi.TF_FP8_E4M3, 1.0, None) == _cabi.TF_ERR_BAD_ARG
+    assert q(None, None, 0, _cabi.TF_FP8_E4M3, _cabi.TF_FP8_E4M3, 1.0, None) == _cabi.TF_ERR_UNSUPPORTED
+    assert dq(None, None, 0, _cabi.TF_BF16, _cabi.TF_BF16, 1.0, None) == _cabi.TF_ERR_UNSUPPORTED
+    assert dq(None, None, 0, _cabi.TF_FP8_E5M2, _cabi.TF_BF16, float("nan"), None) == _cabi.TF_ERR_BAD_ARG
+    assert dq(8, 32, 16, _cabi.TF_FP8_E5M2, _cabi.TF_BF16, 1.0, None) == _cabi.TF_ERR_UNSUPPORTED   # misaligned src
 
 
 @pytest.mark.parametrize("kw,needle", [

@@ -22,6 +22,8 @@ TF_ERR_DEVICE_TIMEOUT = -4
 TF_ERR_WORKSPACE = -5
 TF_F16 = 0
 TF_BF16 = 1
+TF_FP8_E4M3 = 2
+TF_FP8_E5M2 = 3
 
 # Every symbol the header declares (checked by the CPU test-suite).
 EXPORTED = (
@@ -33,6 +35,7 @@ EXPORTED = (
     "tf_shard_head_slice", "tf_shard_kv_slice", "tf_prefill_sharded", "tf_shard_unique_id",
     "tf_shard_create", "tf_shard_transport", "tf_shard_note", "tf_decode_sharded", "tf_shard_destroy",
     "tf_device_status_peek", "tf_set_wait_limit_ms", "tf_attn_bwd", "tf_attn_bwd_workspace_bytes",
+    "tf_fp8_quantize", "tf_fp8_dequantize",
 )
 TF_NCCL_ID_BYTES = 128
 TF_TRANSPORT_AUTO, TF_TRANSPORT_P2P, TF_TRANSPORT_NCCL = 0, 1, 2
@@ -66,6 +69,7 @@ class TfDecodeDesc(C.Structure):
         ("heads_kv", C.c_int32), ("page_size", C.c_int32),
         ("block_table", C.c_void_p), ("max_pages", C.c_int32), ("num_pages", C.c_int32),
         ("k_stride_page", C.c_int64), ("v_stride_page", C.c_int64),
+        ("kv_dtype", C.c_int32), ("k_scale", C.c_float), ("v_scale", C.c_float),
     ]
 
 
@@ -132,6 +136,8 @@ def lib() -> C.CDLL:
     handle.tf_device_status.argtypes = [C.POINTER(C.c_int32)]
     handle.tf_device_status_peek.argtypes = [C.POINTER(C.c_int32)]
     handle.tf_set_wait_limit_ms.argtypes = [C.c_uint32]
+    handle.tf_fp8_quantize.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p]
+    handle.tf_fp8_dequantize.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p]
     handle.tf_shard_head_slice.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]
     handle.tf_shard_kv_slice.argtypes = [i64, i32, i32, i32, C.POINTER(i64), C.POINTER(i64)]
     handle.tf_prefill_sharded.argtypes = [i32, i32, vp, vp, vp, vp, fp, C.POINTER(TfAttnDesc), vp,

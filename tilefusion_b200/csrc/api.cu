@@ -20,6 +20,7 @@
 #include "attn_fwd_pair_sm100.cuh"
 #include "attn_bwd_sm100.cuh"
 #include "decode_sm100.cuh"
+#include "fp8_sm100.cuh"
 #include "internal.h"
 #include "registry.h"
 #include "tilefusion_b200.h"
@@ -415,6 +416,8 @@ int launch_attn_bwd(const void* q, const void* k, const void* v, const void* o, 
   return TF_OK;
 }
 
+bool kv_is_fp8(const TfDecodeDesc* d) { return d->kv_dtype == TF_FP8_E4M3 || d->kv_dtype == TF_FP8_E5M2; }
+
 int check_decode_desc(const TfDecodeDesc* d) {
   if (d == nullptr) return fail(TF_ERR_BAD_ARG, "desc is null");
   if (d->dtype != TF_F16 && d->dtype != TF_BF16)
@@ -449,17 +452,35 @@ int check_decode_desc(const TfDecodeDesc* d) {
                        d->v_stride_b, d->v_stride_h};
   for (int64_t x : s)
     if (x % 8 != 0 || x < 0) return fail(TF_ERR_UNSUPPORTED, "Q/K/V strides must be non-negative multiples of 8 elements (16 bytes)");
+  if (d->kv_dtype != 0 && d->kv_dtype != d->dtype && !kv_is_fp8(d))
+    return fail(TF_ERR_UNSUPPORTED, "kv_dtype must be 0, equal to dtype, TF_FP8_E4M3 or TF_FP8_E5M2 (got %d)", d->kv_dtype);
+  if (kv_is_fp8(d)) {
+    if (d->heads_kv > 0 && d->heads_kv != d->heads)
+      return fail(TF_ERR_UNSUPPORTED, "grouped-query decoding reads a 16-bit K/V cache; an 8-bit cache needs heads_kv == heads");
+    const int64_t kv[] = {d->k_stride_b, d->k_stride_h, d->v_stride_b, d->v_stride_h,
+                          d->page_size != 0 ? d->k_stride_page : 0, d->page_size != 0 ? d->v_stride_page : 0};
+    for (int64_t x : kv)
+      if (x % 16 != 0) return fail(TF_ERR_UNSUPPORTED, "strides of an 8-bit K/V cache must be multiples of 16 elements (16 bytes)");
+  }
+  const float scales[] = {d->k_scale, d->v_scale};
+  for (float x : scales)
+    if (x != 0.f && (!(x > 0.f) || !std::isfinite(x)))
+      return fail(TF_ERR_BAD_ARG, "k_scale and v_scale must be positive and finite (0 stands for 1)");
   return TF_OK;
 }
 
 bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
-template <typename T, int D>
+// KV: the stored K/V element (T itself, or an 8-bit tag).  Two CTAs share an SM,
+// so a CTA's ring is three 32-KB stages of a 16-bit cache or five 16-KB stages
+// of an 8-bit one (whose cross-group reduction buffer is twice as large).
+template <typename T, typename KV, int D>
 int launch_decode_split(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
                         const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream,
                         const tfb::DecodeFuseArgs* fuse = nullptr) {
-  constexpr int kStages = 3;
-  using Smem = tfb::DecodeSmem<D, kStages>;
+  constexpr int kKvBytes = tfb::KvBytes<KV>::value;
+  constexpr int kStages = kKvBytes == 2 ? 3 : 5;
+  using Smem = tfb::DecodeSmem<D, kStages, kKvBytes>;
   tfb::DecodeSplitArgs a;
   a.fuse = fuse != nullptr ? *fuse : tfb::DecodeFuseArgs{};
   a.q = q;
@@ -473,7 +494,8 @@ int launch_decode_split(const void* q, const void* k, const void* v, float* part
   a.num_splits = plan.num_splits;
   a.chunks_per_split = plan.chunks_per_split;
   a.items = d->batch * d->heads * plan.num_splits;
-  a.scale_log2 = d->softmax_scale * 1.4426950408889634f;
+  a.scale_log2 = d->softmax_scale * 1.4426950408889634f * (d->k_scale != 0.f ? d->k_scale : 1.f);
+  a.v_scale = d->v_scale != 0.f ? d->v_scale : 1.f;
   a.q_stride_b = d->q_stride_b;
   a.q_stride_h = d->q_stride_h;
   a.k_stride_b = d->k_stride_b;
@@ -485,7 +507,7 @@ int launch_decode_split(const void* q, const void* k, const void* v, float* part
   a.max_pages = d->max_pages;
   a.k_stride_page = d->k_stride_page;
   a.v_stride_page = d->v_stride_page;
-  auto kern = tfb::decode_split_kernel<T, D, kStages>;
+  auto kern = tfb::decode_split_kernel<T, KV, D, kStages>;
   static thread_local int configured_device = -1;
   int dev = 0;
   TF_CUDA_TRY(cudaGetDevice(&dev));
@@ -574,16 +596,28 @@ int launch_gqa_split(const void* q, const void* k, const void* v, float* part_o,
 
 bool is_grouped(const TfDecodeDesc* d) { return d->heads_kv > 0 && d->heads_kv != d->heads; }
 
+// KvTag: an 8-bit storage tag, or void for a cache stored in the query's type.
+template <typename KvTag>
+int dispatch_split_kv(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
+                      const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream,
+                      const tfb::DecodeFuseArgs* fuse) {
+  using KvH = std::conditional_t<std::is_void<KvTag>::value, __half, KvTag>;
+  using KvB = std::conditional_t<std::is_void<KvTag>::value, __nv_bfloat16, KvTag>;
+  if (d->head_dim == 128)
+    return d->dtype == TF_F16 ? launch_decode_split<__half, KvH, 128>(q, k, v, part_o, part_ml, d, plan, stream, fuse)
+                              : launch_decode_split<__nv_bfloat16, KvB, 128>(q, k, v, part_o, part_ml, d, plan, stream, fuse);
+  return d->dtype == TF_F16 ? launch_decode_split<__half, KvH, 64>(q, k, v, part_o, part_ml, d, plan, stream, fuse)
+                            : launch_decode_split<__nv_bfloat16, KvB, 64>(q, k, v, part_o, part_ml, d, plan, stream, fuse);
+}
+
 // `fuse` (one query head per KV head only): merge, exchange and final combine in the same launch.
 int dispatch_split(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
                    const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream,
                    const tfb::DecodeFuseArgs* fuse = nullptr) {
   if (is_grouped(d)) return launch_gqa_split(q, k, v, part_o, part_ml, d, plan, stream);
-  if (d->head_dim == 128)
-    return d->dtype == TF_F16 ? launch_decode_split<__half, 128>(q, k, v, part_o, part_ml, d, plan, stream, fuse)
-                              : launch_decode_split<__nv_bfloat16, 128>(q, k, v, part_o, part_ml, d, plan, stream, fuse);
-  return d->dtype == TF_F16 ? launch_decode_split<__half, 64>(q, k, v, part_o, part_ml, d, plan, stream, fuse)
-                            : launch_decode_split<__nv_bfloat16, 64>(q, k, v, part_o, part_ml, d, plan, stream, fuse);
+  if (d->kv_dtype == TF_FP8_E4M3) return dispatch_split_kv<tfb::Fp8E4M3>(q, k, v, part_o, part_ml, d, plan, stream, fuse);
+  if (d->kv_dtype == TF_FP8_E5M2) return dispatch_split_kv<tfb::Fp8E5M2>(q, k, v, part_o, part_ml, d, plan, stream, fuse);
+  return dispatch_split_kv<void>(q, k, v, part_o, part_ml, d, plan, stream, fuse);
 }
 
 int plan_and_check_decode(const void* q, const void* k, const void* v, const void* workspace,
@@ -756,6 +790,46 @@ int launch_sharded_decode(const void* q, const void* k, const void* v, void* o, 
 }
 
 }  // namespace tfb
+
+namespace {
+
+// Bulk conversion between a 16-bit tensor and 8-bit storage (both directions).
+template <typename T, bool kE4M3>
+int launch_convert_fp8(const void* src, void* dst, int64_t n, float factor, cudaStream_t stream, bool to_fp8) {
+  const int64_t n_vec = n / tfb::kFp8ElemsPerThread;
+  const int64_t want = std::max<int64_t>(1, (n_vec + tfb::kFp8ConvertThreads - 1) / tfb::kFp8ConvertThreads);
+  const int grid = (int)std::min<int64_t>(want, (int64_t)sm_count() * 8);
+  if (to_fp8)
+    tfb::fp8_quantize_kernel<T, kE4M3><<<grid, tfb::kFp8ConvertThreads, 0, stream>>>(
+        static_cast<const T*>(src), static_cast<uint8_t*>(dst), n, factor);
+  else
+    tfb::fp8_dequantize_kernel<T, kE4M3><<<grid, tfb::kFp8ConvertThreads, 0, stream>>>(
+        static_cast<const uint8_t*>(src), static_cast<T*>(dst), n, factor);
+  TF_CUDA_TRY(cudaGetLastError());
+  return TF_OK;
+}
+
+int convert_fp8(const void* src, void* dst, int64_t n, int32_t wide_dtype, int32_t fp8_dtype, float factor,
+                void* stream, bool to_fp8) {
+  if (n < 0) return fail(TF_ERR_BAD_ARG, "n must be non-negative (got %lld)", (long long)n);
+  if (wide_dtype != TF_F16 && wide_dtype != TF_BF16)
+    return fail(TF_ERR_UNSUPPORTED, "the 16-bit side must be TF_F16 or TF_BF16 (got %d)", wide_dtype);
+  if (fp8_dtype != TF_FP8_E4M3 && fp8_dtype != TF_FP8_E5M2)
+    return fail(TF_ERR_UNSUPPORTED, "the 8-bit side must be TF_FP8_E4M3 or TF_FP8_E5M2 (got %d)", fp8_dtype);
+  if (!(factor > 0.f) || !std::isfinite(factor)) return fail(TF_ERR_BAD_ARG, "factor must be positive and finite");
+  if (n == 0) return TF_OK;
+  if (src == nullptr || dst == nullptr) return fail(TF_ERR_BAD_ARG, "src and dst must be non-null");
+  if (!aligned16(src) || !aligned16(dst)) return fail(TF_ERR_UNSUPPORTED, "src and dst must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool e4 = fp8_dtype == TF_FP8_E4M3;
+  if (wide_dtype == TF_F16)
+    return e4 ? launch_convert_fp8<__half, true>(src, dst, n, factor, st, to_fp8)
+              : launch_convert_fp8<__half, false>(src, dst, n, factor, st, to_fp8);
+  return e4 ? launch_convert_fp8<__nv_bfloat16, true>(src, dst, n, factor, st, to_fp8)
+            : launch_convert_fp8<__nv_bfloat16, false>(src, dst, n, factor, st, to_fp8);
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -1107,6 +1181,16 @@ int tf_set_wait_limit_ms(uint32_t milliseconds) {
   return TF_OK;
 }
 
-int tf_abi_version(void) { return 4; }
+int tf_fp8_quantize(const void* src, void* dst, int64_t n, int32_t src_dtype, int32_t fp8_dtype, float factor,
+                    void* stream) {
+  return convert_fp8(src, dst, n, src_dtype, fp8_dtype, factor, stream, /*to_fp8=*/true);
+}
+
+int tf_fp8_dequantize(const void* src, void* dst, int64_t n, int32_t fp8_dtype, int32_t dst_dtype, float factor,
+                      void* stream) {
+  return convert_fp8(src, dst, n, dst_dtype, fp8_dtype, factor, stream, /*to_fp8=*/false);
+}
+
+int tf_abi_version(void) { return 5; }
 
 }  // extern "C"

@@ -41,7 +41,18 @@
 // grid work on the same one or two rows at any moment, so all of them hit the
 // same counter at once.)  Only plain peer stores and system-scope
 // release/acquire touch peer memory.
+//
+// 8-bit K/V (OCP e4m3 / e5m2 storage, the types TileFusion declares in
+// include/types/base.hpp:13-39 and only converts, tests/cpp/types/test_fp8.cu):
+// the KV template parameter selects the stored element.  The byte stream per key
+// halves, a lane still reads 16 bytes of a row (16 head dims instead of 8), the
+// ring holds twice as many 128-key stages of half the size, and the elements are
+// widened e4m3/e5m2 -> f16x2 -> fp32 in registers; q, the scores, the softmax
+// and the accumulators stay fp32.  Per-tensor dequantisation factors fold into
+// the score scale (K) and into the partial row as it is written (V).
 #pragma once
+
+#include <cuda_fp8.h>
 
 #include <type_traits>
 
@@ -81,6 +92,50 @@ struct DecodeFuseArgs {
   float* lse;                 // [rows] or null
 };
 
+// Tags for 8-bit K/V storage (the KV template parameter; a 16-bit cache passes T).
+struct Fp8E4M3 {};
+struct Fp8E5M2 {};
+
+template <typename KV>
+struct KvBytes {
+  static constexpr int value = 2;
+};
+template <>
+struct KvBytes<Fp8E4M3> {
+  static constexpr int value = 1;
+};
+template <>
+struct KvBytes<Fp8E5M2> {
+  static constexpr int value = 1;
+};
+
+// The 16 bytes a lane reads from a key or value row, widened to fp32: 8 elements
+// of a 16-bit cache, 16 of an 8-bit one.
+template <typename KV>
+__device__ __forceinline__ void unpack_row16(const uint4 v, float (&out)[16 / KvBytes<KV>::value]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  if constexpr (KvBytes<KV>::value == 2) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack2<KV>(w[e]);
+      out[2 * e] = f.x;
+      out[2 * e + 1] = f.y;
+    }
+  } else {
+    constexpr __nv_fp8_interpretation_t kKind = std::is_same<KV, Fp8E4M3>::value ? __NV_E4M3 : __NV_E5M2;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __half2 lo(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[e] & 0xffffu), kKind));
+      const __half2 hi(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[e] >> 16), kKind));
+      const float2 a = __half22float2(lo), b = __half22float2(hi);
+      out[4 * e] = a.x;
+      out[4 * e + 1] = a.y;
+      out[4 * e + 2] = b.x;
+      out[4 * e + 3] = b.y;
+    }
+  }
+}
+
 struct DecodeSplitArgs {
   const void* q;
   const void* k;
@@ -93,7 +148,8 @@ struct DecodeSplitArgs {
   int num_splits;
   int chunks_per_split;
   int items;          // B*H*num_splits
-  float scale_log2;
+  float scale_log2;   // softmax_scale * log2(e) * the keys' dequantisation factor
+  float v_scale;      // the values' dequantisation factor (1 for a 16-bit cache)
   long long q_stride_b, q_stride_h;
   long long k_stride_b, k_stride_h;
   long long v_stride_b, v_stride_h;
@@ -105,13 +161,13 @@ struct DecodeSplitArgs {
   DecodeFuseArgs fuse;
 };
 
-template <int D, int kStages>
+template <int D, int kStages, int kKvBytes = 2>
 struct DecodeSmem {
-  static constexpr int kStageBytes = kDecKeysPerStage * D * 2;
+  static constexpr int kStageBytes = kDecKeysPerStage * D * kKvBytes;
   static constexpr int kOffStages = 0;
   static constexpr int kOffScores = kStages * kStageBytes;              // 2 x kDecMaxChunk fp32
   static constexpr int kOffRed = kOffScores + 2 * kDecMaxChunk * 4;     // [groups][D] fp32
-  static constexpr int kGroups = kDecConsumerThreads / (D / 8);
+  static constexpr int kGroups = kDecConsumerThreads / (D * kKvBytes / 16);
   static constexpr int kOffWarp = kOffRed + kGroups * D * 4;            // 16 fp32 scratch
   static constexpr int kOffBar = kOffWarp + 64;                         // 2*kStages mbarriers
   static constexpr int kOffDone = kOffBar + 2 * kStages * 8;            // kDecDoneSlots "item written" + as many "slot free" mbarriers
@@ -157,13 +213,16 @@ __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerThreads) : "memory");
 }
 
-template <typename T, int D, int kStages>
+template <typename T, typename KV, int D, int kStages>
 __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const DecodeSplitArgs args) {
-  using S = DecodeSmem<D, kStages>;
-  constexpr int kLpr = D / 8;                          // lanes per key row (16 B each)
+  constexpr int kKvBytes = KvBytes<KV>::value;
+  using S = DecodeSmem<D, kStages, kKvBytes>;
+  constexpr int kRowBytes = D * kKvBytes;              // one key or value row
+  constexpr int kEpl = 16 / kKvBytes;                  // head dims per lane (16 B of a row)
+  constexpr int kLpr = D / kEpl;                       // lanes per key row
   constexpr int kGroups = kDecConsumerThreads / kLpr;  // key rows read per step
   constexpr int kKpt = kDecKeysPerStage / kGroups;     // keys per thread per stage
-  static_assert(kKpt == 8 || kKpt == 4, "unexpected keys per thread");
+  static_assert(kKpt == 8 || kKpt == 4 || kKpt == 2, "unexpected keys per thread");
   static_assert(kLpr >= kKpt, "butterfly needs at least kKpt lanes per row");
 
   extern __shared__ uint8_t smem_raw[];
@@ -341,29 +400,32 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
         const int split = item - bh * args.num_splits;
         const int b = bh / args.heads, h = bh - b * args.heads;
         const bool paged = args.page_size > 0;
-        const T* kbase = reinterpret_cast<const T*>(args.k) + (paged ? 0 : b * args.k_stride_b) + h * args.k_stride_h;
-        const T* vbase = reinterpret_cast<const T*>(args.v) + (paged ? 0 : b * args.v_stride_b) + h * args.v_stride_h;
+        // byte addresses: strides count elements of the stored type
+        const uint8_t* kbase = reinterpret_cast<const uint8_t*>(args.k) +
+                               ((paged ? 0 : b * args.k_stride_b) + h * args.k_stride_h) * kKvBytes;
+        const uint8_t* vbase = reinterpret_cast<const uint8_t*>(args.v) +
+                               ((paged ? 0 : b * args.v_stride_b) + h * args.v_stride_h) * kKvBytes;
         const int* pages = paged ? args.block_table + (long long)b * args.max_pages : nullptr;
         const int key_begin = split * keys_per_split;
         const int key_end = min(args.len_kv, key_begin + keys_per_split);
         for (int c0 = key_begin; ok && c0 < key_end; c0 += chunk) {
           const int c1 = min(key_end, c0 + chunk);
           for (int pass = 0; ok && pass < 2; ++pass) {
-            const T* base = pass == 0 ? kbase : vbase;
+            const uint8_t* base = pass == 0 ? kbase : vbase;
             for (int s0 = c0; s0 < c1; s0 += kDecKeysPerStage) {
               const int n = min(kDecKeysPerStage, c1 - s0);
               if (issued >= kStages) {
                 ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, kWaitDecEmpty);
                 if (!ok) break;
               }
-              const uint32_t bytes = uint32_t(n) * D * 2;
+              const uint32_t bytes = uint32_t(n) * kRowBytes;
               mbar_arrive_expect_tx(bar_full + stage * 8, bytes);
               // a 128-key stage never straddles a page (page_size is a multiple of 128)
-              const T* src = base + (long long)s0 * D;
+              const uint8_t* src = base + (long long)s0 * kRowBytes;
               if (paged) {
                 const int pg = s0 / args.page_size;
-                src = base + (long long)pages[pg] * (pass == 0 ? args.k_stride_page : args.v_stride_page) +
-                      (long long)(s0 - pg * args.page_size) * D;
+                src = base + (long long)pages[pg] * (pass == 0 ? args.k_stride_page : args.v_stride_page) * kKvBytes +
+                      (long long)(s0 - pg * args.page_size) * kRowBytes;
               }
               tma_load_1d(smem_base + S::kOffStages + stage * S::kStageBytes, src, bytes,
                           bar_full + stage * 8, policy);
@@ -387,7 +449,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
     }
   } else {
     // ----------------------------------------------------------- consumers --
-    const int g = tid % kLpr;        // which 8 head dims this lane owns
+    const int g = tid % kLpr;        // which kEpl head dims this lane owns
     const int r = tid / kLpr;        // key group
     uint32_t stage = 0, phase = 0;
     uint32_t n_done = 0;             // items this CTA has handed to the merger warp
@@ -415,23 +477,26 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
       const int key_begin = split * keys_per_split;
       const int key_end = min(args.len_kv, key_begin + keys_per_split);
 
-      // q * scale * log2(e) for this lane's 8 dims
-      float qf[8];
+      // q * scale * log2(e) for this lane's dims
+      float qf[kEpl];
       {
-        const T* qp = reinterpret_cast<const T*>(args.q) + b * args.q_stride_b + h * args.q_stride_h + g * 8;
-        const uint4 qv = *reinterpret_cast<const uint4*>(qp);
-        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+        const T* qp = reinterpret_cast<const T*>(args.q) + b * args.q_stride_b + h * args.q_stride_h + g * kEpl;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = unpack2<T>(qw[i]);
-          qf[2 * i] = f.x * args.scale_log2;
-          qf[2 * i + 1] = f.y * args.scale_log2;
+        for (int j = 0; j < kEpl / 8; ++j) {
+          const uint4 qv = *reinterpret_cast<const uint4*>(qp + j * 8);
+          const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = unpack2<T>(qw[i]);
+            qf[j * 8 + 2 * i] = f.x * args.scale_log2;
+            qf[j * 8 + 2 * i + 1] = f.y * args.scale_log2;
+          }
         }
       }
 
-      float acc[8];
+      float acc[kEpl];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int i = 0; i < kEpl; ++i) acc[i] = 0.f;
       float m_run = -INFINITY;
       float l_thread = 0.f;      // this thread's share of sum(p); reduced at the end
       int chunk_idx = 0;
@@ -454,14 +519,10 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
             const int key = i * kGroups + r;
             float d = 0.f;
             if (key < n) {
-              const uint4 kv = *reinterpret_cast<const uint4*>(st + key * (D * 2) + g * 16);
-              const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+              float kf[kEpl];
+              unpack_row16<KV>(*reinterpret_cast<const uint4*>(st + key * kRowBytes + g * 16), kf);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = unpack2<T>(kw[e]);
-                d = fmaf(f.x, qf[2 * e], d);
-                d = fmaf(f.y, qf[2 * e + 1], d);
-              }
+              for (int e = 0; e < kEpl; ++e) d = fmaf(kf[e], qf[e], d);
             }
             part[i] = d;
           }
@@ -519,7 +580,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
         m_run = m_new;
         l_thread *= alpha;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] *= alpha;
+        for (int i = 0; i < kEpl; ++i) acc[i] *= alpha;
         for (int i = tid; i < n_chunk; i += kDecConsumerThreads) {
           const float p = fast_exp2(sc[i] - m_new);
           sc[i] = p;
@@ -539,14 +600,10 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
             const int key = i * kGroups + r;
             if (key < n) {
               const float p = sc[s0 + key];
-              const uint4 vv = *reinterpret_cast<const uint4*>(st + key * (D * 2) + g * 16);
-              const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
+              float vf[kEpl];
+              unpack_row16<KV>(*reinterpret_cast<const uint4*>(st + key * kRowBytes + g * 16), vf);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = unpack2<T>(vw[e]);
-                acc[2 * e] = fmaf(p, f.x, acc[2 * e]);
-                acc[2 * e + 1] = fmaf(p, f.y, acc[2 * e + 1]);
-              }
+              for (int e = 0; e < kEpl; ++e) acc[e] = fmaf(p, vf[e], acc[e]);
             }
           }
           __syncwarp();
@@ -566,16 +623,17 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
       consumer_sync();   // previous item's readers of red / warp_scratch are done
       if (lane == 0) warp_scratch[warp] = l_thread;
       {
-        float4* dst = reinterpret_cast<float4*>(red + r * D + g * 8);
-        dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        float4* dst = reinterpret_cast<float4*>(red + r * D + g * kEpl);
+#pragma unroll
+        for (int j = 0; j < kEpl / 4; ++j)
+          dst[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
       }
       consumer_sync();
       if (tid < D) {
         float o = 0.f;
 #pragma unroll 8
         for (int grp = 0; grp < kGroups; ++grp) o += red[grp * D + tid];
-        args.part_o[(long long)item * D + tid] = o;
+        args.part_o[(long long)item * D + tid] = o * args.v_scale;
       } else if (tid == D) {
         float l = 0.f;
 #pragma unroll

@@ -17,7 +17,8 @@ constexpr AttnVariant kAttnVariants[] = {
     {0, 0, 0, 0, 0},
 };
 constexpr int kDecodeCtasPerSm = 2;
-constexpr int kDecodeStages = 3;
+constexpr int kDecodeStages = 3;        // 32-KB stages of a 16-bit K/V cache
+constexpr int kDecodeStagesFp8 = 5;     // 16-KB stages of an 8-bit one
 }  // namespace
 
 const AttnVariant* attn_variants() { return kAttnVariants; }
@@ -138,7 +139,7 @@ void plan_decode(const TfDecodeDesc& d, int sm_count, TfDecodePlan* plan) {
   plan->chunks_per_split = cps;
   plan->kv_chunk = chunk;
   plan->grid = (int32_t)std::min<int64_t>(grid, bh * splits);
-  plan->stages = kDecodeStages;
+  plan->stages = (d.kv_dtype == TF_FP8_E4M3 || d.kv_dtype == TF_FP8_E5M2) ? kDecodeStagesFp8 : kDecodeStages;
   plan->reserved = 0;
   plan->workspace_bytes = (uint64_t)bh * splits * (d.head_dim + 2) * sizeof(float);
 }

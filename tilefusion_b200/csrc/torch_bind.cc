@@ -50,6 +50,27 @@ int dtype_code(const at::Tensor& t) {
   return t.scalar_type() == at::kHalf ? TF_F16 : TF_BF16;
 }
 
+// 8-bit storage code of a K/V tensor, or -1 when it is not an fp8 tensor.
+int fp8_code(const at::Tensor& t) {
+  if (t.scalar_type() == at::kFloat8_e4m3fn) return TF_FP8_E4M3;
+  if (t.scalar_type() == at::kFloat8_e5m2) return TF_FP8_E5M2;
+  return -1;
+}
+
+// K and V either share Q's type or are both the same 8-bit storage type.
+void set_kv_dtype(TfDecodeDesc* d, const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, double k_scale,
+                  double v_scale) {
+  TORCH_CHECK(K.scalar_type() == V.scalar_type() && (K.scalar_type() == Q.scalar_type() || fp8_code(K) >= 0),
+              "K and V must share Q's dtype, or both be float8_e4m3fn or float8_e5m2");
+  if (fp8_code(K) >= 0) {
+    d->kv_dtype = fp8_code(K);
+    d->k_scale = (float)k_scale;
+    d->v_scale = (float)v_scale;
+  } else {
+    TORCH_CHECK(k_scale == 1.0 && v_scale == 1.0, "k_scale / v_scale apply to an 8-bit K/V cache only");
+  }
+}
+
 void check_status(int rc) { TORCH_CHECK(rc == TF_OK, "tilefusion_b200: ", tf_last_error()); }
 
 // Raises if a device-side wait of an EARLIER launch on this device gave up (its
@@ -224,7 +245,7 @@ void flash_attention_bwd(const at::Tensor& Q, const at::Tensor& K, const at::Ten
 }
 
 TfDecodeDesc decode_desc(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, int64_t kv_chunk,
-                         int64_t num_splits, double softmax_scale) {
+                         int64_t num_splits, double softmax_scale, double k_scale = 1.0, double v_scale = 1.0) {
   TORCH_CHECK(Q.is_cuda() && K.is_cuda() && V.is_cuda(), "Q, K and V must be CUDA tensors");
   TORCH_CHECK(Q.dim() == 4 && K.dim() == 4 && V.dim() == 4,
               "Q must be [B, H, 1, D] and K, V must be [B, H, Lk, D]");
@@ -232,12 +253,11 @@ TfDecodeDesc decode_desc(const at::Tensor& Q, const at::Tensor& K, const at::Ten
   TORCH_CHECK(K.sizes() == V.sizes() && K.size(0) == Q.size(0) && K.size(3) == Q.size(3) && K.size(1) >= 1 &&
                   Q.size(1) % K.size(1) == 0,
               "K and V must be [B, H_kv, Lk, D] with H_kv dividing Q's head count");
-  TORCH_CHECK(Q.scalar_type() == K.scalar_type() && Q.scalar_type() == V.scalar_type(),
-              "Q, K and V must share one dtype");
   TORCH_CHECK(Q.stride(3) == 1 && K.stride(3) == 1 && V.stride(3) == 1 &&
                   (K.size(2) <= 1 || (K.stride(2) == K.size(3) && V.stride(2) == V.size(3))),
               "rows of Q, K and V must be contiguous and consecutive keys D elements apart");
   TfDecodeDesc d{};
+  set_kv_dtype(&d, Q, K, V, k_scale, v_scale);
   d.dtype = dtype_code(Q);
   d.batch = (int32_t)Q.size(0);
   d.heads = (int32_t)Q.size(1);
@@ -263,8 +283,9 @@ at::Tensor decode_workspace(const TfDecodeDesc& d, const at::Tensor& like) {
 }
 
 void flash_decoding(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, at::Tensor& O,
-                    at::Tensor& LSE, int64_t kv_chunk, int64_t num_splits, double softmax_scale) {
-  TfDecodeDesc d = decode_desc(Q, K, V, kv_chunk, num_splits, softmax_scale);
+                    at::Tensor& LSE, int64_t kv_chunk, int64_t num_splits, double softmax_scale, double k_scale,
+                    double v_scale) {
+  TfDecodeDesc d = decode_desc(Q, K, V, kv_chunk, num_splits, softmax_scale, k_scale, v_scale);
   TORCH_CHECK(O.is_cuda() && O.scalar_type() == Q.scalar_type() && O.dim() == 4 && O.size(0) == Q.size(0) &&
                   O.size(1) == Q.size(1) && O.size(2) == 1 && O.size(3) == Q.size(3) && O.stride(3) == 1,
               "O must be [B, H, 1, D] with contiguous rows and Q's dtype");
@@ -284,13 +305,12 @@ void flash_decoding(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& 
 // Paged KV cache: K/V pages [num_pages, H_kv, page_size, D], block_table int32 [B, max_pages].
 void flash_decoding_paged(const at::Tensor& Q, const at::Tensor& Kp, const at::Tensor& Vp,
                           const at::Tensor& block_table, int64_t kv_len, at::Tensor& O, at::Tensor& LSE,
-                          int64_t kv_chunk, int64_t num_splits, double softmax_scale) {
+                          int64_t kv_chunk, int64_t num_splits, double softmax_scale, double k_scale,
+                          double v_scale) {
   TORCH_CHECK(Q.is_cuda() && Kp.is_cuda() && Vp.is_cuda() && block_table.is_cuda(), "inputs must be CUDA tensors");
   TORCH_CHECK(Q.dim() == 4 && Q.size(2) == 1, "Q must be [B, H, 1, D]");
   TORCH_CHECK(Kp.dim() == 4 && Kp.sizes() == Vp.sizes() && Kp.size(3) == Q.size(3) && Q.size(1) % Kp.size(1) == 0,
               "K and V pages must be [num_pages, H_kv, page_size, D] with H_kv dividing Q's head count");
-  TORCH_CHECK(Q.scalar_type() == Kp.scalar_type() && Q.scalar_type() == Vp.scalar_type(),
-              "Q, K and V must share one dtype");
   TORCH_CHECK(Q.stride(3) == 1 && Kp.stride(3) == 1 && Vp.stride(3) == 1 && Kp.stride(2) == Kp.size(3) &&
                   Vp.stride(2) == Vp.size(3),
               "rows of Q, K and V must be contiguous and consecutive keys of a page D elements apart");
@@ -304,6 +324,7 @@ void flash_decoding_paged(const at::Tensor& Q, const at::Tensor& Kp, const at::T
                   LSE.numel() == Q.size(0) * Q.size(1),
               "LSE must be a contiguous fp32 CUDA tensor with B*H elements");
   TfDecodeDesc d{};
+  set_kv_dtype(&d, Q, Kp, Vp, k_scale, v_scale);
   d.dtype = dtype_code(Q);
   d.batch = (int32_t)Q.size(0);
   d.heads = (int32_t)Q.size(1);
@@ -329,6 +350,25 @@ void flash_decoding_paged(const at::Tensor& Q, const at::Tensor& Kp, const at::T
   at::Tensor ws = decode_workspace(d, Q);
   check_status(tf_decode(Q.data_ptr(), Kp.data_ptr(), Vp.data_ptr(), O.data_ptr(), LSE.data_ptr<float>(),
                          ws.data_ptr(), (uint64_t)ws.numel() * 4, &d, at::cuda::getCurrentCUDAStream().stream()));
+}
+
+// Bulk conversion between a contiguous fp16/bf16 tensor and a float8 tensor of the same shape.
+void fp8_quantize(const at::Tensor& src, at::Tensor& dst, double factor) {
+  TORCH_CHECK(src.is_cuda() && dst.is_cuda() && src.is_contiguous() && dst.is_contiguous() &&
+                  src.numel() == dst.numel() && fp8_code(dst) >= 0,
+              "src must be a contiguous fp16/bf16 CUDA tensor and dst a contiguous float8 tensor of the same size");
+  const c10::cuda::CUDAGuard guard(src.device());
+  check_status(tf_fp8_quantize(src.data_ptr(), dst.data_ptr(), src.numel(), dtype_code(src), fp8_code(dst),
+                               (float)factor, at::cuda::getCurrentCUDAStream().stream()));
+}
+
+void fp8_dequantize(const at::Tensor& src, at::Tensor& dst, double factor) {
+  TORCH_CHECK(src.is_cuda() && dst.is_cuda() && src.is_contiguous() && dst.is_contiguous() &&
+                  src.numel() == dst.numel() && fp8_code(src) >= 0,
+              "src must be a contiguous float8 CUDA tensor and dst a contiguous fp16/bf16 tensor of the same size");
+  const c10::cuda::CUDAGuard guard(src.device());
+  check_status(tf_fp8_dequantize(src.data_ptr(), dst.data_ptr(), src.numel(), fp8_code(src), dtype_code(dst),
+                                 (float)factor, at::cuda::getCurrentCUDAStream().stream()));
 }
 
 void flash_decoding_partial(const at::Tensor& Q, const at::Tensor& K, const at::Tensor& V, at::Tensor& slot,
@@ -431,12 +471,13 @@ TF_REGISTER_OP(flash_attention_bwd,
 
 TF_REGISTER_OP(flash_decoding,
                "flash_decoding(Tensor Q, Tensor K, Tensor V, Tensor(a!) O, Tensor(b!) LSE, "
-               "int kv_chunk, int num_splits, float softmax_scale) -> ()",
+               "int kv_chunk, int num_splits, float softmax_scale, float k_scale=1.0, float v_scale=1.0) -> ()",
                &flash_decoding);
 
 TF_REGISTER_OP(flash_decoding_paged,
                "flash_decoding_paged(Tensor Q, Tensor K_pages, Tensor V_pages, Tensor block_table, int kv_len, "
-               "Tensor(a!) O, Tensor(b!) LSE, int kv_chunk, int num_splits, float softmax_scale) -> ()",
+               "Tensor(a!) O, Tensor(b!) LSE, int kv_chunk, int num_splits, float softmax_scale, "
+               "float k_scale=1.0, float v_scale=1.0) -> ()",
                &flash_decoding_paged);
 
 TF_REGISTER_OP(flash_decoding_partial,
@@ -458,6 +499,10 @@ TF_REGISTER_OP(flash_decoding_gathered_wait,
                "flash_decoding_gathered_wait(Tensor slots, Tensor flags, int step, Tensor(a!) O, "
                "Tensor(b!) LSE) -> ()",
                &flash_decoding_gathered_wait);
+
+TF_REGISTER_OP(fp8_quantize, "fp8_quantize(Tensor src, Tensor(a!) dst, float factor) -> ()", &fp8_quantize);
+
+TF_REGISTER_OP(fp8_dequantize, "fp8_dequantize(Tensor src, Tensor(a!) dst, float factor) -> ()", &fp8_dequantize);
 
 TF_REGISTER_OP(fused_two_gemms,
                "fused_two_gemms(Tensor A, Tensor B, Tensor C, Tensor(a!) D, "

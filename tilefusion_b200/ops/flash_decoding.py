@@ -20,10 +20,12 @@ class FlashDecoding:
     """Callable holding the chunk size, split count and scale."""
 
     def __init__(self, kv_chunk: int = 512, num_splits: int = 0,
-                 softmax_scale: Optional[float] = None) -> None:
+                 softmax_scale: Optional[float] = None, k_scale: float = 1.0, v_scale: float = 1.0) -> None:
         self.kv_chunk = kv_chunk
         self.num_splits = num_splits
         self.softmax_scale = softmax_scale
+        self.k_scale = k_scale
+        self.v_scale = v_scale
 
     def __call__(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                  block_table: Optional[torch.Tensor] = None,
@@ -32,7 +34,9 @@ class FlashDecoding:
         dividing ``H`` (grouped-query attention when smaller), or -- with
         ``block_table`` (int32 ``[B, max_pages]``) and ``kv_len`` -- a paged cache
         ``[num_pages, H_kv, page_size, D]`` whose page ``block_table[b, i]`` holds keys
-        ``[i * page_size, (i + 1) * page_size)`` of batch entry ``b``.
+        ``[i * page_size, (i + 1) * page_size)`` of batch entry ``b``.  ``key`` / ``value``
+        may be ``torch.float8_e4m3fn`` or ``torch.float8_e5m2`` (one KV head per query
+        head): the cache is read as ``k_scale * key`` and ``v_scale * value``.
 
         Returns ``O [B, H, 1, D]`` and ``LSE [B, H, 1]`` (fp32, natural log).
         """
@@ -47,11 +51,12 @@ class FlashDecoding:
             if kv_len is None:
                 raise ValueError("kv_len is required with a block_table")
             torch.ops.tilefusion.flash_decoding_paged(
-                query, key, value, block_table, kv_len, out, lse, self.kv_chunk, self.num_splits, scale
+                query, key, value, block_table, kv_len, out, lse, self.kv_chunk, self.num_splits, scale,
+                self.k_scale, self.v_scale
             )
             return out, lse
         torch.ops.tilefusion.flash_decoding(
-            query, key, value, out, lse, self.kv_chunk, self.num_splits, scale
+            query, key, value, out, lse, self.kv_chunk, self.num_splits, scale, self.k_scale, self.v_scale
         )
         return out, lse
 
@@ -59,7 +64,8 @@ class FlashDecoding:
 def flash_decoding(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                    kv_chunk: int = 512, num_splits: int = 0,
                    softmax_scale: Optional[float] = None, block_table: Optional[torch.Tensor] = None,
-                   kv_len: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                   kv_len: Optional[int] = None, k_scale: float = 1.0,
+                   v_scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
     """One-query-row attention over a long KV sequence.
 
     Args:
@@ -70,5 +76,6 @@ def flash_decoding(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
         num_splits: partial rows per (batch, head); 0 lets the registry choose.
         softmax_scale: defaults to ``1/sqrt(D)``.
         block_table, kv_len: paged KV cache (``page_size`` a multiple of 128).
+        k_scale, v_scale: dequantisation factors of a ``float8`` cache.
     """
-    return FlashDecoding(kv_chunk, num_splits, softmax_scale)(query, key, value, block_table, kv_len)
+    return FlashDecoding(kv_chunk, num_splits, softmax_scale, k_scale, v_scale)(query, key, value, block_table, kv_len)
