@@ -730,7 +730,8 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
         torch.cuda.empty_cache()
     d.dtype = _cabi.TF_F16 if w["dtype"] == "fp16" else _cabi.TF_BF16
     d.batch, d.heads, d.len_kv, d.head_dim = w["B"], w["H"], w["L"], w["D"]
-    d.kv_chunk, d.num_splits, d.softmax_scale = 512, 0, scale
+    kv_chunk = 512 if "kv" not in w else 0       # 0: the registry's choice (1024 keys for an 8-bit cache)
+    d.kv_chunk, d.num_splits, d.softmax_scale = kv_chunk, 0, scale
     d.q_stride_b, d.q_stride_h = q.stride(0), q.stride(1)
     d.k_stride_b, d.k_stride_h = k.stride(0), k.stride(1)
     d.v_stride_b, d.v_stride_h = v.stride(0), v.stride(1)
@@ -772,7 +773,7 @@ def run_decode(args, w, name, device, rank, world, steps=None, warmup=None):
 
     def e2e_step():
         out, _ = tilefusion.ops.flash_decoding(hq.to(device, non_blocking=True), hk.to(device, non_blocking=True),
-                                               hv.to(device, non_blocking=True), 512, 0, scale)
+                                               hv.to(device, non_blocking=True), kv_chunk, 0, scale)
         ho.copy_(out, non_blocking=True)
 
     e2e_secs, _ = time_steps(e2e_step, e2e_steps, 2, device, world, max_repeats=1)

@@ -97,7 +97,8 @@ typedef struct TfDecodeDesc {
   int32_t len_kv;       /* keys held by THIS call (a shard when KV is split
                            across GPUs); may be 0                             */
   int32_t head_dim;     /* D in {64, 128}                                     */
-  int32_t kv_chunk;     /* keys per chunk, a multiple of 128; 0 -> 512        */
+  int32_t kv_chunk;     /* keys per chunk, a multiple of 128, at most 1024;
+                           0 -> 512 (1024 for an 8-bit cache)                 */
   int32_t num_splits;   /* splits per (b,h); 0 lets the registry choose       */
   float softmax_scale;
   int64_t q_stride_b, q_stride_h;

@@ -187,7 +187,7 @@ def test_decode_plan_for_an_8bit_cache(native_lib):
     for code in (_cabi.TF_FP8_E4M3, _cabi.TF_FP8_E5M2):
         d.kv_dtype = code
         assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == 0
-        assert plan.stages == 5 and plan.workspace_bytes == 4 * 32 * plan.num_splits * 130 * 4
+        assert plan.stages == 3 and plan.workspace_bytes == 4 * 32 * plan.num_splits * 130 * 4
     d.heads_kv = 8
     assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_UNSUPPORTED
     assert "grouped-query" in native_lib.tf_last_error().decode()

@@ -153,16 +153,21 @@ def test_split_partials_over_8bit_cache_match_oracle(kind, lk, chunk, splits, d)
 
 
 def test_scales_default_to_one_and_strided_cache():
-    """k_scale = v_scale = 0 read as 1; K/V heads taken out of a wider buffer (stride_h > Lk*D)."""
+    """k_scale = v_scale = 0 read as 1; kv_chunk = 0 is the registry's choice (1024 keys for an
+    8-bit cache); K/V heads taken out of a wider buffer (stride_h > Lk*D)."""
     from cabi_helpers import decode
 
-    b, h, lk, d = 2, 4, 900, 128
+    from cabi_helpers import decode_desc, decode_plan
+
+    b, h, lk, d = 2, 4, 2900, 128
     q, k8, v8, k_exact, v_exact = _cache(35, b, h, lk, d, f8.E4M3, torch.float16)
+    assert decode_plan(decode_desc(q, k8, v8, kv_chunk=0)).kv_chunk == 1024
+    assert decode_plan(decode_desc(q, q, q, kv_chunk=0)).kv_chunk == 512
     wide_k = torch.zeros(b, h, lk + 28, d, dtype=torch.uint8).view(torch.float8_e4m3fn)
     wide_v = torch.zeros_like(wide_k)
     wide_k[:, :, :lk] = k8
     wide_v[:, :, :lk] = v8
-    o, lse = decode(q.cuda(), wide_k.cuda()[:, :, :lk], wide_v.cuda()[:, :, :lk])
+    o, lse = decode(q.cuda(), wide_k.cuda()[:, :, :lk], wide_v.cuda()[:, :, :lk], kv_chunk=0)
     ref, lse_ref = orc.decode_fp32(q, k_exact, v_exact)
     _check(o, lse, ref, lse_ref, torch.float16)
 

@@ -429,7 +429,7 @@ int check_decode_desc(const TfDecodeDesc* d) {
     return fail(TF_ERR_UNSUPPORTED, "head_dim %d has no compiled variant (64 and 128 do)", d->head_dim);
   if (!(d->softmax_scale > 0.f) || !std::isfinite(d->softmax_scale))
     return fail(TF_ERR_UNSUPPORTED, "softmax_scale must be positive and finite");
-  const int chunk = d->kv_chunk == 0 ? 512 : d->kv_chunk;
+  const int chunk = d->kv_chunk == 0 ? tfb::default_kv_chunk(*d) : d->kv_chunk;
   if (chunk < 128 || chunk % 128 != 0 || chunk > tfb::kDecMaxChunk)
     return fail(TF_ERR_UNSUPPORTED, "kv_chunk must be a multiple of 128 in [128, %d] (got %d)", tfb::kDecMaxChunk, chunk);
   if (d->num_splits < 0) return fail(TF_ERR_BAD_ARG, "num_splits must be >= 0");
@@ -471,15 +471,15 @@ int check_decode_desc(const TfDecodeDesc* d) {
 
 bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
-// KV: the stored K/V element (T itself, or an 8-bit tag).  Two CTAs share an SM,
-// so a CTA's ring is three 32-KB stages of a 16-bit cache or five 16-KB stages
-// of an 8-bit one (whose cross-group reduction buffer is twice as large).
+// KV: the stored K/V element (T itself, or an 8-bit tag).  Two CTAs share an SM;
+// a CTA's ring is three stages of 256 * D bytes (128 keys of a 16-bit cache, 256
+// of an 8-bit one).
 template <typename T, typename KV, int D>
 int launch_decode_split(const void* q, const void* k, const void* v, float* part_o, float* part_ml,
                         const TfDecodeDesc* d, const TfDecodePlan& plan, cudaStream_t stream,
                         const tfb::DecodeFuseArgs* fuse = nullptr) {
   constexpr int kKvBytes = tfb::KvBytes<KV>::value;
-  constexpr int kStages = kKvBytes == 2 ? 3 : 5;
+  constexpr int kStages = 3;
   using Smem = tfb::DecodeSmem<D, kStages, kKvBytes>;
   tfb::DecodeSplitArgs a;
   a.fuse = fuse != nullptr ? *fuse : tfb::DecodeFuseArgs{};

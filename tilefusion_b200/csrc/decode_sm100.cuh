@@ -45,10 +45,11 @@
 // 8-bit K/V (OCP e4m3 / e5m2 storage, the types TileFusion declares in
 // include/types/base.hpp:13-39 and only converts, tests/cpp/types/test_fp8.cu):
 // the KV template parameter selects the stored element.  The byte stream per key
-// halves, a lane still reads 16 bytes of a row (16 head dims instead of 8), the
-// ring holds twice as many 128-key stages of half the size, and the elements are
-// widened e4m3/e5m2 -> f16x2 -> fp32 in registers; q, the scores, the softmax
-// and the accumulators stay fp32.  Per-tensor dequantisation factors fold into
+// halves, a lane still reads 16 bytes of a row (16 head dims instead of 8), a
+// stage keeps its size and holds 256 keys instead of 128 (so the per-stage
+// barrier and shuffle work is spread over as many bytes as before), and the
+// elements are widened e4m3/e5m2 -> f16x2 -> fp32 in registers; q, the scores,
+// the softmax and the accumulators stay fp32.  Per-tensor dequantisation factors fold into
 // the score scale (K) and into the partial row as it is written (V).
 #pragma once
 
@@ -60,7 +61,8 @@
 
 namespace tfb {
 
-constexpr int kDecKeysPerStage = 128;
+constexpr int kDecStageRows = 128;        // keys of a 16-bit cache per stage; an 8-bit cache takes twice as many
+                                          // (one stage is 256 * D bytes either way); also the paging granule
 constexpr int kDecConsumerThreads = 256;
 constexpr int kDecThreads = kDecConsumerThreads + 64;   // + producer warp + merger warp
 constexpr int kDecDoneSlots = 8;                        // items the consumers may be ahead of the merger
@@ -163,12 +165,12 @@ struct DecodeSplitArgs {
 
 template <int D, int kStages, int kKvBytes = 2>
 struct DecodeSmem {
-  static constexpr int kStageBytes = kDecKeysPerStage * D * kKvBytes;
+  static constexpr int kKeysPerStage = kDecStageRows * 2 / kKvBytes;
+  static constexpr int kStageBytes = kKeysPerStage * D * kKvBytes;
   static constexpr int kOffStages = 0;
   static constexpr int kOffScores = kStages * kStageBytes;              // 2 x kDecMaxChunk fp32
-  static constexpr int kOffRed = kOffScores + 2 * kDecMaxChunk * 4;     // [groups][D] fp32
-  static constexpr int kGroups = kDecConsumerThreads / (D * kKvBytes / 16);
-  static constexpr int kOffWarp = kOffRed + kGroups * D * 4;            // 16 fp32 scratch
+  static constexpr int kOffRed = kOffScores + 2 * kDecMaxChunk * 4;     // [consumer warps][D] fp32
+  static constexpr int kOffWarp = kOffRed + (kDecConsumerThreads / 32) * D * 4;   // 16 fp32 scratch
   static constexpr int kOffBar = kOffWarp + 64;                         // 2*kStages mbarriers
   static constexpr int kOffDone = kOffBar + 2 * kStages * 8;            // kDecDoneSlots "item written" + as many "slot free" mbarriers
   static constexpr int kOffAbort = kOffDone + 2 * kDecDoneSlots * 8;    // abort flag, then the gave-up flag of the final phase
@@ -221,8 +223,10 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
   constexpr int kEpl = 16 / kKvBytes;                  // head dims per lane (16 B of a row)
   constexpr int kLpr = D / kEpl;                       // lanes per key row
   constexpr int kGroups = kDecConsumerThreads / kLpr;  // key rows read per step
-  constexpr int kKpt = kDecKeysPerStage / kGroups;     // keys per thread per stage
+  constexpr int kKps = S::kKeysPerStage;               // keys per stage
+  constexpr int kKpt = kKps / kGroups;                 // keys per thread per stage
   static_assert(kKpt == 8 || kKpt == 4 || kKpt == 2, "unexpected keys per thread");
+
   static_assert(kLpr >= kKpt, "butterfly needs at least kKpt lanes per row");
 
   extern __shared__ uint8_t smem_raw[];
@@ -412,23 +416,29 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
           const int c1 = min(key_end, c0 + chunk);
           for (int pass = 0; ok && pass < 2; ++pass) {
             const uint8_t* base = pass == 0 ? kbase : vbase;
-            for (int s0 = c0; s0 < c1; s0 += kDecKeysPerStage) {
-              const int n = min(kDecKeysPerStage, c1 - s0);
+            for (int s0 = c0; s0 < c1; s0 += kKps) {
+              const int n = min(kKps, c1 - s0);
               if (issued >= kStages) {
                 ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, kWaitDecEmpty);
                 if (!ok) break;
               }
               const uint32_t bytes = uint32_t(n) * kRowBytes;
               mbar_arrive_expect_tx(bar_full + stage * 8, bytes);
-              // a 128-key stage never straddles a page (page_size is a multiple of 128)
-              const uint8_t* src = base + (long long)s0 * kRowBytes;
-              if (paged) {
-                const int pg = s0 / args.page_size;
-                src = base + (long long)pages[pg] * (pass == 0 ? args.k_stride_page : args.v_stride_page) * kKvBytes +
-                      (long long)(s0 - pg * args.page_size) * kRowBytes;
+              const uint32_t dst = smem_base + S::kOffStages + stage * S::kStageBytes;
+              if (!paged) {
+                tma_load_1d(dst, base + (long long)s0 * kRowBytes, bytes, bar_full + stage * 8, policy);
+              } else {
+                // one copy per 128-key granule: s0 is a multiple of 128 and so is page_size, so a
+                // granule never straddles a page (a 256-key stage of an 8-bit cache may)
+                const long long page_stride = (pass == 0 ? args.k_stride_page : args.v_stride_page) * kKvBytes;
+                for (int u0 = 0; u0 < n; u0 += kDecStageRows) {
+                  const int key = s0 + u0;
+                  const int pg = key / args.page_size;
+                  tma_load_1d(dst + u0 * kRowBytes,
+                              base + (long long)pages[pg] * page_stride + (long long)(key - pg * args.page_size) * kRowBytes,
+                              uint32_t(min(kDecStageRows, n - u0)) * kRowBytes, bar_full + stage * 8, policy);
+                }
               }
-              tma_load_1d(smem_base + S::kOffStages + stage * S::kStageBytes, src, bytes,
-                          bar_full + stage * 8, policy);
               ++issued;
               if (++stage == kStages) {
                 stage = 0;
@@ -490,6 +500,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
             const float2 f = unpack2<T>(qw[i]);
             qf[j * 8 + 2 * i] = f.x * args.scale_log2;
             qf[j * 8 + 2 * i + 1] = f.y * args.scale_log2;
+
           }
         }
       }
@@ -507,24 +518,35 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
         float* sc = scores + (chunk_idx & 1) * kDecMaxChunk;
 
         // ---- scores of this chunk ----
-        for (int s0 = 0; s0 < n_chunk; s0 += kDecKeysPerStage) {
-          const int n = min(kDecKeysPerStage, n_chunk - s0);
+        for (int s0 = 0; s0 < n_chunk; s0 += kKps) {
+          const int n = min(kKps, n_chunk - s0);
           ok = __all_sync(0xffffffffu,
                           mbar_wait(bar_full + stage * 8, phase, abort_flag, kWaitDecFullK));
           if (!ok) break;
-          const uint8_t* st = smem_gen + S::kOffStages + stage * S::kStageBytes;
+          const uint8_t* st = smem_gen + S::kOffStages + stage * S::kStageBytes + r * kRowBytes + g * 16;
+          // this thread's kKpt rows first (all loads in flight together), then the arithmetic
+          uint4 raw[kKpt];
+          if (n == kKps) {
+#pragma unroll
+            for (int i = 0; i < kKpt; ++i) raw[i] = *reinterpret_cast<const uint4*>(st + i * kGroups * kRowBytes);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kKpt; ++i)
+              raw[i] = i * kGroups + r < n ? *reinterpret_cast<const uint4*>(st + i * kGroups * kRowBytes)
+                                           : make_uint4(0u, 0u, 0u, 0u);
+          }
           float part[kKpt];
 #pragma unroll
           for (int i = 0; i < kKpt; ++i) {
-            const int key = i * kGroups + r;
-            float d = 0.f;
-            if (key < n) {
-              float kf[kEpl];
-              unpack_row16<KV>(*reinterpret_cast<const uint4*>(st + key * kRowBytes + g * 16), kf);
+            float d0 = 0.f, d1 = 0.f;          // two chains: half the dependent latency
+            float kf[kEpl];
+            unpack_row16<KV>(raw[i], kf);
 #pragma unroll
-              for (int e = 0; e < kEpl; ++e) d = fmaf(kf[e], qf[e], d);
+            for (int e = 0; e < kEpl; e += 2) {
+              d0 = fmaf(kf[e], qf[e], d0);
+              d1 = fmaf(kf[e + 1], qf[e + 1], d1);
             }
-            part[i] = d;
+            part[i] = d0 + d1;
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_empty + stage * 8);
@@ -589,22 +611,35 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
         consumer_sync();
 
         // ---- O += P V ----
-        for (int s0 = 0; s0 < n_chunk; s0 += kDecKeysPerStage) {
-          const int n = min(kDecKeysPerStage, n_chunk - s0);
+        for (int s0 = 0; s0 < n_chunk; s0 += kKps) {
+          const int n = min(kKps, n_chunk - s0);
           ok = __all_sync(0xffffffffu,
                           mbar_wait(bar_full + stage * 8, phase, abort_flag, kWaitDecFullV));
           if (!ok) break;
-          const uint8_t* st = smem_gen + S::kOffStages + stage * S::kStageBytes;
+          const uint8_t* st = smem_gen + S::kOffStages + stage * S::kStageBytes + r * kRowBytes + g * 16;
+          uint4 raw[kKpt];
+          float pk[kKpt];
+          if (n == kKps) {
+#pragma unroll
+            for (int i = 0; i < kKpt; ++i) {
+              raw[i] = *reinterpret_cast<const uint4*>(st + i * kGroups * kRowBytes);
+              pk[i] = sc[s0 + i * kGroups + r];
+            }
+          } else {
+            // rows past the end of the chunk hold stale bytes: they enter as zero weight times zero
+#pragma unroll
+            for (int i = 0; i < kKpt; ++i) {
+              const bool live = i * kGroups + r < n;
+              raw[i] = live ? *reinterpret_cast<const uint4*>(st + i * kGroups * kRowBytes) : make_uint4(0u, 0u, 0u, 0u);
+              pk[i] = live ? sc[s0 + i * kGroups + r] : 0.f;
+            }
+          }
 #pragma unroll
           for (int i = 0; i < kKpt; ++i) {
-            const int key = i * kGroups + r;
-            if (key < n) {
-              const float p = sc[s0 + key];
-              float vf[kEpl];
-              unpack_row16<KV>(*reinterpret_cast<const uint4*>(st + key * kRowBytes + g * 16), vf);
+            float vf[kEpl];
+            unpack_row16<KV>(raw[i], vf);
 #pragma unroll
-              for (int e = 0; e < kEpl; ++e) acc[e] = fmaf(p, vf[e], acc[e]);
-            }
+            for (int e = 0; e < kEpl; ++e) acc[e] = fmaf(pk[i], vf[e], acc[e]);
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_empty + stage * 8);
@@ -620,10 +655,16 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
 #pragma unroll
       for (int off = 16; off >= 1; off >>= 1)
         l_thread += __shfl_xor_sync(0xffffffffu, l_thread, off);
+      // the key groups of a warp (lanes kLpr apart own the same dims) first, then the warps through shared memory
+#pragma unroll
+      for (int off = kLpr; off < 32; off <<= 1) {
+#pragma unroll
+        for (int e = 0; e < kEpl; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+      }
       consumer_sync();   // previous item's readers of red / warp_scratch are done
       if (lane == 0) warp_scratch[warp] = l_thread;
-      {
-        float4* dst = reinterpret_cast<float4*>(red + r * D + g * kEpl);
+      if (lane < kLpr) {
+        float4* dst = reinterpret_cast<float4*>(red + warp * D + lane * kEpl);
 #pragma unroll
         for (int j = 0; j < kEpl / 4; ++j)
           dst[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
@@ -631,8 +672,8 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
       consumer_sync();
       if (tid < D) {
         float o = 0.f;
-#pragma unroll 8
-        for (int grp = 0; grp < kGroups; ++grp) o += red[grp * D + tid];
+#pragma unroll
+        for (int w = 0; w < kDecConsumerThreads / 32; ++w) o += red[w * D + tid];
         args.part_o[(long long)item * D + tid] = o * args.v_scale;
       } else if (tid == D) {
         float l = 0.f;

@@ -33,6 +33,9 @@ int head_dim_bucket(int head_dim, int head_dim_v);
 void plan_attn(const TfAttnDesc& desc, int sm_count, TfAttnPlan* plan);
 void plan_decode(const TfDecodeDesc& desc, int sm_count, TfDecodePlan* plan);
 
+// Keys per chunk when the descriptor leaves kv_chunk at 0: 512, or 1024 for an 8-bit cache.
+int default_kv_chunk(const TfDecodeDesc& desc);
+
 // Which work-item counter word a launch of the two-tile kernel uses (one table
 // per device).  The kernel's CTAs draw item numbers from the word, so two
 // launches that may run at the same time must never share one:

@@ -19,7 +19,7 @@ __all__ = ["FlashDecoding", "flash_decoding"]
 class FlashDecoding:
     """Callable holding the chunk size, split count and scale."""
 
-    def __init__(self, kv_chunk: int = 512, num_splits: int = 0,
+    def __init__(self, kv_chunk: int = 0, num_splits: int = 0,
                  softmax_scale: Optional[float] = None, k_scale: float = 1.0, v_scale: float = 1.0) -> None:
         self.kv_chunk = kv_chunk
         self.num_splits = num_splits
@@ -62,7 +62,7 @@ class FlashDecoding:
 
 
 def flash_decoding(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
-                   kv_chunk: int = 512, num_splits: int = 0,
+                   kv_chunk: int = 0, num_splits: int = 0,
                    softmax_scale: Optional[float] = None, block_table: Optional[torch.Tensor] = None,
                    kv_len: Optional[int] = None, k_scale: float = 1.0,
                    v_scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -72,7 +72,8 @@ def flash_decoding(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
         query: ``[B, H, 1, D]``.
         key, value: ``[B, H_kv, Lk, D]``, rows contiguous (``H_kv`` divides ``H``); or
             pages ``[num_pages, H_kv, page_size, D]`` when ``block_table`` is given.
-        kv_chunk: keys per chunk (multiple of 128, at most 1024).
+        kv_chunk: keys per chunk (multiple of 128, at most 1024); 0: 512, or 1024 for a
+            ``float8`` cache.
         num_splits: partial rows per (batch, head); 0 lets the registry choose.
         softmax_scale: defaults to ``1/sqrt(D)``.
         block_table, kv_len: paged KV cache (``page_size`` a multiple of 128).

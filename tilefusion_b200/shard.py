@@ -97,13 +97,15 @@ class ShardedDecoder:
     def __init__(self, batch: int, heads: int, head_dim: int, dtype: torch.dtype, device,
                  group=None, kv_chunk: int = 512, num_splits: int = 0,
                  partial_fn: Optional[Callable] = None,
-                 gathered_fn: Optional[Callable] = None, transport: Optional[str] = None) -> None:
+                 gathered_fn: Optional[Callable] = None, transport: Optional[str] = None,
+                 k_scale: float = 1.0, v_scale: float = 1.0) -> None:
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.batch, self.heads, self.head_dim = batch, heads, head_dim
         self.dtype = dtype
         self.kv_chunk, self.num_splits = kv_chunk, num_splits
+        self.k_scale, self.v_scale = k_scale, v_scale     # dequantisation factors of a float8 cache
         self.slot_floats = batch * heads * (head_dim + 2)
         self._partial, self._gathered = partial_fn, gathered_fn
         self._ctx = None
@@ -167,8 +169,9 @@ class ShardedDecoder:
                  softmax_scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
                  lse: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """``query [B, H, 1, D]`` (replicated), ``key_local``/``value_local``
-        ``[B, H_kv, Lk_local, D]``.  Returns ``O [B, H, 1, D]`` and ``LSE [B, H, 1]``
-        on every rank."""
+        ``[B, H_kv, Lk_local, D]`` in the query's dtype, or ``float8_e4m3fn`` /
+        ``float8_e5m2`` with ``H_kv == H`` (read as ``k_scale * key``, ``v_scale * value``).
+        Returns ``O [B, H, 1, D]`` and ``LSE [B, H, 1]`` on every rank."""
         scale = 1.0 / math.sqrt(self.head_dim) if softmax_scale is None else softmax_scale
         if out is None:
             out = torch.empty(self.batch, self.heads, 1, self.head_dim, dtype=self.dtype, device=query.device)
@@ -189,6 +192,9 @@ class ShardedDecoder:
         d.heads_kv = key_local.size(1)
         d.len_kv = key_local.size(2)
         d.kv_chunk, d.num_splits, d.softmax_scale = self.kv_chunk, self.num_splits, scale
+        fp8 = {torch.float8_e4m3fn: _cabi.TF_FP8_E4M3, torch.float8_e5m2: _cabi.TF_FP8_E5M2}.get(key_local.dtype)
+        if fp8 is not None:
+            d.kv_dtype, d.k_scale, d.v_scale = fp8, self.k_scale, self.v_scale
         d.q_stride_b, d.q_stride_h = query.stride(0), query.stride(1)
         d.k_stride_b, d.k_stride_h = key_local.stride(0), key_local.stride(1)
         d.v_stride_b, d.v_stride_h = value_local.stride(0), value_local.stride(1)
