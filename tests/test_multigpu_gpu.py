@@ -48,6 +48,21 @@ try:
         torch.cuda.synchronize()
         dist.barrier()          # no rank frees its gather buffer while a peer may still store into it
         dec.close()
+    # the same step over an e4m3 cache: every rank holds its shard in 8 bits
+    from oracle import fp8_oracle as f8
+    k8, v8 = f8.quantize(k, f8.E4M3, 2.0), f8.quantize(v, f8.E4M3, 2.0)
+    ref8, lse_ref8 = orc.decode_fp32(q, f8.decode(k8, f8.E4M3) * 0.5, f8.decode(v8, f8.E4M3) * 0.5)
+    kd8 = k8[:, :, k0:k1].contiguous().view(torch.float8_e4m3fn).to(dev)
+    vd8 = v8[:, :, k0:k1].contiguous().view(torch.float8_e4m3fn).to(dev)
+    dec = ShardedDecoder(b, h, d, torch.float16, dev, kv_chunk=0, k_scale=0.5, v_scale=0.5)
+    for _ in range(3):
+        o, lse = dec(qd, kd8, vd8)
+    if not (orc.max_abs(o.cpu(), ref8) <= 2e-2 and orc.rel_l2(o.cpu(), ref8) <= 1e-3 and
+            orc.max_abs(lse.cpu(), lse_ref8) <= 1e-3):
+        failures.append("decode over an 8-bit cache")
+    torch.cuda.synchronize()
+    dist.barrier()
+    dec.close()
     # a shard may be empty: 300 keys over `world` ranks in blocks of 128
     lk2 = 300
     q3, k3, v3 = orc.seeded_inputs(53, (b, h, 1, d), (b, h, lk2, d), (b, h, lk2, d), 1.0)
