@@ -372,7 +372,8 @@ int launch_attn_bwd(const void* q, const void* k, const void* v, const void* o, 
   da.o_stride_b = da.do_stride_b = d->o_stride_b;
   da.o_stride_h = da.do_stride_h = d->o_stride_h;
   da.o_stride_l = da.do_stride_l = d->o_stride_l;
-  tfb::attn_bwd_delta_kernel<T, D><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(da);
+  constexpr int kDeltaRows = tfb::BwdDeltaShape<D>::kRowsPerBlock;
+  tfb::attn_bwd_delta_kernel<T, D><<<(unsigned)((rows + kDeltaRows - 1) / kDeltaRows), tfb::kBwdDeltaThreads, 0, stream>>>(da);
   TF_CUDA_TRY(cudaGetLastError());
 
   tfb::AttnBwdArgs a;

@@ -11,7 +11,7 @@
 //   dV = P^T dO          dP = dO V^T          delta_i = sum_d dO_id O_id
 //   dS = P o (dP - delta) * s          dQ = dS K          dK = dS^T Q
 // Three kernels:
-//   attn_bwd_delta_kernel   delta rows (fp32), one warp per query row;
+//   attn_bwd_delta_kernel   delta rows (fp32), D / 8 lanes per query row;
 //   attn_bwd_dkv_kernel     one CTA per 128-key tile, loops over the query tiles:
 //                           S^T = K Q^T and dP^T = V dO^T into tensor memory
 //                           (keys on the 128 lanes), threads turn them into P^T
@@ -67,33 +67,38 @@ struct AttnBwdDeltaArgs {
   long long do_stride_b, do_stride_h, do_stride_l;
 };
 
-// delta[b, h, i] = sum_d O[b, h, i, d] * dO[b, h, i, d]; one warp per row.
+// delta[b, h, i] = sum_d O[b, h, i, d] * dO[b, h, i, d]; D / 8 lanes per row, 16 bytes per lane and tensor.
+constexpr int kBwdDeltaThreads = 256;
+template <int D>
+struct BwdDeltaShape {
+  static constexpr int kRowsPerBlock = kBwdDeltaThreads / (D / 8);
+};
+
 template <typename T, int D>
-__global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const AttnBwdDeltaArgs a) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= a.rows) return;
-  const int lane = threadIdx.x & 31;
-  const long long bh = row / a.len_q;
-  const int i = (int)(row - bh * a.len_q);
-  const int b = (int)(bh / a.heads), h = (int)(bh - (long long)b * a.heads);
-  const T* o = reinterpret_cast<const T*>(a.o) + b * a.o_stride_b + h * a.o_stride_h + i * a.o_stride_l;
-  const T* g = reinterpret_cast<const T*>(a.d_o) + b * a.do_stride_b + h * a.do_stride_h + i * a.do_stride_l;
-  constexpr int kPerLane = D / 32;          // 2 or 4 elements
+__global__ void __launch_bounds__(kBwdDeltaThreads) attn_bwd_delta_kernel(const AttnBwdDeltaArgs a) {
+  constexpr int kLanes = D / 8;             // 16 (D = 128) or 8 (D = 64) lanes share a row
+  const long long row = (long long)blockIdx.x * BwdDeltaShape<D>::kRowsPerBlock + threadIdx.x / kLanes;
+  const int part = threadIdx.x % kLanes;
   float acc = 0.f;
-  if constexpr (kPerLane == 4) {
-    const uint2 x = *reinterpret_cast<const uint2*>(o + lane * 4);
-    const uint2 y = *reinterpret_cast<const uint2*>(g + lane * 4);
-    const float2 x0 = unpack2<T>(x.x), x1 = unpack2<T>(x.y), y0 = unpack2<T>(y.x), y1 = unpack2<T>(y.y);
-    acc = x0.x * y0.x + x0.y * y0.y + x1.x * y1.x + x1.y * y1.y;
-  } else {
-    const uint32_t x = *reinterpret_cast<const uint32_t*>(o + lane * 2);
-    const uint32_t y = *reinterpret_cast<const uint32_t*>(g + lane * 2);
-    const float2 x0 = unpack2<T>(x), y0 = unpack2<T>(y);
-    acc = x0.x * y0.x + x0.y * y0.y;
+  if (row < a.rows) {
+    const long long bh = row / a.len_q;
+    const int i = (int)(row - bh * a.len_q);
+    const int b = (int)(bh / a.heads), h = (int)(bh - (long long)b * a.heads);
+    const T* o = reinterpret_cast<const T*>(a.o) + b * a.o_stride_b + h * a.o_stride_h + i * a.o_stride_l;
+    const T* g = reinterpret_cast<const T*>(a.d_o) + b * a.do_stride_b + h * a.do_stride_h + i * a.do_stride_l;
+    const uint4 x = __ldg(reinterpret_cast<const uint4*>(o + part * 8));
+    const uint4 y = __ldg(reinterpret_cast<const uint4*>(g + part * 8));
+    const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 xf = unpack2<T>(xw[e]), yf = unpack2<T>(yw[e]);
+      acc = fmaf(xf.x, yf.x, acc);
+      acc = fmaf(xf.y, yf.y, acc);
+    }
   }
 #pragma unroll
-  for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) a.delta[row] = acc;
+  for (int off = kLanes / 2; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (part == 0 && row < a.rows) a.delta[row] = acc;
 }
 
 template <int D>
@@ -318,13 +323,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const long long row_base = (long long)batch * args.row_stride_b + (long long)head * args.row_stride_h;
     bool ok = true;
 
-    // dq: this thread's query row keeps its own lse2 / delta
-    float my_lse2 = 0.f, my_delta = 0.f;
+    // dq: this thread's query row keeps its own -lse2 / -delta (as packed pairs)
+    uint64_t my_nlse2 = 0ull, my_ndelta = 0ull;
     if (!kDkv) {
       const bool valid = fixed_idx < args.len_q;
-      my_lse2 = valid ? args.lse[row_base + fixed_idx] * 1.4426950408889634f : INFINITY;
-      my_delta = valid ? args.delta[row_base + fixed_idx] : 0.f;
+      const float l2 = valid ? -args.lse[row_base + fixed_idx] * 1.4426950408889634f : -INFINITY;
+      const float dl = valid ? -args.delta[row_base + fixed_idx] : 0.f;
+      my_nlse2 = f2_pack(l2, l2);
+      my_ndelta = f2_pack(dl, dl);
     }
+    const uint64_t scale_log2_2 = f2_pack(args.scale_log2, args.scale_log2);
+    const uint64_t scale_2 = f2_pack(args.scale, args.scale);
 
     for (int it = 0; it < n; ++it) {
       const int s0 = (first + it) * kAttnTile;              // first streamed row (query for dkv, key for dq)
@@ -334,9 +343,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // lse2 / delta of the streamed queries: one value per thread, shared through shared memory
         const int qi = s0 + row;
         const bool valid = qi < args.len_q;
+        // (stored negated: they enter the arithmetic below as addends, two rows per 64-bit operand)
         if (kChunkStep == 1 || chunk == 0)
-          rows_lse2[row] = valid ? args.lse[row_base + qi] * 1.4426950408889634f : INFINITY;   // P = 0 beyond len_q
-        if (kChunkStep == 1 || chunk == 1) rows_delta[row] = valid ? args.delta[row_base + qi] : 0.f;
+          rows_lse2[row] = valid ? -args.lse[row_base + qi] * 1.4426950408889634f : -INFINITY;   // P = 0 beyond len_q
+        if (kChunkStep == 1 || chunk == 1) rows_delta[row] = valid ? -args.delta[row_base + qi] : 0.f;
         bwd_rows_sync();
       }
       for (int hh = 0; hh < 2; ++hh) {
@@ -345,6 +355,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!ok) break;
         tc_fence_after();
         const uint32_t col_s = b * 128, col_dp = b * 128 + 64;
+        // Only a tile cut by the diagonal (or by the end of the keys) needs the element-wise mask.
+        const bool need_mask = kDkv ? (args.causal && s0 < t0 + kAttnTile)
+                                    : (s0 + kAttnTile > args.len_kv || (args.causal && s0 + kAttnTile - 1 > t0));
 #pragma unroll
         for (int c = chunk; c < 2; c += kChunkStep) {
           uint32_t sr[32], dp[32];
@@ -352,30 +365,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tmem_ld32(t_lane + col_dp + c * 32, dp);
           tmem_wait_ld();
           uint32_t pk[16], dk[16];
+          // Per pair of streamed rows, in packed fp32 pairs:  P = 2^(s * scale_log2 - lse2),
+          // dS = (P * scale) * (dP - delta).
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p[2], ds[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int local = hh * 64 + c * 32 + i + e;     // row of the streamed tile
-              const int col = s0 + local;                     // its global index
-              float lse2, delta;
-              bool masked;
-              if (kDkv) {
-                lse2 = rows_lse2[local];
-                delta = rows_delta[local];
-                masked = args.causal && fixed_idx > col;      // key beyond the query
-              } else {
-                lse2 = my_lse2;
-                delta = my_delta;
-                masked = col >= args.len_kv || (args.causal && col > fixed_idx);
-              }
-              const float pe = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(sr[i + e]), args.scale_log2, -lse2));
-              p[e] = pe;
-              ds[e] = pe * (__uint_as_float(dp[i + e]) - delta) * args.scale;
+          for (int i = 0; i < 32; i += 4) {
+            const int local = hh * 64 + c * 32 + i;           // first of four rows of the streamed tile
+            uint64_t nl[2], nd[2];
+            if (kDkv) {
+              const ulonglong2 l4 = *reinterpret_cast<const ulonglong2*>(rows_lse2 + local);
+              const ulonglong2 d4 = *reinterpret_cast<const ulonglong2*>(rows_delta + local);
+              nl[0] = l4.x; nl[1] = l4.y;
+              nd[0] = d4.x; nd[1] = d4.y;
+            } else {
+              nl[0] = nl[1] = my_nlse2;
+              nd[0] = nd[1] = my_ndelta;
             }
-            pk[i >> 1] = pack2<T>(p[0], p[1]);
-            dk[i >> 1] = pack2<T>(ds[0], ds[1]);
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int j = i + 2 * h2;
+              float x0, x1;
+              f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[j]), __uint_as_float(sr[j + 1])), scale_log2_2, nl[h2]), x0, x1);
+              float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              if (need_mask) {
+                const int col = s0 + local + 2 * h2;          // global index of the first of the two rows
+                const bool m0 = kDkv ? fixed_idx > col : (col >= args.len_kv || (args.causal && col > fixed_idx));
+                const bool m1 = kDkv ? fixed_idx > col + 1 : (col + 1 >= args.len_kv || (args.causal && col + 1 > fixed_idx));
+                p0 = m0 ? 0.f : p0;
+                p1 = m1 ? 0.f : p1;
+              }
+              const uint64_t p2 = f2_pack(p0, p1);
+              float d0, d1;
+              f2_unpack(f2_mul(f2_mul(p2, scale_2),
+                               f2_add(f2_pack(__uint_as_float(dp[j]), __uint_as_float(dp[j + 1])), nd[h2])), d0, d1);
+              pk[j >> 1] = pack2<T>(p0, p1);
+              dk[j >> 1] = pack2<T>(d0, d1);
+            }
           }
           // 16-bit P over S and dS over dP, each thread over the start of the 32 fp32 columns it
           // has just read (so the row's other thread is never disturbed): chunk c lands in
