@@ -36,6 +36,8 @@ bounded sample.
 
 Besides the headline workload the default line carries, at every N:
   decode      decode_c3, one batch per rank
+  decode_fp8  decode_c3 over an e4m3 K/V cache (written on the device by the
+              library's conversion kernel); GB/s count the 8-bit bytes
   decode_c4   long-context decode with the KV length sharded over the N ranks
               (N = 1: the whole sequence on one GPU), both transports, with a
               parity object: every rank evaluates the fp32 expression on its own
@@ -89,6 +91,9 @@ WORKLOADS["decode_c4_profile"] = dict(WORKLOADS["decode_c4"], L=16384)
 # One rank's share of decode_c4 when the KV length is sharded over 8 GPUs.
 WORKLOADS["decode_c4_shard8"] = dict(WORKLOADS["decode_c4"], L=131072 // 8, scaling="weak")
 # fused_two_gemms, D = (A B^T) C^T: the reference's own test case and one GEMM-sized case.
+# the backward pass of the C2 shapes on its own line (and the smaller case an ncu capture takes)
+WORKLOADS["backward_c2"] = dict(WORKLOADS["prefill_c2"], kind="backward")
+WORKLOADS["backward_profile"] = dict(WORKLOADS["backward_c2"], B=4)
 WORKLOADS["two_gemms_ref"] = dict(kind="two_gemms", dtype="fp16", M=256, N=128, K=64, P=64, scaling="weak")
 WORKLOADS["two_gemms"] = dict(kind="two_gemms", dtype="fp16", M=262144, N=8192, K=128, P=128, scaling="weak")
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)   # earlier measurement on this pool
@@ -329,7 +334,8 @@ def run_reference_arm(args, w, name):
 
 
 def metric_name(w):
-    return {"prefill": "prefill_tflops", "decode": "decode_hbm_gbs", "two_gemms": "fused_two_gemms_tflops"}[w["kind"]]
+    return {"prefill": "prefill_tflops", "decode": "decode_hbm_gbs", "two_gemms": "fused_two_gemms_tflops",
+            "backward": "backward_tflops"}[w["kind"]]
 
 
 def workload_config(w, name, n_gpus, causal=False):
@@ -339,9 +345,9 @@ def workload_config(w, name, n_gpus, causal=False):
                        else "plumbing case: everything is L2-resident, launch-latency bound"),
                 "timing": "median of repeated regions of exactly `steps` steps, idle gap between regions"}
     return {"workload": name + ("+causal" if causal else ""), "batch_per_step": w["B"] * (n_gpus if w["scaling"] == "weak" else 1),
-            "heads": w["H"], "len_q": w["L"] if w["kind"] == "prefill" else 1, "len_kv": w["L"],
+            "heads": w["H"], "len_q": w["L"] if w["kind"] in ("prefill", "backward") else 1, "len_kv": w["L"],
             "head_dim": w["D"], "causal": bool(causal), "softmax_scale": "1/sqrt(D)",
-            "sharding": ("batch x heads, no collective" if w["kind"] == "prefill" or w["scaling"] == "weak"
+            "sharding": ("batch x heads, no collective" if w["kind"] in ("prefill", "backward") or w["scaling"] == "weak"
                          else "KV length; (O, m, l) rows exchanged by peer stores inside the decode kernel, "
                               "or by one NCCL all-gather"),
             "l2": "inputs larger than L2 (126 MB); no flush between steps",
@@ -569,7 +575,7 @@ def run_backward(args, w, device, rank, world, steps, warmup):
     lib = _cabi.lib()
     scale = 1.0 / math.sqrt(w["D"])
     stream = torch.cuda.current_stream(device).cuda_stream
-    q, k, v = make_inputs(dict(w, seed=w["seed"] + 1000 * rank), device)
+    q, k, v = make_inputs(dict(w, kind="prefill", seed=w["seed"] + 1000 * rank), device)
     g = torch.Generator(device=device).manual_seed(w["seed"] + 77 + 1000 * rank)
     d_o = (torch.randn(q.shape, generator=g, device=device) * w["sigma"]).to(q.dtype)
     o = torch.empty_like(q)
@@ -596,6 +602,8 @@ def run_backward(args, w, device, rank, world, steps, warmup):
                          "flops_counted": "10*B*H*Lq*Lk*D (2.5 x forward); the kernels execute 14 (S and dP are "
                                           "recomputed by the dQ kernel)",
                          "peak_source": pk["source"] + " (burst cuBLAS bf16)"})
+    if args.profile:
+        return res
     # parity of one head: gradient of the fp32 expression by torch.autograd on the device
     qh, kh, vh = (t[0, 0].float().detach().requires_grad_(True) for t in (q, k, v))
     ref, _ = gpu_attention_fp32(qh, kh, vh, scale, False)
@@ -879,6 +887,8 @@ def main():
         res = run_prefill(args, w, args.workload, device, rank, world, causal=args.causal)
     elif w["kind"] == "two_gemms":
         res = run_two_gemms(args, w, device, rank, world)
+    elif w["kind"] == "backward":
+        res = run_backward(args, w, device, rank, world, args.steps, args.warmup)
     else:
         res = run_decode(args, w, args.workload, device, rank, world)
 
@@ -932,7 +942,7 @@ def main():
         bw = run_backward(args, w, device, rank, world, max(5, min(args.steps, 20)), 3)
         line["backward"] = secondary_object("prefill_c2 backward", bw, max(5, min(args.steps, 20)), world)
 
-    if rank == 0 and world == 1 and not args.no_secondary:
+    if rank == 0 and world == 1 and not args.no_secondary and w["kind"] in ("prefill", "decode"):
         line["cpu_baseline"] = cpu_baseline(w)
     if world > 1:
         import torch.distributed as dist
