@@ -94,6 +94,8 @@ WORKLOADS["decode_c4_shard8"] = dict(WORKLOADS["decode_c4"], L=131072 // 8, scal
 # the backward pass of the C2 shapes on its own line (and the smaller case an ncu capture takes)
 WORKLOADS["backward_c2"] = dict(WORKLOADS["prefill_c2"], kind="backward")
 WORKLOADS["backward_profile"] = dict(WORKLOADS["backward_c2"], B=4)
+# not a benchmark of the path: SM clocks per tcgen05.mma for the operand forms the kernels use
+WORKLOADS["mma_rate"] = dict(kind="mma_rate", dtype="fp16", scaling="weak")
 WORKLOADS["two_gemms_ref"] = dict(kind="two_gemms", dtype="fp16", M=256, N=128, K=64, P=64, scaling="weak")
 WORKLOADS["two_gemms"] = dict(kind="two_gemms", dtype="fp16", M=262144, N=8192, K=128, P=128, scaling="weak")
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)   # earlier measurement on this pool
@@ -830,6 +832,34 @@ def run_two_gemms(args, w, device, rank, world):
     return res
 
 
+def run_mma_rate():
+    """Prints one JSON line: SM clocks per M128 K16 tcgen05.mma (fp16 operands, fp32 accumulators), 256
+    issued back to back by one thread on one SM, for the operand forms the kernels use."""
+    import ctypes as C
+
+    from tilefusion_b200 import _cabi
+
+    lib = _cabi.lib()
+    rows = []
+    for n in (64, 128, 256):
+        for a_tmem in (0, 1):
+            for b_mn in (0, 1):
+                for desc32, uniform in ((0, 0), (1, 0), (1, 1)):
+                    best = None
+                    for _ in range(3):
+                        issue, done = C.c_int64(0), C.c_int64(0)
+                        _cabi.check(lib.tf_probe_mma_clocks(a_tmem, n, b_mn, desc32, uniform, 256, C.byref(issue), C.byref(done)))
+                        if best is None or done.value < best[1]:
+                            best = (issue.value, done.value)
+                    rows.append({"n": n, "a": "tmem" if a_tmem else "smem", "b": "mn-major" if b_mn else "k-major",
+                                 "descriptors": "32-bit halves" if desc32 else "64-bit, built per MMA",
+                                 "issuer": "elected lane of a whole warp" if uniform else "lane 0 in a branch",
+                                 "issue_clk_per_mma": best[0] / 256, "complete_clk_per_mma": best[1] / 256,
+                                 "nominal_clk_per_mma": 128 * n * 16 * 2 / 8192})
+    print(json.dumps({"metric": "mma_clocks", "unit": "SM clocks per tcgen05.mma (M128 K16)", "n_mma": 256,
+                      "nominal": "8192 dense fp16 FLOP per clock and SM", "rows": rows}), flush=True)
+
+
 def secondary_object(wname, res, steps, world):
     """Compact form of a secondary workload's result for the default line."""
     obj = {"workload": wname, "value": res["value"], "unit": res["unit"], "value_per_gpu": res["value"] / world,
@@ -883,6 +913,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
+    if w["kind"] == "mma_rate":
+        if rank == 0:
+            run_mma_rate()
+        return
     if w["kind"] == "prefill":
         res = run_prefill(args, w, args.workload, device, rank, world, causal=args.causal)
     elif w["kind"] == "two_gemms":

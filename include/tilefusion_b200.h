@@ -479,6 +479,27 @@ TF_EXPORT int tf_fp8_dequantize(const void* src, void* dst, int64_t n,
                                 int32_t fp8_dtype, int32_t dst_dtype, float factor,
                                 void* stream);
 
+/* ---- measurement --------------------------------------------------------- */
+
+/*
+ * Tensor-pipe time of `n_mma` back-to-back tcgen05.mma (M128, K16, fp16 in,
+ * fp32 accumulate, N = `n` in {64, 128, 256}) issued by one thread on one SM of
+ * the current device: SM clocks until the last one is issued and until all are
+ * complete.  a_from_tmem selects the A operand (0 shared memory, 1 tensor
+ * memory), b_mn_major the layout of B (0: rows along the contraction, 1: rows
+ * along N), desc32 how the issuing thread forms the shared-memory descriptors
+ * (0: a 64-bit descriptor built per MMA, 1: 32-bit low halves advanced by
+ * constants, as the kernels do), uniform_issue whether that thread is alone in
+ * a branch on its lane number (0) or the elected lane of a warp that walks the
+ * loop as a whole (1, as the kernels do).  Computes nothing useful; it exists so that the
+ * per-MMA figures the design notes quote can be re-measured
+ * (bench.py --workload mma_rate).
+ * Synchronous; allocates 16 bytes for the duration of the call.
+ */
+TF_EXPORT int tf_probe_mma_clocks(int32_t a_from_tmem, int32_t n, int32_t b_mn_major,
+                                  int32_t desc32, int32_t uniform_issue, int32_t n_mma,
+                                  int64_t* issue_clocks, int64_t* complete_clocks);
+
 /* Library ABI version (bumped when a struct above changes). */
 TF_EXPORT int tf_abi_version(void);
 

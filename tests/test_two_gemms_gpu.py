@@ -70,3 +70,24 @@ def test_unsupported_widths_are_reported():
     rc = _cabi.lib().tf_fused_two_gemms(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), 64, 64, 264, 264,
                                         _cabi.TF_F16, 264, 264, 264, 264, None)
     assert rc == _cabi.TF_ERR_UNSUPPORTED and "multiples of 8" in _cabi.lib().tf_last_error().decode()
+
+
+def test_mma_probe_reports_plausible_clocks():
+    """tf_probe_mma_clocks: back-to-back M128 K16 MMAs retire no faster than the nominal rate
+    (N / 2 clocks) and within a small multiple of it, for every operand form."""
+    import ctypes as C
+
+    from tilefusion_b200 import _cabi
+
+    lib = _cabi.lib()
+    for n in (64, 128, 256):
+        for a_tmem in (0, 1):
+            for b_mn in (0, 1):
+                for desc32, uniform in ((0, 0), (1, 0), (1, 1)):
+                    issue, done = C.c_int64(0), C.c_int64(0)
+                    _cabi.check(lib.tf_probe_mma_clocks(a_tmem, n, b_mn, desc32, uniform, 256, C.byref(issue), C.byref(done)))
+                    per_mma = done.value / 256
+                    assert 0.9 * n / 2 <= per_mma <= 6 * n, (n, a_tmem, b_mn, desc32, uniform, per_mma)
+                    assert 0 < issue.value <= done.value
+    assert lib.tf_probe_mma_clocks(0, 96, 0, 1, 1, 256, C.byref(issue), C.byref(done)) == _cabi.TF_ERR_BAD_ARG
+    assert lib.tf_probe_mma_clocks(0, 128, 0, 1, 1, 12, C.byref(issue), C.byref(done)) == _cabi.TF_ERR_BAD_ARG

@@ -22,6 +22,7 @@
 #include "decode_sm100.cuh"
 #include "fp8_sm100.cuh"
 #include "internal.h"
+#include "probe_sm100.cuh"
 #include "registry.h"
 #include "tilefusion_b200.h"
 
@@ -1190,6 +1191,30 @@ int tf_fp8_quantize(const void* src, void* dst, int64_t n, int32_t src_dtype, in
 int tf_fp8_dequantize(const void* src, void* dst, int64_t n, int32_t fp8_dtype, int32_t dst_dtype, float factor,
                       void* stream) {
   return convert_fp8(src, dst, n, dst_dtype, fp8_dtype, factor, stream, /*to_fp8=*/false);
+}
+
+int tf_probe_mma_clocks(int32_t a_from_tmem, int32_t n, int32_t b_mn_major, int32_t desc32, int32_t uniform_issue,
+                        int32_t n_mma, int64_t* issue_clocks, int64_t* complete_clocks) {
+  if (n != 64 && n != 128 && n != 256) return fail(TF_ERR_BAD_ARG, "n must be 64, 128 or 256 (got %d)", n);
+  if (n_mma < 8 || n_mma % 8 != 0 || n_mma > (1 << 20))
+    return fail(TF_ERR_BAD_ARG, "n_mma must be a multiple of 8 in [8, 2^20] (got %d)", n_mma);
+  if (issue_clocks == nullptr || complete_clocks == nullptr) return fail(TF_ERR_BAD_ARG, "the outputs must be non-null");
+  if (int rc = tfb::ensure_device_ready()) return rc;
+  long long* dev = nullptr;
+  TF_CUDA_TRY(cudaMalloc(&dev, 2 * sizeof(long long)));
+  tfb::ProbeMmaArgs a{a_from_tmem != 0, n, b_mn_major != 0, desc32 != 0, uniform_issue != 0, n_mma, dev};
+  cudaError_t e = cudaFuncSetAttribute(tfb::probe_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tfb::kProbeSmemBytes);
+  long long host[2] = {0, 0};
+  if (e == cudaSuccess) {
+    tfb::probe_mma_kernel<<<1, 128, tfb::kProbeSmemBytes>>>(a);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemcpy(host, dev, sizeof(host), cudaMemcpyDeviceToHost);    // (synchronises)
+  cudaFree(dev);
+  if (e != cudaSuccess) return fail(TF_ERR_CUDA, "the probe kernel failed: %s", cudaGetErrorString(e));
+  *issue_clocks = host[0];
+  *complete_clocks = host[1];
+  return TF_OK;
 }
 
 int tf_abi_version(void) { return 5; }

@@ -204,12 +204,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == kBwdComputeWarps) {
-    if (lane == 0 && n > 0) {
+    if (n > 0) {
       // ------------------------------------------------ TMA + MMA issuer ----
-      tma_prefetch_desc(&map_q);
-      tma_prefetch_desc(&map_k);
-      tma_prefetch_desc(&map_v);
-      tma_prefetch_desc(&map_do);
+      // The whole warp walks the schedule and one elected lane issues: in warp-uniform code the
+      // descriptors stay in uniform registers and an MMA is issued every ~74 clocks, where a
+      // branch on lane 0 took ~95 per MMA (bench.py --workload mma_rate) -- more than the tensor
+      // pipe needs for the M128 N64 products of this kernel.
+      const bool leader = elect_one();
+      if (leader) {
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        tma_prefetch_desc(&map_do);
+      }
       const CUtensorMap* m_fix0 = kDkv ? &map_k : &map_q;
       const CUtensorMap* m_fix1 = kDkv ? &map_v : &map_do;
       const CUtensorMap* m_str0 = kDkv ? &map_q : &map_k;
@@ -220,26 +227,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tma_load_4d(dst + blk * S::kBlockBytes, map, bar, blk * 64, row0, head, batch);
       };
       auto load_stream = [&](int it) {
+        if (!leader) return;
         const int slot = it & 1;
         mbar_arrive_expect_tx(bar_str + slot * 8, 2 * S::kTileBytes);
         load_tile(sStr0(slot), m_str0, bar_str + slot * 8, (first + it) * kAttnTile);
         load_tile(sStr1(slot), m_str1, bar_str + slot * 8, (first + it) * kAttnTile);
       };
       // All operands are [128 rows][D] tiles, rows 128 B per 64-column block, 128-byte swizzle.
-      // As the K-major operand of a product over D (rows = the tile's own index):
-      auto desc_kmajor = [&](uint32_t tile_smem, int k) {
-        return make_smem_desc(tile_smem + (k >> 2) * S::kBlockBytes + (k & 3) * 32, 16, 1024);
-      };
-      // As the MN-major B operand of a product over the tile's rows (N = D):
-      auto desc_rows = [&](uint32_t tile_smem, int k) {
-        return make_smem_desc(tile_smem + k * 2048, S::kBlockBytes, 1024);
-      };
+      // Descriptors are kept as 32-bit low halves (address and LBO; the high half is the same for all)
+      // and advanced by constants: one thread issues every MMA, and building a 64-bit descriptor per
+      // MMA costs it more clocks (96 per MMA, measured) than the tensor pipe needs for the MMA.
+      //   K-major operand of a product over D (rows = the tile's own index): 32 bytes per K16 step
+      //   within a 64-column block, LBO 16;
+      //   MN-major B operand of a product over the tile's rows (N = D): 16 rows = 2048 bytes per K16
+      //   step, LBO = one 64-column block.
+      auto koff = [](int k) { return (uint32_t)(((k >> 2) * S::kBlockBytes + (k & 3) * 32) >> 4); };
+      const uint32_t fix0_lo = desc_lo(sFix0, 16), fix1_lo = desc_lo(sFix1, 16);
+      const uint32_t str0_k_lo[2] = {desc_lo(sStr0(0), 16), desc_lo(sStr0(1), 16)};
+      const uint32_t str1_k_lo[2] = {desc_lo(sStr1(0), 16), desc_lo(sStr1(1), 16)};
+      const uint32_t str0_r_lo[2] = {desc_lo(sStr0(0), S::kBlockBytes), desc_lo(sStr0(1), S::kBlockBytes)};
+      const uint32_t str1_r_lo[2] = {desc_lo(sStr1(0), S::kBlockBytes), desc_lo(sStr1(1), S::kBlockBytes)};
       const uint32_t idesc_sd = make_idesc(128, 64, kIsBf16, 0, 0);
       const uint32_t idesc_acc = make_idesc(128, D, kIsBf16, 0, 1);
 
-      mbar_arrive_expect_tx(bar_fix, 2 * S::kTileBytes);
-      load_tile(sFix0, m_fix0, bar_fix, t0);
-      load_tile(sFix1, m_fix1, bar_fix, t0);
+      if (leader) {
+        mbar_arrive_expect_tx(bar_fix, 2 * S::kTileBytes);
+        load_tile(sFix0, m_fix0, bar_fix, t0);
+        load_tile(sFix1, m_fix1, bar_fix, t0);
+      }
       load_stream(0);
       if (n > 1) load_stream(1);
 
@@ -254,20 +269,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // The tensor pipe executes in issue order, so P1(u + 2) overwrites buffer u & 1 only after P2(u)
       // has read it.
       const int n_half = 2 * n;
-      bool ok = mbar_wait(bar_fix, 0, abort_flag, kBWaitFixed);
+      bool ok = mbar_wait_warp(bar_fix, 0, abort_flag, kBWaitFixed);
       auto issue_p1 = [&](int u) -> bool {
         const int it = u >> 1, hh = u & 1, slot = it & 1, b = u & 1;
         if (hh == 0) {
-          if (!mbar_wait(bar_str + slot * 8, (it >> 1) & 1, abort_flag, kBWaitStream)) return false;
+          if (!mbar_wait_warp(bar_str + slot * 8, (it >> 1) & 1, abort_flag, kBWaitStream)) return false;
           tc_fence_after();
         }
-        const uint32_t rows = hh * 64 * 128;            // 64 rows of 128 B inside every 64-column block
+        if (!leader) return true;
+        const uint32_t rows = (hh * 64 * 128) >> 4;     // 64 rows of 128 B inside every 64-column block
+        const uint32_t b0 = str0_k_lo[slot] + rows, b1 = str1_k_lo[slot] + rows;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_ss(tmem_base + b * 128, desc_kmajor(sFix0, k), desc_kmajor(sStr0(slot) + rows, k), idesc_sd, k > 0);
+          umma_ss_lohi(tmem_base + b * 128, fix0_lo + koff(k), b0 + koff(k), kDescHiSw128, idesc_sd, k > 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_ss(tmem_base + b * 128 + 64, desc_kmajor(sFix1, k), desc_kmajor(sStr1(slot) + rows, k), idesc_sd, k > 0);
+          umma_ss_lohi(tmem_base + b * 128 + 64, fix1_lo + koff(k), b1 + koff(k), kDescHiSw128, idesc_sd, k > 0);
         umma_commit(bar_s + b * 8);
         return true;
       };
@@ -280,27 +297,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         // the other slot is free once the second pairs of the previous tile have read it
         if (hh == 0 && it >= 1 && it + 1 < n) {
-          ok = mbar_wait(bar_o + (slot ^ 1) * 8, ((it - 1) >> 1) & 1, abort_flag, kBWaitSlot);
+          ok = mbar_wait_warp(bar_o + (slot ^ 1) * 8, ((it - 1) >> 1) & 1, abort_flag, kBWaitSlot);
           if (!ok) break;
           load_stream(it + 1);
         }
-        ok = mbar_wait(bar_p + b * 8, (u >> 1) & 1, abort_flag, kBWaitP);
+        ok = mbar_wait_warp(bar_p + b * 8, (u >> 1) & 1, abort_flag, kBWaitP);
         if (!ok) break;
         tc_fence_after();
+        if (!leader) continue;
+        const uint32_t r0 = str0_r_lo[slot] + ((hh * 4 * 2048) >> 4), r1 = str1_r_lo[slot] + ((hh * 4 * 2048) >> 4);
         if (kDkv) {
 #pragma unroll
           for (int k = 0; k < 4; ++k)      // dV += P^T dO
-            umma_ts(tmem_base + kColAcc0, tmem_base + b * 128 + (k >> 1) * 32 + (k & 1) * 8, desc_rows(sStr1(slot), hh * 4 + k), idesc_acc,
-                    (u > 0) || (k > 0));
+            umma_ts_lohi(tmem_base + kColAcc0, tmem_base + b * 128 + (k >> 1) * 32 + (k & 1) * 8, r1 + ((k * 2048) >> 4),
+                         kDescHiSw128, idesc_acc, (u > 0) || (k > 0));
 #pragma unroll
           for (int k = 0; k < 4; ++k)      // dK += dS^T Q
-            umma_ts(tmem_base + kColAcc1, tmem_base + b * 128 + 64 + (k >> 1) * 32 + (k & 1) * 8, desc_rows(sStr0(slot), hh * 4 + k), idesc_acc,
-                    (u > 0) || (k > 0));
+            umma_ts_lohi(tmem_base + kColAcc1, tmem_base + b * 128 + 64 + (k >> 1) * 32 + (k & 1) * 8, r0 + ((k * 2048) >> 4),
+                         kDescHiSw128, idesc_acc, (u > 0) || (k > 0));
         } else {
 #pragma unroll
           for (int k = 0; k < 4; ++k)      // dQ += dS K
-            umma_ts(tmem_base + kColAcc0, tmem_base + b * 128 + 64 + (k >> 1) * 32 + (k & 1) * 8, desc_rows(sStr0(slot), hh * 4 + k), idesc_acc,
-                    (u > 0) || (k > 0));
+            umma_ts_lohi(tmem_base + kColAcc0, tmem_base + b * 128 + 64 + (k >> 1) * 32 + (k & 1) * 8, r0 + ((k * 2048) >> 4),
+                         kDescHiSw128, idesc_acc, (u > 0) || (k > 0));
         }
         if (hh == 1) umma_commit(bar_o + slot * 8);
       }
