@@ -26,7 +26,10 @@
 // A streamed tile is worked in two halves of 64 rows that alternate between two
 // TMEM buffers, so the element-wise stage of one half runs under the MMAs of its
 // neighbours.  TMEM: two buffers of (S | dP) = 2 x (64 + 64) columns, then dV | dK
-// (D + D columns; dK/dV kernel) or dQ (dQ kernel).
+// (D + D columns; dK/dV kernel) or dQ and, in the columns the dQ kernel has left,
+// copies of its fixed tiles Q and dO as TMEM A operands of the first MMA pair.
+// One warp issues all copies and MMAs (warp-uniform code, one elected lane),
+// eight warps do the element-wise stage.
 // P and dS are rounded to the 16-bit input type before the second MMAs, all
 // accumulation is fp32.  The two kernels recompute S and dP independently (7
 // tile products per tile pair instead of 5), which keeps dQ free of atomics and
@@ -120,9 +123,10 @@ enum AttnBwdWaitCode {
 };
 
 // Element-wise warps: 4 (one thread per row of the fixed tile) or 8 (two threads per row, 32 of the 64
-// streamed columns of a half tile each).  Eight measured no faster (520 against 534 TFLOP/s on the fp16
-// prefill config): the kernels wait for their streamed tiles, not for this stage.
-constexpr int kBwdComputeWarps = 4;
+// streamed columns of a half tile each).  While the MMAs were issued from a branch on lane 0 (95 clocks per
+// MMA) eight were no faster than four (520 against 534 TFLOP/s on the fp16 prefill config); with the
+// warp-uniform issuer they are: 636 against 591.
+constexpr int kBwdComputeWarps = 8;
 constexpr int kBwdThreads = (kBwdComputeWarps + 1) * 32;  // + the TMA / MMA issuer warp
 
 __device__ __forceinline__ void bwd_rows_sync() {
@@ -145,6 +149,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   // Two buffers of (S | dP) for 64 streamed rows each: buffer b has S in columns [128 b, 128 b + 64) and
   // dP in [128 b + 64, 128 b + 128); the accumulators follow.
   constexpr int kColAcc0 = 256, kColAcc1 = 256 + D;
+  // dQ kernel: the accumulator takes D columns only, so the fixed tiles (Q, dO) are copied into the
+  // remaining tensor memory (D / 2 columns each, two 16-bit values per column) and serve as TMEM A
+  // operands of the first MMA pair: 43 instead of 76 clocks per M128 N64 K16 product.
+  constexpr int kColFixA0 = 384, kColFixA1 = 384 + D / 2;
+  constexpr bool kFixedInTmem = !kDkv;
   constexpr int kBlocks = D / 64;
 
   extern __shared__ uint8_t smem_raw[];
@@ -160,6 +169,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t bar_s = smem_base + S::kOffBar + 24;      // [2]  first MMA pair of a half tile is complete (per TMEM buffer)
   const uint32_t bar_p = smem_base + S::kOffBar + 40;      // [2]  P / dS of a half tile are in place (per TMEM buffer)
   const uint32_t bar_o = smem_base + S::kOffBar + 56;      // [2]  second MMA pairs of a streamed tile are complete (per slot)
+  const uint32_t bar_fixt = smem_base + S::kOffBar + 72;   //      (dQ kernel) the fixed tiles are in tensor memory
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kOffTmemSlot);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
 
@@ -191,6 +201,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar_p + 8, kBwdComputeWarps * 32);
     mbar_init(bar_o, 1);
     mbar_init(bar_o + 8, 1);
+    mbar_init(bar_fixt, 128);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -269,7 +280,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // The tensor pipe executes in issue order, so P1(u + 2) overwrites buffer u & 1 only after P2(u)
       // has read it.
       const int n_half = 2 * n;
-      bool ok = mbar_wait_warp(bar_fix, 0, abort_flag, kBWaitFixed);
+      bool ok = kFixedInTmem ? mbar_wait_warp(bar_fixt, 0, abort_flag, kBWaitFixed)
+                             : mbar_wait_warp(bar_fix, 0, abort_flag, kBWaitFixed);
+      if (kFixedInTmem) tc_fence_after();
       auto issue_p1 = [&](int u) -> bool {
         const int it = u >> 1, hh = u & 1, slot = it & 1, b = u & 1;
         if (hh == 0) {
@@ -279,12 +292,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!leader) return true;
         const uint32_t rows = (hh * 64 * 128) >> 4;     // 64 rows of 128 B inside every 64-column block
         const uint32_t b0 = str0_k_lo[slot] + rows, b1 = str1_k_lo[slot] + rows;
+        if (kFixedInTmem) {
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_ss_lohi(tmem_base + b * 128, fix0_lo + koff(k), b0 + koff(k), kDescHiSw128, idesc_sd, k > 0);
+          for (int k = 0; k < D / 16; ++k)
+            umma_ts_lohi(tmem_base + b * 128, tmem_base + kColFixA0 + k * 8, b0 + koff(k), kDescHiSw128, idesc_sd, k > 0);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_ss_lohi(tmem_base + b * 128 + 64, fix1_lo + koff(k), b1 + koff(k), kDescHiSw128, idesc_sd, k > 0);
+          for (int k = 0; k < D / 16; ++k)
+            umma_ts_lohi(tmem_base + b * 128 + 64, tmem_base + kColFixA1 + k * 8, b1 + koff(k), kDescHiSw128, idesc_sd, k > 0);
+        } else {
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k)
+            umma_ss_lohi(tmem_base + b * 128, fix0_lo + koff(k), b0 + koff(k), kDescHiSw128, idesc_sd, k > 0);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k)
+            umma_ss_lohi(tmem_base + b * 128 + 64, fix1_lo + koff(k), b1 + koff(k), kDescHiSw128, idesc_sd, k > 0);
+        }
         umma_commit(bar_s + b * 8);
         return true;
       };
@@ -353,6 +375,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     const uint64_t scale_log2_2 = f2_pack(args.scale_log2, args.scale_log2);
     const uint64_t scale_2 = f2_pack(args.scale, args.scale);
+
+    if (kFixedInTmem && n > 0) {
+      // Q and dO of this CTA's query tile: shared memory (128-byte swizzle: the 16-byte unit u of row r
+      // sits at unit u ^ (r & 7) of its 128-byte row) -> this thread's lane of tensor memory, in the
+      // layout of a 16-bit A operand (two consecutive head dims per column).
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_fix, 0, abort_flag, kBWaitFixed));
+      if (ok && chunk == 0) {
+#pragma unroll
+        for (int f = 0; f < 2; ++f) {
+          const uint8_t* tile_rows = smem_gen + S::kOffFixed + f * S::kTileBytes + row * 128;
+#pragma unroll
+          for (int blk = 0; blk < kBlocks; ++blk) {
+            uint32_t w[32];
+#pragma unroll
+            for (int un = 0; un < 8; ++un) {
+              const uint4 v4 = *reinterpret_cast<const uint4*>(tile_rows + blk * S::kBlockBytes + ((un ^ (row & 7)) << 4));
+              w[4 * un + 0] = v4.x;
+              w[4 * un + 1] = v4.y;
+              w[4 * un + 2] = v4.z;
+              w[4 * un + 3] = v4.w;
+            }
+            tmem_st32(t_lane + (f == 0 ? kColFixA0 : kColFixA1) + blk * 32, w);
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_fixt);
+      }
+    }
 
     for (int it = 0; it < n; ++it) {
       const int s0 = (first + it) * kAttnTile;              // first streamed row (query for dkv, key for dq)
