@@ -785,9 +785,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           }
           return true;
         };
-        // P = 2^(s*scale - m) for 64 keys (chunks 2*half, 2*half + 1) on the MUFU
-        // (an FMA-pipe polynomial for part of the scores measured slower in this
-        // kernel), written as 16-bit over the start of S; returns their sum.
+        // P = 2^(s*scale - m) for 64 keys (chunks 2*half, 2*half + 1), written as 16-bit over the
+        // start of S; returns their sum.  Head dim 128: every exponential on the MUFU (an FMA-pipe
+        // polynomial for 1, 2 or 3 of every 8 pairs measured 3-5 % slower).  Head dim 64, where a
+        // step has half the tensor work under the same exponentials: 2 of every 8 pairs on the
+        // FMA pipe measured 2 % faster (3 of 8 even, 4 of 8 4 % slower).
+        constexpr int kPolyPairsOf8 = D == 64 ? 2 : 0;
         const uint64_t scale2 = f2_pack(args.scale_log2, args.scale_log2);
         auto p_half = [&](int half) -> float {
           const float m_scaled = m_used * args.scale_log2;
@@ -802,8 +805,18 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
               float x0, x1;
               f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, negm2),
                         x0, x1);
-              const float p0 = fast_exp2(x0);
-              const float p1 = fast_exp2(x1);
+              float p0, p1;
+              if constexpr (kPolyPairsOf8 > 0) {
+                if (((i >> 1) & 7) < kPolyPairsOf8) {
+                  poly_exp2_x2(x0, x1, p0, p1);
+                } else {
+                  p0 = fast_exp2(x0);
+                  p1 = fast_exp2(x1);
+                }
+              } else {
+                p0 = fast_exp2(x0);
+                p1 = fast_exp2(x1);
+              }
               ls2[(i >> 1) & 3] = f2_add(ls2[(i >> 1) & 3], f2_pack(p0, p1));
               pk[i >> 1] = pack2<T>(p0, p1);
             }

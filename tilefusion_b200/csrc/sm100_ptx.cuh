@@ -438,6 +438,27 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
+// 2^x for a packed pair on the FMA pipe (no MUFU): x = n + f with |f| <= 0.5 (the magic-number
+// add rounds x to the nearest integer in the low mantissa bits), a degree-3 minimax polynomial for
+// 2^f (relative error 7e-5, below the 16-bit rounding of P), n added into the exponent field.
+// Arguments below -125 are clamped (the result, < 2^-125, counts as zero everywhere it is used).
+__device__ __forceinline__ void poly_exp2_x2(float x0, float x1, float& r0, float& r1) {
+  const uint64_t x2 = f2_pack(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
+  const uint64_t magic = f2_pack(12582912.0f, 12582912.0f);
+  const uint64_t neg_magic = f2_pack(-12582912.0f, -12582912.0f);
+  const uint64_t t2 = f2_add(x2, magic);
+  const uint64_t n2 = f2_add(t2, neg_magic);
+  const uint64_t f2 = f2_fma(n2, f2_pack(-1.0f, -1.0f), x2);
+  uint64_t p2 = f2_fma(f2, f2_pack(0.0551716648f, 0.0551716648f), f2_pack(0.2426111251f, 0.2426111251f));
+  p2 = f2_fma(p2, f2, f2_pack(0.6932609677f, 0.6932609677f));
+  p2 = f2_fma(p2, f2, f2_pack(0.9999280572f, 0.9999280572f));
+  float p0, p1, t0, t1;
+  f2_unpack(p2, p0, p1);
+  f2_unpack(t2, t0, t1);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <>
