@@ -399,6 +399,8 @@ int launch_attn_bwd(const void* q, const void* k, const void* v, const void* o, 
   a.dv_stride_l = d->v_stride_l;
   a.row_stride_b = (long long)d->heads * d->len_q;
   a.row_stride_h = d->len_q;
+  a.heads = d->heads;
+  a.batch = d->batch;
   auto dkv = tfb::attn_bwd_kernel<T, D, true>;
   auto dqk = tfb::attn_bwd_kernel<T, D, false>;
   static thread_local int configured_device = -1;
@@ -411,9 +413,15 @@ int launch_attn_bwd(const void* q, const void* k, const void* v, const void* o, 
   }
   const int n_q_tiles = (d->len_q + tfb::kAttnTile - 1) / tfb::kAttnTile;
   const int n_kv_tiles = (d->len_kv + tfb::kAttnTile - 1) / tfb::kAttnTile;
-  dkv<<<dim3(n_kv_tiles, d->heads, d->batch), tfb::kBwdThreads, Smem::kBytes, stream>>>(mq, mk, mv, mdo, a);
+  // persistent: one CTA per SM (or per work item when there are fewer); the kernels walk the items
+  const long long bh = (long long)d->heads * d->batch;
+  const int live_kv_tiles = d->causal ? std::min(n_kv_tiles, n_q_tiles) : n_kv_tiles;
+  const int sms = sm_count();
+  const int grid_dkv = (int)std::max<long long>(1, std::min<long long>((long long)live_kv_tiles * bh, sms));
+  const int grid_dq = (int)std::max<long long>(1, std::min<long long>((long long)n_q_tiles * bh, sms));
+  dkv<<<grid_dkv, tfb::kBwdThreads, Smem::kBytes, stream>>>(mq, mk, mv, mdo, a);
   TF_CUDA_TRY(cudaGetLastError());
-  dqk<<<dim3(n_q_tiles, d->heads, d->batch), tfb::kBwdThreads, Smem::kBytes, stream>>>(mq, mk, mv, mdo, a);
+  dqk<<<grid_dq, tfb::kBwdThreads, Smem::kBytes, stream>>>(mq, mk, mv, mdo, a);
   TF_CUDA_TRY(cudaGetLastError());
   return TF_OK;
 }

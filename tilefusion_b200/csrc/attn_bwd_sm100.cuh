@@ -12,7 +12,7 @@
 //   dS = P o (dP - delta) * s          dQ = dS K          dK = dS^T Q
 // Three kernels:
 //   attn_bwd_delta_kernel   delta rows (fp32), D / 8 lanes per query row;
-//   attn_bwd_dkv_kernel     one CTA per 128-key tile, loops over the query tiles:
+//   attn_bwd_dkv_kernel     work item = one 128-key tile, loops over the query tiles:
 //                           S^T = K Q^T and dP^T = V dO^T into tensor memory
 //                           (keys on the 128 lanes), threads turn them into P^T
 //                           and dS^T (16-bit, written over the fp32 tiles they
@@ -21,7 +21,7 @@
 //                           and Q tiles in shared memory serve both pairs: as
 //                           K-major B operands of the first and MN-major B
 //                           operands of the second, so nothing is transposed;
-//   attn_bwd_dq_kernel      one CTA per 128-query tile, loops over the key tiles:
+//   attn_bwd_dq_kernel      work item = one 128-query tile, loops over the key tiles:
 //                           S = Q K^T, dP = dO V^T, dS over dP, dQ += dS K.
 // A streamed tile is worked in two halves of 64 rows that alternate between two
 // TMEM buffers, so the element-wise stage of one half runs under the MMAs of its
@@ -29,7 +29,9 @@
 // (D + D columns; dK/dV kernel) or dQ and, in the columns the dQ kernel has left,
 // copies of its fixed tiles Q and dO as TMEM A operands of the first MMA pair.
 // One warp issues all copies and MMAs (warp-uniform code, one elected lane),
-// eight warps do the element-wise stage.
+// eight warps do the element-wise stage.  Both kernels are persistent: one CTA
+// per SM walks the work items, and the barrier phases run on across them, so an
+// item's loads and first MMAs overlap the previous item's epilogue.
 // P and dS are rounded to the 16-bit input type before the second MMAs, all
 // accumulation is fp32.  The two kernels recompute S and dP independently (7
 // tile products per tile pair instead of 5), which keeps dQ free of atomics and
@@ -57,6 +59,8 @@ struct AttnBwdArgs {
   long long dk_stride_b, dk_stride_h, dk_stride_l;
   long long dv_stride_b, dv_stride_h, dv_stride_l;
   long long row_stride_b, row_stride_h;     // of lse and delta
+  int heads;
+  int batch;
 };
 
 struct AttnBwdDeltaArgs {
@@ -113,13 +117,14 @@ struct AttnBwdSmem {
   static constexpr int kOffStream = 2 * kTileBytes;
   static constexpr int kOffRows = 6 * kTileBytes;               // lse2 / delta of the streamed tile: [2][2][128] fp32
   static constexpr int kOffBar = kOffRows + 2 * 2 * kAttnTile * 4;
-  static constexpr int kOffTmemSlot = kOffBar + 80;
-  static constexpr int kOffAbort = kOffBar + 84;
+  static constexpr int kOffTmemSlot = kOffBar + 96;
+  static constexpr int kOffAbort = kOffBar + 100;
   static constexpr int kBytes = kOffBar + 128 + 1024;
 };
 
 enum AttnBwdWaitCode {
-  kBWaitFixed = 501, kBWaitStream = 502, kBWaitS = 503, kBWaitP = 504, kBWaitSlot = 505, kBWaitEpi = 506
+  kBWaitFixed = 501, kBWaitStream = 502, kBWaitS = 503, kBWaitP = 504, kBWaitSlot = 505, kBWaitEpi = 506,
+  kBWaitDrain = 507, kBWaitAcc = 508
 };
 
 // Element-wise warps: 4 (one thread per row of the fixed tile) or 8 (two threads per row, 32 of the 64
@@ -138,6 +143,38 @@ __device__ __forceinline__ void bwd_rows_sync() {
 //                 lanes = keys;   outputs dV (columns 256..) and dK
 //   kDkv = false: fixed = (Q, dO) of query tile `tile`; streamed = (K, V) of key tiles
 //                 lanes = queries; output dQ
+// Persistent: one CTA per SM walks the work items (batch, head, fixed tile) number blockIdx.x,
+// blockIdx.x + gridDim.x, ...; all barrier phases run on across items (counted in streamed tiles and
+// items), so that the loads and the first MMAs of an item are issued while the element-wise warps
+// still write the previous item's gradients out.  Items are head-major (the CTAs running at any
+// moment stream the same few heads); under a causal mask the tiles of a head are taken heaviest
+// first in even heads and lightest first in odd ones, which evens out what a CTA gets.
+struct BwdItem {
+  int tile, head, batch;
+  int first, n;            // streamed tiles visited: [first, first + n), n >= 1
+};
+
+template <bool kDkv>
+__device__ __forceinline__ BwdItem bwd_item_decode(const AttnBwdArgs& args, int item, int n_tiles, int n_q_tiles,
+                                                   int n_kv_tiles) {
+  BwdItem it;
+  const int bh = item / n_tiles;
+  int r = item - bh * n_tiles;
+  if (args.causal && (bh & 1)) r = n_tiles - 1 - r;
+  it.batch = bh / args.heads;
+  it.head = bh - it.batch * args.heads;
+  if (kDkv) {
+    it.tile = r;                                            // key tile 0 is seen by every query tile
+    it.first = args.causal ? it.tile : 0;                   // query tiles above the diagonal see none of these keys
+    it.n = n_q_tiles - it.first;                            // (>= 1: key tiles no query sees are not items)
+  } else {
+    it.tile = args.causal ? n_tiles - 1 - r : r;            // the last query tile sees the most keys
+    it.first = 0;
+    it.n = args.causal ? min(n_kv_tiles, it.tile + 1) : n_kv_tiles;
+  }
+  return it;
+}
+
 template <typename T, int D, bool kDkv>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -170,26 +207,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t bar_p = smem_base + S::kOffBar + 40;      // [2]  P / dS of a half tile are in place (per TMEM buffer)
   const uint32_t bar_o = smem_base + S::kOffBar + 56;      // [2]  second MMA pairs of a streamed tile are complete (per slot)
   const uint32_t bar_fixt = smem_base + S::kOffBar + 72;   //      (dQ kernel) the fixed tiles are in tensor memory
+  const uint32_t bar_acc = smem_base + S::kOffBar + 80;    //      the item's gradients have left the accumulators
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kOffTmemSlot);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tile = blockIdx.x;
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z;
-  const int t0 = tile * kAttnTile;              // first key (dkv) / query (dq) of this CTA
-
-  // streamed tiles visited: [first, first + n)
   const int n_q_tiles = (args.len_q + kAttnTile - 1) / kAttnTile;
   const int n_kv_tiles = (args.len_kv + kAttnTile - 1) / kAttnTile;
-  int first = 0, n = 0;
-  if (kDkv) {
-    first = args.causal ? min(tile, n_q_tiles) : 0;      // query tiles below the diagonal see none of these keys
-    n = n_q_tiles - first;
-  } else {
-    n = args.causal ? min(n_kv_tiles, tile + 1) : n_kv_tiles;
-  }
+  // Every item has at least one streamed tile: under a causal mask the key tiles that no query can see
+  // (more keys than queries) are not items; their gradients are zero-filled after the loop.
+  const int n_tiles = kDkv ? (args.causal ? min(n_kv_tiles, n_q_tiles) : n_kv_tiles) : n_q_tiles;
+  const int n_items = n_tiles * args.heads * args.batch;
 
   if (threadIdx.x == 0) {
     mbar_init(bar_fix, 1);
@@ -202,6 +231,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar_o, 1);
     mbar_init(bar_o + 8, 1);
     mbar_init(bar_fixt, 128);
+    mbar_init(bar_acc, kBwdComputeWarps * 32);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -215,7 +245,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == kBwdComputeWarps) {
-    if (n > 0) {
+    {
       // ------------------------------------------------ TMA + MMA issuer ----
       // The whole warp walks the schedule and one elected lane issues: in warp-uniform code the
       // descriptors stay in uniform registers and an MMA is issued every ~74 clocks, where a
@@ -232,18 +262,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const CUtensorMap* m_fix1 = kDkv ? &map_v : &map_do;
       const CUtensorMap* m_str0 = kDkv ? &map_q : &map_k;
       const CUtensorMap* m_str1 = kDkv ? &map_do : &map_v;
-      auto load_tile = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int row0) {
-#pragma unroll
-        for (int blk = 0; blk < kBlocks; ++blk)
-          tma_load_4d(dst + blk * S::kBlockBytes, map, bar, blk * 64, row0, head, batch);
-      };
-      auto load_stream = [&](int it) {
-        if (!leader) return;
-        const int slot = it & 1;
-        mbar_arrive_expect_tx(bar_str + slot * 8, 2 * S::kTileBytes);
-        load_tile(sStr0(slot), m_str0, bar_str + slot * 8, (first + it) * kAttnTile);
-        load_tile(sStr1(slot), m_str1, bar_str + slot * 8, (first + it) * kAttnTile);
-      };
       // All operands are [128 rows][D] tiles, rows 128 B per 64-column block, 128-byte swizzle.
       // Descriptors are kept as 32-bit low halves (address and LBO; the high half is the same for all)
       // and advanced by constants: one thread issues every MMA, and building a 64-bit descriptor per
@@ -261,6 +279,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const uint32_t idesc_sd = make_idesc(128, 64, kIsBf16, 0, 0);
       const uint32_t idesc_acc = make_idesc(128, D, kIsBf16, 0, 1);
 
+      uint32_t g = 0;          // streamed tiles of earlier items: slots and phases of bar_str / bar_s / bar_p / bar_o
+      uint32_t k_item = 0;     // earlier items: phases of bar_fix / bar_fixt / bar_acc
+      bool ok = true;
+      for (int number = blockIdx.x; ok && number < n_items; number += gridDim.x, ++k_item) {
+      const BwdItem item = bwd_item_decode<kDkv>(args, number, n_tiles, n_q_tiles, n_kv_tiles);
+      const int n = item.n, first = item.first, head = item.head, batch = item.batch;
+      const int t0 = item.tile * kAttnTile;
+      auto load_tile = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int row0) {
+#pragma unroll
+        for (int blk = 0; blk < kBlocks; ++blk)
+          tma_load_4d(dst + blk * S::kBlockBytes, map, bar, blk * 64, row0, head, batch);
+      };
+      auto load_stream = [&](int it) {
+        if (!leader) return;
+        const int slot = (g + it) & 1;
+        mbar_arrive_expect_tx(bar_str + slot * 8, 2 * S::kTileBytes);
+        load_tile(sStr0(slot), m_str0, bar_str + slot * 8, (first + it) * kAttnTile);
+        load_tile(sStr1(slot), m_str1, bar_str + slot * 8, (first + it) * kAttnTile);
+      };
+      // Shared memory is free once every MMA of the previous item has completed: the commit of its
+      // last streamed tile covers them all.
+      if (g > 0) {
+        ok = mbar_wait_warp(bar_o + ((g - 1) & 1) * 8, ((g - 1) >> 1) & 1, abort_flag, kBWaitDrain);
+        if (!ok) break;
+      }
       if (leader) {
         mbar_arrive_expect_tx(bar_fix, 2 * S::kTileBytes);
         load_tile(sFix0, m_fix0, bar_fix, t0);
@@ -280,13 +323,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // The tensor pipe executes in issue order, so P1(u + 2) overwrites buffer u & 1 only after P2(u)
       // has read it.
       const int n_half = 2 * n;
-      bool ok = kFixedInTmem ? mbar_wait_warp(bar_fixt, 0, abort_flag, kBWaitFixed)
-                             : mbar_wait_warp(bar_fix, 0, abort_flag, kBWaitFixed);
+      ok = kFixedInTmem ? mbar_wait_warp(bar_fixt, k_item & 1, abort_flag, kBWaitFixed)
+                        : mbar_wait_warp(bar_fix, k_item & 1, abort_flag, kBWaitFixed);
       if (kFixedInTmem) tc_fence_after();
       auto issue_p1 = [&](int u) -> bool {
-        const int it = u >> 1, hh = u & 1, slot = it & 1, b = u & 1;
+        const int it = u >> 1, hh = u & 1, slot = (g + it) & 1, b = u & 1;
         if (hh == 0) {
-          if (!mbar_wait_warp(bar_str + slot * 8, (it >> 1) & 1, abort_flag, kBWaitStream)) return false;
+          if (!mbar_wait_warp(bar_str + slot * 8, ((g + it) >> 1) & 1, abort_flag, kBWaitStream)) return false;
           tc_fence_after();
         }
         if (!leader) return true;
@@ -312,19 +355,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       };
       if (ok) ok = issue_p1(0);
       for (int u = 0; ok && u < n_half; ++u) {
-        const int it = u >> 1, hh = u & 1, slot = it & 1, b = u & 1;
+        const int it = u >> 1, hh = u & 1, slot = (g + it) & 1, b = u & 1;
         if (u + 1 < n_half) {
           ok = issue_p1(u + 1);
           if (!ok) break;
         }
         // the other slot is free once the second pairs of the previous tile have read it
         if (hh == 0 && it >= 1 && it + 1 < n) {
-          ok = mbar_wait_warp(bar_o + (slot ^ 1) * 8, ((it - 1) >> 1) & 1, abort_flag, kBWaitSlot);
+          ok = mbar_wait_warp(bar_o + (slot ^ 1) * 8, ((g + it - 1) >> 1) & 1, abort_flag, kBWaitSlot);
           if (!ok) break;
           load_stream(it + 1);
         }
-        ok = mbar_wait_warp(bar_p + b * 8, (u >> 1) & 1, abort_flag, kBWaitP);
+        ok = mbar_wait_warp(bar_p + b * 8, ((2 * g + u) >> 1) & 1, abort_flag, kBWaitP);
         if (!ok) break;
+        if (u == 0 && k_item > 0) {
+          // the first accumulating MMAs overwrite the accumulators: the previous item's gradients must have left
+          ok = mbar_wait_warp(bar_acc, (k_item - 1) & 1, abort_flag, kBWaitAcc);
+          if (!ok) break;
+        }
         tc_fence_after();
         if (!leader) continue;
         const uint32_t r0 = str0_r_lo[slot] + ((hh * 4 * 2048) >> 4), r1 = str1_r_lo[slot] + ((hh * 4 * 2048) >> 4);
@@ -345,6 +393,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         if (hh == 1) umma_commit(bar_o + slot * 8);
       }
+      g += n;
+      }   // items
+      if (ok && g > 0) {
+        // the last MMAs (and with them every copy) are complete before the CTA gives up its shared memory
+        ok = mbar_wait_warp(bar_o + ((g - 1) & 1) * 8, ((g - 1) >> 1) & 1, abort_flag, kBWaitDrain);
+      }
       if (!ok) {
         // let copies still in flight land before the CTA gives up its shared memory
         const unsigned long long t_start = global_timer_ns();
@@ -360,9 +414,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int quarter = warp & 3, chunk = warp >> 2;
     const int row = quarter * 32 + lane;                    // lane of tensor memory == row of the fixed tile
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
+    const uint64_t scale_log2_2 = f2_pack(args.scale_log2, args.scale_log2);
+    const uint64_t scale_2 = f2_pack(args.scale, args.scale);
+    bool ok = true;
+    uint32_t g = 0;                                         // streamed tiles of earlier items
+    uint32_t k_item = 0;                                    // earlier items
+
+    for (int number = blockIdx.x; ok && number < n_items; number += gridDim.x, ++k_item) {
+    const BwdItem item = bwd_item_decode<kDkv>(args, number, n_tiles, n_q_tiles, n_kv_tiles);
+    const int n = item.n, first = item.first, head = item.head, batch = item.batch;
+    const int t0 = item.tile * kAttnTile;                   // first key (dkv) / query (dq) of this item
     const int fixed_idx = t0 + row;                         // key index (dkv) / query index (dq)
     const long long row_base = (long long)batch * args.row_stride_b + (long long)head * args.row_stride_h;
-    bool ok = true;
 
     // dq: this thread's query row keeps its own -lse2 / -delta (as packed pairs)
     uint64_t my_nlse2 = 0ull, my_ndelta = 0ull;
@@ -373,14 +436,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       my_nlse2 = f2_pack(l2, l2);
       my_ndelta = f2_pack(dl, dl);
     }
-    const uint64_t scale_log2_2 = f2_pack(args.scale_log2, args.scale_log2);
-    const uint64_t scale_2 = f2_pack(args.scale, args.scale);
 
-    if (kFixedInTmem && n > 0) {
+    if (kFixedInTmem) {
       // Q and dO of this CTA's query tile: shared memory (128-byte swizzle: the 16-byte unit u of row r
       // sits at unit u ^ (r & 7) of its 128-byte row) -> this thread's lane of tensor memory, in the
-      // layout of a 16-bit A operand (two consecutive head dims per column).
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_fix, 0, abort_flag, kBWaitFixed));
+      // layout of a 16-bit A operand (two consecutive head dims per column).  (Every MMA that read
+      // the previous item's copy completed before this thread left that item's epilogue.)
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_fix, k_item & 1, abort_flag, kBWaitFixed));
       if (ok && chunk == 0) {
 #pragma unroll
         for (int f = 0; f < 2; ++f) {
@@ -407,7 +469,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
     for (int it = 0; it < n; ++it) {
       const int s0 = (first + it) * kAttnTile;              // first streamed row (query for dkv, key for dq)
-      float* rows_lse2 = s_rows + (it & 1) * 2 * kAttnTile;
+      float* rows_lse2 = s_rows + ((g + it) & 1) * 2 * kAttnTile;
       float* rows_delta = rows_lse2 + kAttnTile;
       if (kDkv) {
         // lse2 / delta of the streamed queries: one value per thread, shared through shared memory
@@ -420,7 +482,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         bwd_rows_sync();
       }
       for (int hh = 0; hh < 2; ++hh) {
-        const int u = 2 * it + hh, b = u & 1;
+        const uint32_t u = 2 * (g + it) + hh;
+        const int b = u & 1;
         ok = __all_sync(0xffffffffu, mbar_wait(bar_s + b * 8, (u >> 1) & 1, abort_flag, kBWaitS));
         if (!ok) break;
         tc_fence_after();
@@ -484,11 +547,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!ok) break;
     }
 
-    // ------------------------------------------------------------ epilogue --
-    if (ok && n > 0)
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_o + ((n - 1) & 1) * 8, ((n - 1) >> 1) & 1, abort_flag, kBWaitEpi));
-    if (ok) {
-      if (n > 0) tc_fence_after();
+    // ---------------------------------------------------- the item's epilogue --
+    if (!ok) break;
+    ok = __all_sync(0xffffffffu, mbar_wait(bar_o + ((g + n - 1) & 1) * 8, ((g + n - 1) >> 1) & 1, abort_flag, kBWaitEpi));
+    if (!ok) break;
+    tc_fence_after();
+    {
       auto store_rows = [&](uint32_t col0, void* base, long long sb, long long sh, long long sl, int len) {
         const bool row_valid = fixed_idx < len;
         T* out = reinterpret_cast<T*>(base) + (long long)batch * sb + (long long)head * sh + (long long)fixed_idx * sl;
@@ -496,14 +560,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int c = 0; c < D / 32; ++c) {
           if (kChunkStep == 2 && (c & 1) != chunk) continue;      // two threads per row take alternate chunks
           uint32_t acc[32];
-          if (n > 0) {
-            tmem_ld32(t_lane + col0 + c * 32, acc);
-            tmem_wait_ld();
-          } else {
-            // (causal, more keys than queries: a key tile no query can see gets zero gradients)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0u;
-          }
+          tmem_ld32(t_lane + col0 + c * 32, acc);
+          tmem_wait_ld();
           if (row_valid) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -522,6 +580,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         store_rows(kColAcc1, args.dk, args.dk_stride_b, args.dk_stride_h, args.dk_stride_l, args.len_kv);
       } else {
         store_rows(kColAcc0, args.dq, args.dq_stride_b, args.dq_stride_h, args.dq_stride_l, args.len_q);
+      }
+    }
+    // the accumulators are free for the next item's first accumulating MMAs
+    tc_fence_before();
+    mbar_arrive(bar_acc);
+    g += n;
+    }   // items
+
+    if (kDkv && args.causal && ok) {
+      // causal with more keys than queries: key tiles beyond the last query get zero gradients
+      const int n_dead = n_kv_tiles - n_tiles;
+      for (int idx = blockIdx.x; idx < n_dead * args.heads * args.batch; idx += gridDim.x) {
+        const int bh = idx / n_dead;
+        const int key = (n_tiles + (idx - bh * n_dead)) * kAttnTile + row;
+        const int batch = bh / args.heads, head = bh - batch * args.heads;
+        if (key < args.len_kv && chunk == 0) {
+          T* dk_row = reinterpret_cast<T*>(args.dk) + (long long)batch * args.dk_stride_b +
+                      (long long)head * args.dk_stride_h + (long long)key * args.dk_stride_l;
+          T* dv_row = reinterpret_cast<T*>(args.dv) + (long long)batch * args.dv_stride_b +
+                      (long long)head * args.dv_stride_h + (long long)key * args.dv_stride_l;
+#pragma unroll
+          for (int c = 0; c < D / 8; ++c) {
+            reinterpret_cast<uint4*>(dk_row)[c] = make_uint4(0u, 0u, 0u, 0u);
+            reinterpret_cast<uint4*>(dv_row)[c] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
       }
     }
   }
