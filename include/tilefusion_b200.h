@@ -138,7 +138,10 @@ typedef struct TfDecodePlan {
   int32_t kv_chunk;
   int32_t grid;              /* CTAs of the split kernel                      */
   int32_t stages;            /* depth of the shared-memory ring               */
-  int32_t reserved;
+  int32_t reserved;          /* grouped-query decoding: partial rows per (row,
+                                split) -- 4 when the query rows of a group are
+                                replicated in the kernel (num_splits counts
+                                them all), else 0 or 1                        */
   uint64_t workspace_bytes;  /* fp32 partials: B*H*num_splits*(D+2)*4         */
 } TfDecodePlan;
 

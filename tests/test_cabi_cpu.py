@@ -163,11 +163,19 @@ def test_grouped_query_decode_plan(native_lib):
     plan = _cabi.TfDecodePlan()
     assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == 0
     n_tiles = 8192 // 128
-    assert plan.kv_chunk == 128 and plan.num_splits * plan.chunks_per_split >= n_tiles
-    assert (plan.num_splits - 1) * plan.chunks_per_split < n_tiles
-    items = 32 * 8 * plan.num_splits
+    # four query heads per KV head: the rows are replicated in the kernel, four partial rows per
+    # (row, split), all counted by num_splits
+    assert plan.reserved == 4 and plan.num_splits % 4 == 0
+    splits = plan.num_splits // 4
+    assert plan.kv_chunk == 128 and splits * plan.chunks_per_split >= n_tiles
+    assert (splits - 1) * plan.chunks_per_split < n_tiles
+    items = 32 * 8 * splits
     assert -(-items // 148) * plan.chunks_per_split <= 1.05 * 32 * 8 * n_tiles / 148 + plan.chunks_per_split
     assert plan.workspace_bytes == 32 * 32 * plan.num_splits * 130 * 4
+    # more than 32 query heads per KV head: no replication
+    wide = _decode_desc(2, 128, 8192)
+    wide.heads_kv = 2
+    assert native_lib.tf_decode_plan(C.byref(wide), C.byref(plan)) == 0 and plan.reserved == 1
     d.heads_kv = 5
     assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_BAD_ARG
 

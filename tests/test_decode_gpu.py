@@ -115,7 +115,10 @@ GQA_CASES = [
     (1, 8, 1, 4096, 128),      # multi-query: all 8 heads share one KV head
     (3, 6, 3, 130, 64),        # group of 2, D = 64
     (2, 32, 8, 8192, 128),
-    (1, 16, 2, 1, 128),        # a single key
+    (1, 16, 2, 1, 128),        # a single key: three of the four row copies see no key at all
+    (1, 64, 2, 700, 128),      # group of 32: the largest that is replicated in the lane quarters
+    (1, 128, 2, 700, 128),     # group of 64: not replicated
+    (2, 12, 4, 40, 64),        # fewer keys than one quarter holds in the last copy
 ]
 
 

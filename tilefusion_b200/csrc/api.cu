@@ -281,13 +281,15 @@ int pair_queue_word(cudaStream_t stream, int** out) {
 }
 
 // Two Q tiles per CTA, persistent grid of one CTA per SM.
-template <typename T, int D>
+// kRepl: split-KV mode with the (at most 32) query rows replicated in the four lane quarters of Q
+// tile 0 (the Q tensor map's box is then 32 rows high); every (row, split) has four partial rows.
+template <typename T, int D, bool kRepl = false>
 int launch_attn_pair(const AttnLaunch& L, const TfAttnDesc* d, const TfAttnPlan& plan, cudaStream_t stream,
                      int kv_splits = 0, int tiles_per_split = 0, float* part_o = nullptr,
                      float* part_ml = nullptr, const int* block_table = nullptr, int page_size = 0,
                      int max_pages = 0) {
   using Smem = tfb::AttnPairSmem<D>;
-  auto kern = tfb::attn_fwd_pair_kernel<T, D>;
+  auto kern = tfb::attn_fwd_pair_kernel<T, D, kRepl>;
   static thread_local int configured_device = -1;
   int dev = 0;
   TF_CUDA_TRY(cudaGetDevice(&dev));
@@ -595,13 +597,30 @@ int launch_gqa_split(const void* q, const void* k, const void* v, float* part_o,
     if (int rc = encode_map(&L.mv, d->dtype, v, dims, vs, 64, tfb::kAttnTile, "V pages")) return rc;
   }
   const int* table = d->page_size > 0 ? d->block_table : nullptr;
+  // plan.reserved: partial rows per (row, split) -- 4 when the query rows of a group are replicated
+  // in the four lane quarters (at most 32 query heads per KV head), else 1
+  const int copies = plan.reserved == 4 ? 4 : 1;
+  const int kv_splits = plan.num_splits / copies;
+  if (copies == 4) {
+    // Q map with a 32-row box: the group's rows are loaded once per lane quarter
+    const uint64_t qdims[4] = {(uint64_t)D, (uint64_t)group, (uint64_t)d->heads_kv, (uint64_t)d->batch};
+    const int64_t qstr[3] = {ad.q_stride_l, ad.q_stride_h, ad.q_stride_b};
+    if (int rc = encode_map(&L.mq, d->dtype, q, qdims, qstr, 64, 32, "Q (grouped)")) return rc;
+    if (D == 128)
+      return d->dtype == TF_F16
+                 ? launch_attn_pair<__half, 128, true>(L, &ad, ap, stream, kv_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages)
+                 : launch_attn_pair<__nv_bfloat16, 128, true>(L, &ad, ap, stream, kv_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages);
+    return d->dtype == TF_F16
+               ? launch_attn_pair<__half, 64, true>(L, &ad, ap, stream, kv_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages)
+               : launch_attn_pair<__nv_bfloat16, 64, true>(L, &ad, ap, stream, kv_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages);
+  }
   if (D == 128)
     return d->dtype == TF_F16
-               ? launch_attn_pair<__half, 128>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages)
-               : launch_attn_pair<__nv_bfloat16, 128>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages);
+               ? launch_attn_pair<__half, 128>(L, &ad, ap, stream, kv_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages)
+               : launch_attn_pair<__nv_bfloat16, 128>(L, &ad, ap, stream, kv_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages);
   return d->dtype == TF_F16
-             ? launch_attn_pair<__half, 64>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages)
-             : launch_attn_pair<__nv_bfloat16, 64>(L, &ad, ap, stream, plan.num_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages);
+             ? launch_attn_pair<__half, 64>(L, &ad, ap, stream, kv_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages)
+             : launch_attn_pair<__nv_bfloat16, 64>(L, &ad, ap, stream, kv_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages);
 }
 
 bool is_grouped(const TfDecodeDesc* d) { return d->heads_kv > 0 && d->heads_kv != d->heads; }

@@ -71,6 +71,10 @@ struct AttnPairArgs {
   // decode_combine_kernel reads ([row][split], row = (b * heads + h) * len_q + q).
   int kv_splits;
   int tiles_per_split;
+  // kRepl instantiation (split-KV mode with at most 32 query rows per item): the rows are loaded
+  // four times, once into every 32-lane quarter of Q tile 0, and the warp of quarter c takes keys
+  // [32 c, 32 c + 32) of every KV tile for its copy of the rows; each copy writes a partial row of
+  // its own, so a (row, split) has four partial rows: index split * 4 + c of kv_splits * 4.
   float* part_o;
   float* part_ml;
   // Paged KV cache (split-KV mode only; page_size > 0): the K and V tensor maps
@@ -178,7 +182,7 @@ __device__ __forceinline__ int kv_tiles_for(const AttnPairArgs& p, int q0, int s
   return n;
 }
 
-template <typename T, int D>
+template <typename T, int D, bool kRepl = false>
 __global__ void __launch_bounds__(kPairThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                      const __grid_constant__ CUtensorMap map_k,
@@ -325,10 +329,20 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
               !mbar_wait(bar(S::kBarQEmpty + x), (q_uses[x] - 1) & 1, abort_flag, kPWaitQEmpty))
             return false;
           mbar_arrive_expect_tx(bar(S::kBarQFull + x), S::kTileBytes);
+          if constexpr (kRepl) {
+            // the same (at most 32) rows into every lane quarter: the tensor map's box is 32 rows high
 #pragma unroll
-          for (int blk = 0; blk < kBlocks; ++blk)
-            tma_load_4d(smem_base + S::kOffQ + x * S::kTileBytes + blk * S::kBlockBytes, &map_q,
-                        bar(S::kBarQFull + x), blk * 64, q0 + x * kAttnTile, h, b);
+            for (int copy = 0; copy < 4; ++copy)
+#pragma unroll
+              for (int blk = 0; blk < kBlocks; ++blk)
+                tma_load_4d(smem_base + S::kOffQ + x * S::kTileBytes + blk * S::kBlockBytes + copy * 32 * 128, &map_q,
+                            bar(S::kBarQFull + x), blk * 64, q0, h, b);
+          } else {
+#pragma unroll
+            for (int blk = 0; blk < kBlocks; ++blk)
+              tma_load_4d(smem_base + S::kOffQ + x * S::kTileBytes + blk * S::kBlockBytes, &map_q,
+                          bar(S::kBarQFull + x), blk * 64, q0 + x * kAttnTile, h, b);
+          }
           ++q_uses[x];
           return true;
         };
@@ -567,13 +581,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       const int b = item_ring[slot].b, h = item_ring[slot].h;
       const int split = item_ring[slot].split;
       const int q0 = item_ring[slot].pair * 2 * kAttnTile + x * kAttnTile;
-      const int q_idx = q0 + row;
+      const int q_idx = kRepl ? q0 + (row & 31) : q0 + row;
       const float inv_l = pend_inv_l;
       const bool row_valid = q_idx < args.len_q;
       if (pargs.kv_splits > 0) {
-        // split-KV mode: one fp32 partial row (normalised O, log2-sum-exp) per split
+        // split-KV mode: one fp32 partial row (normalised O, log2-sum-exp) per split (and row copy)
         const long long prow =
-            (((long long)b * pargs.heads + h) * args.len_q + q_idx) * pargs.kv_splits + split;
+            kRepl ? (((long long)b * pargs.heads + h) * args.len_q + q_idx) * (pargs.kv_splits * 4) + split * 4 + quarter
+                  : (((long long)b * pargs.heads + h) * args.len_q + q_idx) * pargs.kv_splits + split;
         float* p_row = pargs.part_o + prow * D;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
@@ -698,7 +713,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         ok = flush_pending(prev_slot);
         continue;
       }
-      const int q_idx = q0 + row;
+      const int q_idx = kRepl ? q0 + (row & 31) : q0 + row;
       float m_used = -INFINITY;
       float l_run = 0.f;
 
@@ -707,6 +722,89 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         if (!ok) break;
         ++s_cnt;
         tc_fence_after();
+
+        if constexpr (kRepl) {
+          // This warp's 32 keys of the tile for its copy of the rows; the other 96 keys of P are
+          // zero in this copy, so the P.V MMAs add nothing for them.
+          const int key0 = (j0 + j) * kAttnTile + quarter * 32;
+          uint32_t s1[32];
+          tmem_ld32(t_lane + col_s + quarter * 32, s1);
+          tmem_wait_ld();
+          if (key0 + 32 > args.len_kv) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (key0 + i >= args.len_kv) s1[i] = 0xff800000u;  // -inf
+          }
+          auto chunk_max = [&]() -> float {
+            float ma = max3(__uint_as_float(s1[0]), __uint_as_float(s1[1]), __uint_as_float(s1[2]));
+            float mb = max3(__uint_as_float(s1[3]), __uint_as_float(s1[4]), __uint_as_float(s1[5]));
+#pragma unroll
+            for (int i = 6; i + 3 < 32; i += 4) {
+              ma = max3(ma, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+              mb = max3(mb, __uint_as_float(s1[i + 2]), __uint_as_float(s1[i + 3]));
+            }
+            return max3(ma, mb, fmaxf(__uint_as_float(s1[30]), __uint_as_float(s1[31])));
+          };
+          // Nothing has been accumulated under a maximum of -inf (every key so far was masked), so
+          // the first finite maximum is taken over without a rescale.
+          if (m_used == -INFINITY) m_used = chunk_max();
+          uint32_t pk[16];
+          float sum = 0.f;
+          auto probs = [&]() {
+            const float nm = -m_used * args.scale_log2;
+            sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              // (m_used = -inf only if every key of this chunk is masked as well: P = 0)
+              const float p0 = m_used == -INFINITY ? 0.f : fast_exp2(fmaf(__uint_as_float(s1[i]), args.scale_log2, nm));
+              const float p1 = m_used == -INFINITY ? 0.f : fast_exp2(fmaf(__uint_as_float(s1[i + 1]), args.scale_log2, nm));
+              sum += p0 + p1;
+              pk[i >> 1] = pack2<T>(p0, p1);
+            }
+          };
+          probs();
+          if (__any_sync(0xffffffffu, !(sum <= kPairSumLimit))) {
+            // the maximum in use is stale by more than the limit allows: rescale what has been
+            // accumulated (O only once the previous tile's P.V is complete) and compute again
+            const float m_new = fmaxf(m_used, chunk_max());
+            const float alpha = fast_exp2((m_used - m_new) * args.scale_log2);
+            m_used = m_new;
+            l_run *= alpha;
+            if (j > 0) {
+              ok = __all_sync(0xffffffffu, mbar_wait(bar_o, (o_base + j - 1) & 1, abort_flag, kPWaitOFull));
+              if (!ok) break;
+              tc_fence_after();
+#pragma unroll
+              for (int c = 0; c < D / 16; ++c) {
+                uint32_t orow[16];
+                tmem_ld16(t_lane + col_o + c * 16, orow);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
+                tmem_st16(t_lane + col_o + c * 16, orow);
+              }
+            }
+            probs();
+          }
+          uint32_t zeros[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) zeros[i] = 0u;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (c == quarter) tmem_st16(t_lane + col_p + c * 16, pk);
+            else tmem_st16(t_lane + col_p + c * 16, zeros);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar_p);
+          mbar_arrive(bar_p_hi);
+          l_run += sum;
+          if (j == 0) {
+            ok = flush_pending(prev_slot);
+            if (!ok) break;
+          }
+          continue;
+        }
 
         // Load the whole S row (four 32-column chunks) into registers.
         const int kv0 = (j0 + j) * kAttnTile;
@@ -884,8 +982,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
         if (q_idx < args.len_q) {
           if (pargs.kv_splits > 0) {
             const long long prow =
-                (((long long)b * pargs.heads + h) * args.len_q + q_idx) * pargs.kv_splits + split;
-            pargs.part_ml[prow * 2 + 0] = m_used * args.scale_log2 + log2f(l_run);
+                kRepl ? (((long long)b * pargs.heads + h) * args.len_q + q_idx) * (pargs.kv_splits * 4) + split * 4 + quarter
+                      : (((long long)b * pargs.heads + h) * args.len_q + q_idx) * pargs.kv_splits + split;
+            // (a row copy that saw no key at all: l = 0, m = -inf, which the combine gives weight 0)
+            pargs.part_ml[prow * 2 + 0] = l_run > 0.f ? m_used * args.scale_log2 + log2f(l_run) : -INFINITY;
             pargs.part_ml[prow * 2 + 1] = 1.0f;
           } else if (args.lse != nullptr) {
             args.lse[(long long)b * args.lse_stride_b + (long long)h * args.lse_stride_h + q_idx] =
@@ -893,7 +993,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
       }
-      pend_inv_l = 1.0f / l_run;
+      pend_inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
       have_pending = true;
       o_base += n_kv;
     }

@@ -99,13 +99,17 @@ void plan_decode(const TfDecodeDesc& d, int sm_count, TfDecodePlan* plan) {
     }
     const int tps = (n_tiles + want - 1) / want;
     const int splits = (n_tiles + tps - 1) / tps;
-    plan->num_splits = splits;
+    // With at most 32 query heads per KV head the rows of a group are replicated in the four lane
+    // quarters of the Q tile and every quarter takes a quarter of each KV tile's keys (a fourth of
+    // the exponentials per thread and tile): four partial rows per (row, split).
+    const int copies = d.heads / d.heads_kv <= 32 ? 4 : 1;
+    plan->num_splits = splits * copies;
     plan->chunks_per_split = tps;
     plan->kv_chunk = 128;
     plan->grid = (int32_t)std::min<int64_t>(grid, groups * splits);
     plan->stages = 5;
-    plan->reserved = 0;
-    plan->workspace_bytes = (uint64_t)d.batch * d.heads * splits * (d.head_dim + 2) * sizeof(float);
+    plan->reserved = copies;
+    plan->workspace_bytes = (uint64_t)d.batch * d.heads * splits * copies * (d.head_dim + 2) * sizeof(float);
     return;
   }
   const bool kv8 = d.kv_dtype == TF_FP8_E4M3 || d.kv_dtype == TF_FP8_E5M2;
