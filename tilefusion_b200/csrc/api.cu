@@ -344,8 +344,9 @@ int run_attn(const void* q, const void* k, const void* v, void* o, float* lse, c
   return launch_attn<T, D>(L, d, stream);
 }
 
-// Backward: delta rows, then the dK/dV kernel (one CTA per key tile) and the dQ
-// kernel (one CTA per query tile).
+// Backward: delta rows, then the dK/dV kernel (items = live key tiles) and the dQ
+// kernel (items = query tiles), each on a persistent grid of at most one CTA per
+// SM that walks its items in a fixed order.
 template <typename T, int D>
 int launch_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
                     void* dq, void* dk, void* dv, float* delta, const TfAttnDesc* d, cudaStream_t stream) {
