@@ -834,7 +834,8 @@ def run_two_gemms(args, w, device, rank, world):
 
 def run_mma_rate():
     """Prints one JSON line: SM clocks per M128 K16 tcgen05.mma (fp16 operands, fp32 accumulators), 256
-    issued back to back by one thread on one SM, for the operand forms the kernels use."""
+    issued back to back by one thread on one SM, for the operand forms the kernels use, and for the
+    two-CTA form (M256 over a pair of SMs) the kernels do not use."""
     import ctypes as C
 
     from tilefusion_b200 import _cabi
@@ -856,6 +857,20 @@ def run_mma_rate():
                                  "issuer": "elected lane of a whole warp" if uniform else "lane 0 in a branch",
                                  "issue_clk_per_mma": best[0] / 256, "complete_clk_per_mma": best[1] / 256,
                                  "nominal_clk_per_mma": 128 * n * 16 * 2 / 8192})
+    # the two-CTA form: M256 over two SMs, the same arithmetic per SM as the M128 rows above
+    for n in (64, 128, 256):
+        for a_tmem in (0, 1):
+            for b_mn in (0, 1):
+                best = None
+                for _ in range(3):
+                    issue, done = C.c_int64(0), C.c_int64(0)
+                    _cabi.check(lib.tf_probe_mma_pair_clocks(a_tmem, n, b_mn, 256, C.byref(issue), C.byref(done)))
+                    if best is None or done.value < best[1]:
+                        best = (issue.value, done.value)
+                rows.append({"n": n, "form": "cta_group::2, M256 over two SMs", "a": "tmem" if a_tmem else "smem",
+                             "b": "mn-major" if b_mn else "k-major", "descriptors": "32-bit halves",
+                             "issuer": "elected lane of a whole warp", "issue_clk_per_mma": best[0] / 256,
+                             "complete_clk_per_mma": best[1] / 256, "nominal_clk_per_mma": 128 * n * 16 * 2 / 8192})
     print(json.dumps({"metric": "mma_clocks", "unit": "SM clocks per tcgen05.mma (M128 K16)", "n_mma": 256,
                       "nominal": "8192 dense fp16 FLOP per clock and SM", "rows": rows}), flush=True)
 

@@ -503,6 +503,18 @@ TF_EXPORT int tf_probe_mma_clocks(int32_t a_from_tmem, int32_t n, int32_t b_mn_m
                                   int32_t desc32, int32_t uniform_issue, int32_t n_mma,
                                   int64_t* issue_clocks, int64_t* complete_clocks);
 
+/*
+ * The same measurement for the two-CTA form (tcgen05.mma.cta_group::2, M = 256
+ * over a cluster of two CTAs on two SMs, each holding its own 128 rows of A and
+ * n / 2 columns of B): per SM the arithmetic of one such MMA equals that of an
+ * M128 single-CTA MMA of the same n, so the clocks compare directly with
+ * tf_probe_mma_clocks(..., desc32 = 1, uniform_issue = 1, ...).  No counterpart
+ * in the reference.  Synchronous; allocates 16 bytes for the duration of the call.
+ */
+TF_EXPORT int tf_probe_mma_pair_clocks(int32_t a_from_tmem, int32_t n, int32_t b_mn_major,
+                                       int32_t n_mma, int64_t* issue_clocks,
+                                       int64_t* complete_clocks);
+
 /* Library ABI version (bumped when a struct above changes). */
 TF_EXPORT int tf_abi_version(void);
 

@@ -91,3 +91,33 @@ def test_mma_probe_reports_plausible_clocks():
                     assert 0 < issue.value <= done.value
     assert lib.tf_probe_mma_clocks(0, 96, 0, 1, 1, 256, C.byref(issue), C.byref(done)) == _cabi.TF_ERR_BAD_ARG
     assert lib.tf_probe_mma_clocks(0, 128, 0, 1, 1, 12, C.byref(issue), C.byref(done)) == _cabi.TF_ERR_BAD_ARG
+
+
+def test_mma_pair_probe_matches_the_single_cta_clocks():
+    """tf_probe_mma_pair_clocks: an M256 MMA over a pair of SMs (128 rows and n / 2 of B's columns in
+    each) takes, per SM, the clocks of the M128 single-CTA MMA of the same n (within 10 %): the
+    two-CTA form saves shared memory, not tensor-pipe time."""
+    import ctypes as C
+
+    from tilefusion_b200 import _cabi
+    from cabi_helpers import device_status
+
+    lib = _cabi.lib()
+    for n in (64, 128, 256):
+        for a_tmem in (0, 1):
+            for b_mn in (0, 1):
+                one = []
+                for probe in (lambda *o: lib.tf_probe_mma_clocks(a_tmem, n, b_mn, 1, 1, 256, *o),
+                              lambda *o: lib.tf_probe_mma_pair_clocks(a_tmem, n, b_mn, 256, *o)):
+                    best = None
+                    for _ in range(3):
+                        issue, done = C.c_int64(0), C.c_int64(0)
+                        _cabi.check(probe(C.byref(issue), C.byref(done)))
+                        assert 0 < issue.value <= done.value
+                        best = done.value if best is None else min(best, done.value)
+                    one.append(best / 256)
+                assert 0.9 * n / 2 <= one[1] <= 6 * n, (n, a_tmem, b_mn, one)
+                assert abs(one[1] - one[0]) <= 0.1 * one[0], (n, a_tmem, b_mn, one)
+    assert device_status() == 0
+    assert lib.tf_probe_mma_pair_clocks(0, 96, 0, 256, C.byref(issue), C.byref(done)) == _cabi.TF_ERR_BAD_ARG
+    assert lib.tf_probe_mma_pair_clocks(0, 128, 0, 12, C.byref(issue), C.byref(done)) == _cabi.TF_ERR_BAD_ARG

@@ -35,7 +35,7 @@ EXPORTED = (
     "tf_shard_head_slice", "tf_shard_kv_slice", "tf_prefill_sharded", "tf_shard_unique_id",
     "tf_shard_create", "tf_shard_transport", "tf_shard_note", "tf_decode_sharded", "tf_shard_destroy",
     "tf_device_status_peek", "tf_set_wait_limit_ms", "tf_attn_bwd", "tf_attn_bwd_workspace_bytes",
-    "tf_fp8_quantize", "tf_fp8_dequantize", "tf_probe_mma_clocks",
+    "tf_fp8_quantize", "tf_fp8_dequantize", "tf_probe_mma_clocks", "tf_probe_mma_pair_clocks",
 )
 TF_NCCL_ID_BYTES = 128
 TF_TRANSPORT_AUTO, TF_TRANSPORT_P2P, TF_TRANSPORT_NCCL = 0, 1, 2
@@ -138,6 +138,8 @@ def lib() -> C.CDLL:
     handle.tf_set_wait_limit_ms.argtypes = [C.c_uint32]
     handle.tf_probe_mma_clocks.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                            C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+    handle.tf_probe_mma_pair_clocks.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                                C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
     handle.tf_fp8_quantize.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p]
     handle.tf_fp8_dequantize.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p]
     handle.tf_shard_head_slice.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]

@@ -1245,6 +1245,30 @@ int tf_probe_mma_clocks(int32_t a_from_tmem, int32_t n, int32_t b_mn_major, int3
   return TF_OK;
 }
 
+int tf_probe_mma_pair_clocks(int32_t a_from_tmem, int32_t n, int32_t b_mn_major, int32_t n_mma,
+                             int64_t* issue_clocks, int64_t* complete_clocks) {
+  if (n != 64 && n != 128 && n != 256) return fail(TF_ERR_BAD_ARG, "n must be 64, 128 or 256 (got %d)", n);
+  if (n_mma < 8 || n_mma % 8 != 0 || n_mma > (1 << 20))
+    return fail(TF_ERR_BAD_ARG, "n_mma must be a multiple of 8 in [8, 2^20] (got %d)", n_mma);
+  if (issue_clocks == nullptr || complete_clocks == nullptr) return fail(TF_ERR_BAD_ARG, "the outputs must be non-null");
+  if (int rc = tfb::ensure_device_ready()) return rc;
+  long long* dev = nullptr;
+  TF_CUDA_TRY(cudaMalloc(&dev, 2 * sizeof(long long)));
+  tfb::ProbePairArgs a{a_from_tmem != 0, n, b_mn_major != 0, n_mma, dev};
+  cudaError_t e = cudaFuncSetAttribute(tfb::probe_mma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tfb::kProbeSmemBytes);
+  long long host[2] = {0, 0};
+  if (e == cudaSuccess) {
+    tfb::probe_mma_pair_kernel<<<2, 128, tfb::kProbeSmemBytes>>>(a);     // one cluster of two CTAs
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemcpy(host, dev, sizeof(host), cudaMemcpyDeviceToHost);    // (synchronises)
+  cudaFree(dev);
+  if (e != cudaSuccess) return fail(TF_ERR_CUDA, "the probe kernel failed: %s", cudaGetErrorString(e));
+  *issue_clocks = host[0];
+  *complete_clocks = host[1];
+  return TF_OK;
+}
+
 int tf_abi_version(void) { return 5; }
 
 }  // extern "C"
