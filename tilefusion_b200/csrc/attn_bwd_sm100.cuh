@@ -188,9 +188,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   constexpr int kColAcc0 = 256, kColAcc1 = 256 + D;
   // dQ kernel: the accumulator takes D columns only, so the fixed tiles (Q, dO) are copied into the
   // remaining tensor memory (D / 2 columns each, two 16-bit values per column) and serve as TMEM A
-  // operands of the first MMA pair: 43 instead of 76 clocks per M128 N64 K16 product.
+  // operands of the first MMA pair: 43 instead of 76 clocks per M128 N64 K16 product.  At head dim
+  // 64 the dK/dV kernel's two accumulators end at column 384 as well, and K and V go the same way.
   constexpr int kColFixA0 = 384, kColFixA1 = 384 + D / 2;
-  constexpr bool kFixedInTmem = !kDkv;
+  constexpr bool kFixedInTmem = !kDkv || D == 64;
+  static_assert(!kFixedInTmem || (kDkv ? 256 + 2 * D : 256 + D) <= kColFixA0, "accumulators overlap the fixed tiles");
+  static_assert(kColFixA1 + D / 2 <= kTmemCols, "fixed tiles exceed tensor memory");
   constexpr int kBlocks = D / 64;
 
   extern __shared__ uint8_t smem_raw[];
@@ -206,7 +209,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t bar_s = smem_base + S::kOffBar + 24;      // [2]  first MMA pair of a half tile is complete (per TMEM buffer)
   const uint32_t bar_p = smem_base + S::kOffBar + 40;      // [2]  P / dS of a half tile are in place (per TMEM buffer)
   const uint32_t bar_o = smem_base + S::kOffBar + 56;      // [2]  second MMA pairs of a streamed tile are complete (per slot)
-  const uint32_t bar_fixt = smem_base + S::kOffBar + 72;   //      (dQ kernel) the fixed tiles are in tensor memory
+  const uint32_t bar_fixt = smem_base + S::kOffBar + 72;   //      the fixed tiles are in tensor memory (where they are copied there)
   const uint32_t bar_acc = smem_base + S::kOffBar + 80;    //      the item's gradients have left the accumulators
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + S::kOffTmemSlot);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + S::kOffAbort);
@@ -415,7 +418,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int row = quarter * 32 + lane;                    // lane of tensor memory == row of the fixed tile
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
     const uint64_t scale_log2_2 = f2_pack(args.scale_log2, args.scale_log2);
-    const uint64_t scale_2 = f2_pack(args.scale, args.scale);
+    // log2(scale) rides in the exponent's addend, so the exponential yields P * scale (what dS needs);
+    // the dK/dV kernel feeds that to dV += P^T dO as well and divides dV by scale on the way out.
+    const float log2_scale = log2f(args.scale);
     bool ok = true;
     uint32_t g = 0;                                         // streamed tiles of earlier items
     uint32_t k_item = 0;                                    // earlier items
@@ -431,14 +436,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     uint64_t my_nlse2 = 0ull, my_ndelta = 0ull;
     if (!kDkv) {
       const bool valid = fixed_idx < args.len_q;
-      const float l2 = valid ? -args.lse[row_base + fixed_idx] * 1.4426950408889634f : -INFINITY;
+      const float l2 = valid ? log2_scale - args.lse[row_base + fixed_idx] * 1.4426950408889634f : -INFINITY;
       const float dl = valid ? -args.delta[row_base + fixed_idx] : 0.f;
       my_nlse2 = f2_pack(l2, l2);
       my_ndelta = f2_pack(dl, dl);
     }
 
     if (kFixedInTmem) {
-      // Q and dO of this CTA's query tile: shared memory (128-byte swizzle: the 16-byte unit u of row r
+      // The fixed tiles (Q and dO of this CTA's query tile; K and V of its key tile): shared memory (128-byte swizzle: the 16-byte unit u of row r
       // sits at unit u ^ (r & 7) of its 128-byte row) -> this thread's lane of tensor memory, in the
       // layout of a 16-bit A operand (two consecutive head dims per column).  (Every MMA that read
       // the previous item's copy completed before this thread left that item's epilogue.)
@@ -477,7 +482,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const bool valid = qi < args.len_q;
         // (stored negated: they enter the arithmetic below as addends, two rows per 64-bit operand)
         if (kChunkStep == 1 || chunk == 0)
-          rows_lse2[row] = valid ? -args.lse[row_base + qi] * 1.4426950408889634f : -INFINITY;   // P = 0 beyond len_q
+          rows_lse2[row] = valid ? log2_scale - args.lse[row_base + qi] * 1.4426950408889634f : -INFINITY;   // P = 0 beyond len_q
         if (kChunkStep == 1 || chunk == 1) rows_delta[row] = valid ? -args.delta[row_base + qi] : 0.f;
         bwd_rows_sync();
       }
@@ -498,8 +503,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tmem_ld32(t_lane + col_dp + c * 32, dp);
           tmem_wait_ld();
           uint32_t pk[16], dk[16];
-          // Per pair of streamed rows, in packed fp32 pairs:  P = 2^(s * scale_log2 - lse2),
-          // dS = (P * scale) * (dP - delta).
+          // Per pair of streamed rows, in packed fp32 pairs:  P' = P * scale = 2^(s * scale_log2 - lse2
+          // + log2 scale),  dS = P' * (dP - delta).  Two copies of the loop, with and without the mask:
+          // a branch per pair of rows keeps the compiler from interleaving the pairs' dependency chains.
+          auto rows = [&](auto masked_c) {
+          constexpr bool kMasked = decltype(masked_c)::value;
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const int local = hh * 64 + c * 32 + i;           // first of four rows of the streamed tile
@@ -519,7 +527,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               float x0, x1;
               f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[j]), __uint_as_float(sr[j + 1])), scale_log2_2, nl[h2]), x0, x1);
               float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-              if (need_mask) {
+              if (kMasked) {
                 const int col = s0 + local + 2 * h2;          // global index of the first of the two rows
                 const bool m0 = kDkv ? fixed_idx > col : (col >= args.len_kv || (args.causal && col > fixed_idx));
                 const bool m1 = kDkv ? fixed_idx > col + 1 : (col + 1 >= args.len_kv || (args.causal && col + 1 > fixed_idx));
@@ -528,12 +536,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               }
               const uint64_t p2 = f2_pack(p0, p1);
               float d0, d1;
-              f2_unpack(f2_mul(f2_mul(p2, scale_2),
-                               f2_add(f2_pack(__uint_as_float(dp[j]), __uint_as_float(dp[j + 1])), nd[h2])), d0, d1);
+              f2_unpack(f2_mul(p2, f2_add(f2_pack(__uint_as_float(dp[j]), __uint_as_float(dp[j + 1])), nd[h2])), d0, d1);
               pk[j >> 1] = pack2<T>(p0, p1);
               dk[j >> 1] = pack2<T>(d0, d1);
             }
           }
+          };
+          if (need_mask) rows(std::true_type{}); else rows(std::false_type{});
           // 16-bit P over S and dS over dP, each thread over the start of the 32 fp32 columns it
           // has just read (so the row's other thread is never disturbed): chunk c lands in
           // columns [32c, 32c + 16) of the buffer.
@@ -553,7 +562,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (!ok) break;
     tc_fence_after();
     {
-      auto store_rows = [&](uint32_t col0, void* base, long long sb, long long sh, long long sl, int len) {
+      auto store_rows = [&](uint32_t col0, void* base, long long sb, long long sh, long long sl, int len, float mul) {
         const bool row_valid = fixed_idx < len;
         T* out = reinterpret_cast<T*>(base) + (long long)batch * sb + (long long)head * sh + (long long)fixed_idx * sl;
 #pragma unroll
@@ -566,20 +575,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 o4;
-              o4.x = pack2<T>(__uint_as_float(acc[v * 8 + 0]), __uint_as_float(acc[v * 8 + 1]));
-              o4.y = pack2<T>(__uint_as_float(acc[v * 8 + 2]), __uint_as_float(acc[v * 8 + 3]));
-              o4.z = pack2<T>(__uint_as_float(acc[v * 8 + 4]), __uint_as_float(acc[v * 8 + 5]));
-              o4.w = pack2<T>(__uint_as_float(acc[v * 8 + 6]), __uint_as_float(acc[v * 8 + 7]));
+              o4.x = pack2<T>(__uint_as_float(acc[v * 8 + 0]) * mul, __uint_as_float(acc[v * 8 + 1]) * mul);
+              o4.y = pack2<T>(__uint_as_float(acc[v * 8 + 2]) * mul, __uint_as_float(acc[v * 8 + 3]) * mul);
+              o4.z = pack2<T>(__uint_as_float(acc[v * 8 + 4]) * mul, __uint_as_float(acc[v * 8 + 5]) * mul);
+              o4.w = pack2<T>(__uint_as_float(acc[v * 8 + 6]) * mul, __uint_as_float(acc[v * 8 + 7]) * mul);
               *reinterpret_cast<uint4*>(out + c * 32 + v * 8) = o4;
             }
           }
         }
       };
       if (kDkv) {
-        store_rows(kColAcc0, args.dv, args.dv_stride_b, args.dv_stride_h, args.dv_stride_l, args.len_kv);
-        store_rows(kColAcc1, args.dk, args.dk_stride_b, args.dk_stride_h, args.dk_stride_l, args.len_kv);
+        store_rows(kColAcc0, args.dv, args.dv_stride_b, args.dv_stride_h, args.dv_stride_l, args.len_kv, 1.0f / args.scale);   // P' = P * scale
+        store_rows(kColAcc1, args.dk, args.dk_stride_b, args.dk_stride_h, args.dk_stride_l, args.len_kv, 1.0f);
       } else {
-        store_rows(kColAcc0, args.dq, args.dq_stride_b, args.dq_stride_h, args.dq_stride_l, args.len_q);
+        store_rows(kColAcc0, args.dq, args.dq_stride_b, args.dq_stride_h, args.dq_stride_l, args.len_q, 1.0f);
       }
     }
     // the accumulators are free for the next item's first accumulating MMAs
