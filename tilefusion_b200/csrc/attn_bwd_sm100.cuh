@@ -418,9 +418,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int row = quarter * 32 + lane;                    // lane of tensor memory == row of the fixed tile
     const uint32_t t_lane = tmem_base + (uint32_t(quarter * 32) << 16);
     const uint64_t scale_log2_2 = f2_pack(args.scale_log2, args.scale_log2);
-    // log2(scale) rides in the exponent's addend, so the exponential yields P * scale (what dS needs);
-    // the dK/dV kernel feeds that to dV += P^T dO as well and divides dV by scale on the way out.
-    const float log2_scale = log2f(args.scale);
+    // dQ kernel: log2(scale) rides in the exponent's addend, so the exponential yields P * scale, which is
+    // all dS needs.  The dK/dV kernel needs P itself for dV += P^T dO (P * scale in 16 bits would put more
+    // of the small probabilities into fp16's subnormal range: dV's error grew by half when that was tried)
+    // and multiplies by scale afterwards.
+    const uint64_t scale_2 = f2_pack(args.scale, args.scale);
     bool ok = true;
     uint32_t g = 0;                                         // streamed tiles of earlier items
     uint32_t k_item = 0;                                    // earlier items
@@ -436,7 +438,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     uint64_t my_nlse2 = 0ull, my_ndelta = 0ull;
     if (!kDkv) {
       const bool valid = fixed_idx < args.len_q;
-      const float l2 = valid ? log2_scale - args.lse[row_base + fixed_idx] * 1.4426950408889634f : -INFINITY;
+      const float l2 = valid ? log2f(args.scale) - args.lse[row_base + fixed_idx] * 1.4426950408889634f : -INFINITY;
       const float dl = valid ? -args.delta[row_base + fixed_idx] : 0.f;
       my_nlse2 = f2_pack(l2, l2);
       my_ndelta = f2_pack(dl, dl);
@@ -482,7 +484,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const bool valid = qi < args.len_q;
         // (stored negated: they enter the arithmetic below as addends, two rows per 64-bit operand)
         if (kChunkStep == 1 || chunk == 0)
-          rows_lse2[row] = valid ? log2_scale - args.lse[row_base + qi] * 1.4426950408889634f : -INFINITY;   // P = 0 beyond len_q
+          rows_lse2[row] = valid ? -args.lse[row_base + qi] * 1.4426950408889634f : -INFINITY;   // P = 0 beyond len_q
         if (kChunkStep == 1 || chunk == 1) rows_delta[row] = valid ? -args.delta[row_base + qi] : 0.f;
         bwd_rows_sync();
       }
@@ -503,8 +505,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tmem_ld32(t_lane + col_dp + c * 32, dp);
           tmem_wait_ld();
           uint32_t pk[16], dk[16];
-          // Per pair of streamed rows, in packed fp32 pairs:  P' = P * scale = 2^(s * scale_log2 - lse2
-          // + log2 scale),  dS = P' * (dP - delta).  Two copies of the loop, with and without the mask:
+          // Per pair of streamed rows, in packed fp32 pairs:  P = 2^(s * scale_log2 - lse2),
+          // dS = (P * scale) * (dP - delta); in the dQ kernel the exponential gives P * scale
+          // directly.  Two copies of the loop, with and without the mask:
           // a branch per pair of rows keeps the compiler from interleaving the pairs' dependency chains.
           auto rows = [&](auto masked_c) {
           constexpr bool kMasked = decltype(masked_c)::value;
@@ -536,7 +539,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               }
               const uint64_t p2 = f2_pack(p0, p1);
               float d0, d1;
-              f2_unpack(f2_mul(p2, f2_add(f2_pack(__uint_as_float(dp[j]), __uint_as_float(dp[j + 1])), nd[h2])), d0, d1);
+              const uint64_t dpd = f2_add(f2_pack(__uint_as_float(dp[j]), __uint_as_float(dp[j + 1])), nd[h2]);
+              f2_unpack(f2_mul(kDkv ? f2_mul(p2, scale_2) : p2, dpd), d0, d1);
               pk[j >> 1] = pack2<T>(p0, p1);
               dk[j >> 1] = pack2<T>(d0, d1);
             }
@@ -562,7 +566,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (!ok) break;
     tc_fence_after();
     {
-      auto store_rows = [&](uint32_t col0, void* base, long long sb, long long sh, long long sl, int len, float mul) {
+      auto store_rows = [&](uint32_t col0, void* base, long long sb, long long sh, long long sl, int len) {
         const bool row_valid = fixed_idx < len;
         T* out = reinterpret_cast<T*>(base) + (long long)batch * sb + (long long)head * sh + (long long)fixed_idx * sl;
 #pragma unroll
@@ -575,20 +579,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 o4;
-              o4.x = pack2<T>(__uint_as_float(acc[v * 8 + 0]) * mul, __uint_as_float(acc[v * 8 + 1]) * mul);
-              o4.y = pack2<T>(__uint_as_float(acc[v * 8 + 2]) * mul, __uint_as_float(acc[v * 8 + 3]) * mul);
-              o4.z = pack2<T>(__uint_as_float(acc[v * 8 + 4]) * mul, __uint_as_float(acc[v * 8 + 5]) * mul);
-              o4.w = pack2<T>(__uint_as_float(acc[v * 8 + 6]) * mul, __uint_as_float(acc[v * 8 + 7]) * mul);
+              o4.x = pack2<T>(__uint_as_float(acc[v * 8 + 0]), __uint_as_float(acc[v * 8 + 1]));
+              o4.y = pack2<T>(__uint_as_float(acc[v * 8 + 2]), __uint_as_float(acc[v * 8 + 3]));
+              o4.z = pack2<T>(__uint_as_float(acc[v * 8 + 4]), __uint_as_float(acc[v * 8 + 5]));
+              o4.w = pack2<T>(__uint_as_float(acc[v * 8 + 6]), __uint_as_float(acc[v * 8 + 7]));
               *reinterpret_cast<uint4*>(out + c * 32 + v * 8) = o4;
             }
           }
         }
       };
       if (kDkv) {
-        store_rows(kColAcc0, args.dv, args.dv_stride_b, args.dv_stride_h, args.dv_stride_l, args.len_kv, 1.0f / args.scale);   // P' = P * scale
-        store_rows(kColAcc1, args.dk, args.dk_stride_b, args.dk_stride_h, args.dk_stride_l, args.len_kv, 1.0f);
+        store_rows(kColAcc0, args.dv, args.dv_stride_b, args.dv_stride_h, args.dv_stride_l, args.len_kv);
+        store_rows(kColAcc1, args.dk, args.dk_stride_b, args.dk_stride_h, args.dk_stride_l, args.len_kv);
       } else {
-        store_rows(kColAcc0, args.dq, args.dq_stride_b, args.dq_stride_h, args.dq_stride_l, args.len_q, 1.0f);
+        store_rows(kColAcc0, args.dq, args.dq_stride_b, args.dq_stride_h, args.dq_stride_l, args.len_q);
       }
     }
     // the accumulators are free for the next item's first accumulating MMAs
