@@ -196,9 +196,11 @@ def test_decode_plan_for_an_8bit_cache(native_lib):
         d.kv_dtype = code
         assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == 0
         assert plan.stages == 3 and plan.workspace_bytes == 4 * 32 * plan.num_splits * 130 * 4
+    # grouped-query heads over an 8-bit cache: the split kernel's plan (one item per query head and
+    # split), not the two-tile kernel's
     d.heads_kv = 8
-    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_UNSUPPORTED
-    assert "grouped-query" in native_lib.tf_last_error().decode()
+    assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == 0
+    assert plan.reserved == 0 and plan.workspace_bytes == 4 * 32 * plan.num_splits * 130 * 4
     d.heads_kv = 0
     d.k_stride_h += 8
     assert native_lib.tf_decode_plan(C.byref(d), C.byref(plan)) == _cabi.TF_ERR_UNSUPPORTED

@@ -238,13 +238,82 @@ def test_sharded_context_and_static_entry_over_8bit_cache():
     assert device_status() == 0
 
 
+GROUPED_CASES = [
+    # B, Hkv, group, Lk, D, kv_chunk, num_splits
+    (2, 2, 4, 1000, 128, 512, 0),
+    (1, 1, 8, 4096, 128, 1024, 0),    # multi-query: one KV head
+    (3, 2, 2, 777, 64, 256, 0),
+    (2, 3, 5, 2049, 128, 512, 3),     # a group size that is no power of two, uneven splits
+    (1, 2, 32, 300, 64, 128, 0),
+]
+
+
+@pytest.mark.parametrize("case", GROUPED_CASES, ids=lambda c: "x".join(map(str, c)))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("kind", list(KINDS))
+def test_grouped_query_heads_over_8bit_cache_match_oracle(case, dtype, kind):
+    """Query head h reads KV head h // group; every query head is a row of its own."""
+    from cabi_helpers import decode, device_status
+
+    b, hkv, g, lk, d, chunk, splits = case
+    q, _, _ = orc.seeded_inputs(41, (b, hkv * g, 1, d), (1, 1, 8, d), (1, 1, 8, d), 1.0, dtype)
+    _, k8, v8, k_exact, v_exact = _cache(43, b, hkv, lk, d, kind, dtype, k_factor=2.0, v_factor=4.0)
+    o, lse = decode(q.cuda(), k8.cuda(), v8.cuda(), None, chunk, splits, k_scale=0.5, v_scale=0.25)
+    ref, lse_ref = orc.decode_fp32(q, k_exact.repeat_interleave(g, dim=1), v_exact.repeat_interleave(g, dim=1))
+    _check(o, lse, ref, lse_ref, dtype)
+    assert device_status() == 0
+
+
+def test_grouped_query_heads_over_paged_8bit_cache_static_and_sharded():
+    """The same rows through the paged operator, the no-allocation entry point and the one-launch
+    sharded step (world of one)."""
+    import ctypes as C
+
+    import tilefusion_b200 as tilefusion
+    from cabi_helpers import decode_desc, device_status
+    from tilefusion_b200 import _cabi
+
+    b, hkv, g, lk, d, kind = 2, 2, 4, 1500, 128, f8.E4M3
+    q, _, _ = orc.seeded_inputs(45, (b, hkv * g, 1, d), (1, 1, 8, d), (1, 1, 8, d), 1.0, torch.float16)
+    _, k8, v8, k_exact, v_exact = _cache(47, b, hkv, lk, d, kind, torch.float16, k_factor=2.0)
+    ref, lse_ref = orc.decode_fp32(q, k_exact.repeat_interleave(g, dim=1), v_exact.repeat_interleave(g, dim=1))
+
+    kp, vp, table = _paginate(k8.view(torch.uint8), v8.view(torch.uint8), 256, 7)
+    o, lse = tilefusion.ops.flash_decoding(q.cuda(), _as_fp8(kp, kind).cuda(), _as_fp8(vp, kind).cuda(),
+                                           block_table=table.cuda(), kv_len=lk, k_scale=0.5)
+    _check(o, lse, ref, lse_ref, torch.float16)
+
+    qd, kd, vd = q.cuda(), k8.cuda(), v8.cuda()
+    lib = _cabi.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    o = torch.full((b, hkv * g, 1, d), float("nan"), dtype=torch.float16, device="cuda")
+    lse = torch.full((b, hkv * g, 1), float("nan"), dtype=torch.float32, device="cuda")
+    desc = decode_desc(qd, kd, vd, o, k_scale=0.5)
+    _cabi.check(lib.tf_decode_static(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                     C.byref(desc), stream))
+    _check(o, lse, ref, lse_ref, torch.float16)
+
+    ctx = C.c_void_p()
+    _cabi.check(lib.tf_shard_create(0, 1, None, _cabi.TF_TRANSPORT_P2P, b, hkv * g, d, _cabi.TF_F16, C.byref(ctx)))
+    try:
+        o.fill_(float("nan"))
+        lse.fill_(float("nan"))
+        _cabi.check(lib.tf_decode_sharded(ctx, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(),
+                                          lse.data_ptr(), C.byref(desc), stream))
+        _check(o, lse, ref, lse_ref, torch.float16)
+    finally:
+        torch.cuda.synchronize()
+        lib.tf_shard_destroy(ctx)
+    assert device_status() == 0
+
+
 def test_unsupported_8bit_layouts_report_errors():
     from cabi_helpers import decode_desc, decode_plan
     from tilefusion_b200 import _cabi
 
     q = torch.zeros(1, 8, 1, 128, dtype=torch.float16, device="cuda")
-    k = torch.zeros(1, 2, 256, 128, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
-    with pytest.raises(_cabi.TileFusionError, match="grouped-query"):
+    k = torch.zeros(1, 3, 256, 128, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    with pytest.raises(_cabi.TileFusionError, match="multiple of heads_kv"):
         decode_plan(decode_desc(q, k, k))
     k = torch.zeros(1, 8, 256, 128, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
     d = decode_desc(q, k, k)

@@ -80,7 +80,7 @@ def test_random_decode_shapes(seed):
         g = rng.choice([1, 1, 2, 4, 8, 32, 64])
         lk = rng.choice([1, 31, 33, 127, 128, 129, 640, 1000, 2049, 5000])
         chunk, splits = rng.choice([128, 256, 512, 1024]), rng.choice([0, 0, 1, 3])
-        fp8 = g == 1 and rng.random() < 0.5
+        fp8 = g <= 8 and rng.random() < 0.5
         q, k, v = orc.seeded_inputs(2000 * seed + it, (b, hkv * g, 1, d), (b, hkv, lk, d), (b, hkv, lk, d), 1.0, dt)
         name = f"decode B{b} Hkv{hkv} group{g} Lk{lk} D{d} chunk{chunk} splits{splits} fp8={fp8} {dt}"
         if fp8:
@@ -89,7 +89,8 @@ def test_random_decode_shapes(seed):
             k8, v8 = f8.quantize(k, kind, 2.0), f8.quantize(v, kind, 2.0)
             o, lse = decode(q.cuda(), k8.view(tdt).cuda(), v8.view(tdt).cuda(), None, chunk, splits,
                             k_scale=0.5, v_scale=0.5)
-            ref, lse_ref = orc.decode_fp32(q, f8.decode(k8, kind) * 0.5, f8.decode(v8, kind) * 0.5)
+            ref, lse_ref = orc.decode_fp32(q, (f8.decode(k8, kind) * 0.5).repeat_interleave(g, dim=1),
+                                           (f8.decode(v8, kind) * 0.5).repeat_interleave(g, dim=1))
         else:
             o, lse = decode(q.cuda(), k.cuda(), v.cuda(), None, chunk, splits)
             ref, lse_ref = orc.decode_fp32(q, k.repeat_interleave(g, dim=1), v.repeat_interleave(g, dim=1))

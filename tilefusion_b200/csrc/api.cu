@@ -468,8 +468,6 @@ int check_decode_desc(const TfDecodeDesc* d) {
   if (d->kv_dtype != 0 && d->kv_dtype != d->dtype && !kv_is_fp8(d))
     return fail(TF_ERR_UNSUPPORTED, "kv_dtype must be 0, equal to dtype, TF_FP8_E4M3 or TF_FP8_E5M2 (got %d)", d->kv_dtype);
   if (kv_is_fp8(d)) {
-    if (d->heads_kv > 0 && d->heads_kv != d->heads)
-      return fail(TF_ERR_UNSUPPORTED, "grouped-query decoding reads a 16-bit K/V cache; an 8-bit cache needs heads_kv == heads");
     const int64_t kv[] = {d->k_stride_b, d->k_stride_h, d->v_stride_b, d->v_stride_h,
                           d->page_size != 0 ? d->k_stride_page : 0, d->page_size != 0 ? d->v_stride_page : 0};
     for (int64_t x : kv)
@@ -502,6 +500,7 @@ int launch_decode_split(const void* q, const void* k, const void* v, float* part
   a.part_o = part_o;
   a.part_ml = part_ml;
   a.heads = d->heads;
+  a.group = (d->heads_kv > 0 && d->heads_kv != d->heads) ? d->heads / d->heads_kv : 1;
   a.len_kv = d->len_kv;
   a.kv_chunk = plan.kv_chunk;
   a.num_splits = plan.num_splits;
@@ -624,7 +623,10 @@ int launch_gqa_split(const void* q, const void* k, const void* v, float* part_o,
              : launch_attn_pair<__nv_bfloat16, 64>(L, &ad, ap, stream, kv_splits, plan.chunks_per_split, part_o, part_ml, table, d->page_size, d->max_pages);
 }
 
-bool is_grouped(const TfDecodeDesc* d) { return d->heads_kv > 0 && d->heads_kv != d->heads; }
+// Grouped-query heads over a 16-bit cache run on the two-tile (tensor-core) kernel.  Over an 8-bit
+// cache they run on the split kernel, one work item per query head and split: each query head of a
+// group streams its KV head's chunks itself (the re-reads within a group meet in L2).
+bool is_grouped(const TfDecodeDesc* d) { return d->heads_kv > 0 && d->heads_kv != d->heads && !kv_is_fp8(d); }
 
 // KvTag: an 8-bit storage tag, or void for a cache stored in the query's type.
 template <typename KvTag>

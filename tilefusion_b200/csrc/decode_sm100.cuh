@@ -144,7 +144,8 @@ struct DecodeSplitArgs {
   const void* v;
   float* part_o;      // [items][D]
   float* part_ml;     // [items][2]
-  int heads;
+  int heads;          // query heads
+  int group;          // query heads per KV head: head h reads K/V head h / group
   int len_kv;
   int kv_chunk;
   int num_splits;
@@ -405,10 +406,11 @@ __global__ void __launch_bounds__(kDecThreads, 2) decode_split_kernel(const Deco
         const int b = bh / args.heads, h = bh - b * args.heads;
         const bool paged = args.page_size > 0;
         // byte addresses: strides count elements of the stored type
+        const int hk = h / args.group;                      // the KV head this query head reads
         const uint8_t* kbase = reinterpret_cast<const uint8_t*>(args.k) +
-                               ((paged ? 0 : b * args.k_stride_b) + h * args.k_stride_h) * kKvBytes;
+                               ((paged ? 0 : b * args.k_stride_b) + hk * args.k_stride_h) * kKvBytes;
         const uint8_t* vbase = reinterpret_cast<const uint8_t*>(args.v) +
-                               ((paged ? 0 : b * args.v_stride_b) + h * args.v_stride_h) * kKvBytes;
+                               ((paged ? 0 : b * args.v_stride_b) + hk * args.v_stride_h) * kKvBytes;
         const int* pages = paged ? args.block_table + (long long)b * args.max_pages : nullptr;
         const int key_begin = split * keys_per_split;
         const int key_end = min(args.len_kv, key_begin + keys_per_split);

@@ -75,8 +75,9 @@ int default_kv_chunk(const TfDecodeDesc& d) {
 }
 
 void plan_decode(const TfDecodeDesc& d, int sm_count, TfDecodePlan* plan) {
-  if (d.heads_kv > 0 && d.heads_kv != d.heads) {
-    // Grouped-query decoding runs on the two-tile attention kernel in split-KV
+  const bool kv8 = d.kv_dtype == TF_FP8_E4M3 || d.kv_dtype == TF_FP8_E5M2;
+  if (d.heads_kv > 0 && d.heads_kv != d.heads && !kv8) {
+    // Grouped-query decoding over a 16-bit cache runs on the two-tile attention kernel in split-KV
     // mode: work item = (batch, KV head, split), a split walks whole 128-key
     // tiles.  Enough splits for about two items per SM, never an empty one.
     const int64_t groups = (int64_t)d.batch * d.heads_kv;
@@ -112,7 +113,6 @@ void plan_decode(const TfDecodeDesc& d, int sm_count, TfDecodePlan* plan) {
     plan->workspace_bytes = (uint64_t)d.batch * d.heads * splits * copies * (d.head_dim + 2) * sizeof(float);
     return;
   }
-  const bool kv8 = d.kv_dtype == TF_FP8_E4M3 || d.kv_dtype == TF_FP8_E5M2;
   const int chunk = d.kv_chunk == 0 ? default_kv_chunk(d) : d.kv_chunk;
   const int64_t bh = (int64_t)d.batch * d.heads;
   const int n_chunks = std::max(1, (d.len_kv + chunk - 1) / chunk);

@@ -35,8 +35,9 @@ class FlashDecoding:
         ``block_table`` (int32 ``[B, max_pages]``) and ``kv_len`` -- a paged cache
         ``[num_pages, H_kv, page_size, D]`` whose page ``block_table[b, i]`` holds keys
         ``[i * page_size, (i + 1) * page_size)`` of batch entry ``b``.  ``key`` / ``value``
-        may be ``torch.float8_e4m3fn`` or ``torch.float8_e5m2`` (one KV head per query
-        head): the cache is read as ``k_scale * key`` and ``v_scale * value``.
+        may be ``torch.float8_e4m3fn`` or ``torch.float8_e5m2``: the cache is read as
+        ``k_scale * key`` and ``v_scale * value`` (with grouped-query heads every query
+        head then streams its KV head's bytes itself).
 
         Returns ``O [B, H, 1, D]`` and ``LSE [B, H, 1]`` (fp32, natural log).
         """
